@@ -1,0 +1,47 @@
+/* Entry points that exist only in the B200 engine (no counterpart in the
+ * reference): introspection and tooling hooks used by the tests, the
+ * benchmark and build-time kernel checks. None of them computes anything. */
+#ifndef GPUARRAY_B200_H
+#define GPUARRAY_B200_H
+
+#include <gpuarray/buffer.h>
+#include <gpuarray/elemwise.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Code of the last error recorded on `ctx` (NULL: the process-global record);
+ * gpucontext_error() gives the matching text. */
+GPUARRAY_PUBLIC int gpuarray_b200_error_code(gpucontext *ctx);
+
+/* Compiles CUDA C++ `src` for sm_100a with the library's in-memory headers
+ * ("cluda.h", the kernel templates) and NVRTC; needs no GPU. `defines` is a
+ * NULL-terminated list of "-DNAME=VALUE" options or NULL; `cache_dir` (may be
+ * NULL) is a directory of cubin files reused across runs. On failure *log
+ * (malloc'ed, may be NULL) holds the numbered source and the compiler log. */
+GPUARRAY_PUBLIC int gpuarray_b200_compile_check(const char *src, const char *const *defines,
+                                                const char *cache_dir, size_t *cubin_size,
+                                                char **log);
+
+/* The kernel source GpuElemwise would compile for one variant: kind 0
+ * contiguous, 1 strided, 2 tiled transpose; `ept` elements per thread chunk;
+ * `modes` packs two bits per array argument (0 scalar access, 1 vector,
+ * 2 broadcast). malloc'ed; the caller frees. */
+GPUARRAY_PUBLIC char *gpuarray_b200_elemwise_source(const char *preamble, const char *expr,
+                                                    unsigned int n, gpuelemwise_arg *args,
+                                                    int flags, int kind, int ept, int unroll,
+                                                    unsigned int nd, int idx32,
+                                                    unsigned long long modes, int tp, int tq);
+
+/* The kernel source GpuReduction would compile for one variant: `shape`
+ * 0 rows, 1 cols, 2 general; `vec` elements per load; `tpo` threads per
+ * output (general); `stage2` non-zero for the pass over partial results.
+ * malloc'ed; the caller frees. */
+GPUARRAY_PUBLIC char *gpuarray_b200_reduction_source(int op, int src_tc, int dst_tc, int shape,
+                                                     int vec, int idx64, int tpo, int stage2);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

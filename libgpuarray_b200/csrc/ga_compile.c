@@ -1,0 +1,279 @@
+/* Kernel source -> sm_100a machine code -> CUfunction.
+ *
+ * Replaces the compile half of the reference's CUDA backend
+ * (src/gpuarray_buffer_cuda.c:1073-1482): there, source goes NVRTC -> PTX for
+ * "compute_XY" -> cuLink -> cubin, the architecture string is derived from the
+ * device (and comes out truncated for compute capability 10.0), and a 2Q cache
+ * is keyed by the full source text. Here NVRTC is asked for sm_100a SASS
+ * directly (nvrtcGetCUBIN), the only option besides the architecture is the
+ * language level, so floating-point contraction stays at NVRTC's default
+ * (fused multiply-add on), like the reference which passes only -arch.
+ *
+ * Caches: per context, a list of loaded modules keyed by a 128-bit hash of
+ * (library tag, options, source); optionally a directory of cubin files with
+ * the same key (GPUARRAY_CACHE_PATH or gpucontext_props_kernel_cache), which
+ * can be filled on a machine without a GPU. */
+#include <sys/stat.h>
+#include <unistd.h>
+#include "private.h"
+
+#define GA_KERNEL_ABI_TAG "ga-b200-k1"
+#define GA_ARCH_OPT "--gpu-architecture=sm_100a"
+
+struct ga_module {
+  uint64_t key[2];
+  CUmodule mod;
+  struct ga_module *next;
+};
+
+static void make_key(const char *src, const char *const *defines, uint64_t key[2]) {
+  ga_strb sb;
+  unsigned int i;
+  ga_strb_init(&sb);
+  ga_strb_puts(&sb, GA_KERNEL_ABI_TAG "\n" GA_ARCH_OPT "\n");
+  if (defines != NULL)
+    for (; *defines != NULL; defines++) {
+      ga_strb_puts(&sb, *defines);
+      ga_strb_puts(&sb, "\n");
+    }
+  /* the in-library headers are part of the program text */
+  for (i = 0; i < ga_template_count; i++) {
+    uint64_t h = ga_hash64(ga_template_sources[i], strlen(ga_template_sources[i]), 7);
+    ga_strb_printf(&sb, "%s:%016llx\n", ga_template_names[i], (unsigned long long)h);
+  }
+  ga_strb_puts(&sb, src);
+  key[0] = ga_hash64(ga_strb_cstr(&sb), sb.len, 0);
+  key[1] = ga_hash64(ga_strb_cstr(&sb), sb.len, 0x9e3779b97f4a7c15ULL);
+  ga_strb_free(&sb);
+}
+
+/* "0001\t<line>\n..." followed by the compiler log, like the reference's
+ * gpukernel_source_with_line_numbers (src/gpuarray_util.c:85-109). */
+static char *numbered_listing(const char *src, const char *log) {
+  ga_strb sb;
+  unsigned line = 1;
+  const char *p = src, *nl;
+  ga_strb_init(&sb);
+  while (*p != '\0') {
+    nl = strchr(p, '\n');
+    ga_strb_printf(&sb, "%04u\t", line++);
+    if (nl == NULL) {
+      ga_strb_puts(&sb, p);
+      ga_strb_puts(&sb, "\n");
+      break;
+    }
+    ga_strb_putn(&sb, p, (size_t)(nl - p) + 1);
+    p = nl + 1;
+  }
+  if (log != NULL) {
+    ga_strb_puts(&sb, "\nCompiler log:\n");
+    ga_strb_puts(&sb, log);
+  }
+  return sb.s; /* ownership moves to the caller */
+}
+
+static int disk_get(const char *dir, const uint64_t key[2], char **bin, size_t *sz) {
+  char path[4096];
+  FILE *f;
+  long n;
+  if (dir == NULL) return -1;
+  snprintf(path, sizeof(path), "%s/%016llx%016llx.cubin", dir, (unsigned long long)key[0],
+           (unsigned long long)key[1]);
+  f = fopen(path, "rb");
+  if (f == NULL) return -1;
+  if (fseek(f, 0, SEEK_END) != 0 || (n = ftell(f)) <= 0 || fseek(f, 0, SEEK_SET) != 0) {
+    fclose(f);
+    return -1;
+  }
+  *bin = malloc((size_t)n);
+  if (*bin == NULL || fread(*bin, 1, (size_t)n, f) != (size_t)n) {
+    free(*bin);
+    *bin = NULL;
+    fclose(f);
+    return -1;
+  }
+  fclose(f);
+  *sz = (size_t)n;
+  return 0;
+}
+
+static void disk_put(const char *dir, const uint64_t key[2], const char *bin, size_t sz) {
+  char path[4096], tmp[4200];
+  FILE *f;
+  if (dir == NULL) return;
+  mkdir(dir, 0777);
+  snprintf(path, sizeof(path), "%s/%016llx%016llx.cubin", dir, (unsigned long long)key[0],
+           (unsigned long long)key[1]);
+  snprintf(tmp, sizeof(tmp), "%s.%ld.tmp", path, (long)getpid());
+  f = fopen(tmp, "wb");
+  if (f == NULL) return;
+  if (fwrite(bin, 1, sz, f) == sz && fclose(f) == 0) rename(tmp, path);
+  else {
+    unlink(tmp);
+  }
+}
+
+static int nvrtc_build(ga_error_rec *e, const char *src, const char *const *defines, char **bin,
+                       size_t *bin_sz, char **err_str) {
+  nvrtcProgram prog = NULL;
+  nvrtcResult r;
+  const char *opts[64];
+  int nopts = 0, err;
+  size_t logsz = 0;
+  char *log = NULL;
+
+  err = ga_load_nvrtc(e);
+  if (err != GA_NO_ERROR) return err;
+
+  opts[nopts++] = GA_ARCH_OPT;
+  opts[nopts++] = "--std=c++17";
+  if (defines != NULL)
+    for (; *defines != NULL && nopts < 63; defines++) opts[nopts++] = *defines;
+
+  r = ga_rtc.p_nvrtcCreateProgram(&prog, src, "ga_kernel.cu", (int)ga_template_count,
+                                  (const char *const *)ga_template_sources,
+                                  (const char *const *)ga_template_names);
+  if (r != NVRTC_SUCCESS)
+    return ga_err_fmt(e, GA_IMPL_ERROR, "nvrtcCreateProgram: %s", ga_rtc.p_nvrtcGetErrorString(r));
+
+  r = ga_rtc.p_nvrtcCompileProgram(prog, nopts, opts);
+  if (r != NVRTC_SUCCESS) {
+    if (ga_rtc.p_nvrtcGetProgramLogSize(prog, &logsz) == NVRTC_SUCCESS && logsz > 1) {
+      log = malloc(logsz);
+      if (log != NULL && ga_rtc.p_nvrtcGetProgramLog(prog, log) != NVRTC_SUCCESS) {
+        free(log);
+        log = NULL;
+      }
+    }
+    if (err_str != NULL) *err_str = numbered_listing(src, log);
+    /* keep the head of the log in the error message: it usually names the
+     * offending token of the user's expression */
+    err = ga_err_fmt(e, GA_IMPL_ERROR, "nvrtcCompileProgram: %s%s%.800s",
+                     ga_rtc.p_nvrtcGetErrorString(r), log ? ": " : "", log ? log : "");
+    free(log);
+    ga_rtc.p_nvrtcDestroyProgram(&prog);
+    return err;
+  }
+  r = ga_rtc.p_nvrtcGetCUBINSize(prog, bin_sz);
+  if (r == NVRTC_SUCCESS) {
+    *bin = malloc(*bin_sz);
+    if (*bin == NULL) {
+      ga_rtc.p_nvrtcDestroyProgram(&prog);
+      return ga_err_sys(e, "malloc");
+    }
+    r = ga_rtc.p_nvrtcGetCUBIN(prog, *bin);
+  }
+  ga_rtc.p_nvrtcDestroyProgram(&prog);
+  if (r != NVRTC_SUCCESS) {
+    free(*bin);
+    *bin = NULL;
+    return ga_err_fmt(e, GA_IMPL_ERROR, "nvrtcGetCUBIN: %s", ga_rtc.p_nvrtcGetErrorString(r));
+  }
+  return GA_NO_ERROR;
+}
+
+int ga_compile_cubin(ga_error_rec *e, const char *src, const char *const *defines,
+                     const char *cache_dir, char **bin, size_t *bin_sz, char **err_str) {
+  uint64_t key[2];
+  int err;
+  if (err_str != NULL) *err_str = NULL;
+  make_key(src, defines, key);
+  if (disk_get(cache_dir, key, bin, bin_sz) == 0) return GA_NO_ERROR;
+  err = nvrtc_build(e, src, defines, bin, bin_sz, err_str);
+  if (err == GA_NO_ERROR) disk_put(cache_dir, key, *bin, *bin_sz);
+  return err;
+}
+
+int ga_compile(gpucontext *ctx, const char *src, const char *fname, const char *const *defines,
+               ga_function *out, char **err_str) {
+  uint64_t key[2];
+  struct ga_module *m;
+  CUresult r;
+  int err = GA_NO_ERROR;
+
+  if (err_str != NULL) *err_str = NULL;
+  make_key(src, defines, key);
+  for (m = ctx->modules; m != NULL; m = m->next)
+    if (m->key[0] == key[0] && m->key[1] == key[1]) break;
+
+  if (m == NULL) {
+    char *bin = NULL;
+    size_t bin_sz = 0;
+    if (disk_get(ctx->kernel_cache_path, key, &bin, &bin_sz) != 0) {
+      err = nvrtc_build(ctx->err, src, defines, &bin, &bin_sz, err_str);
+      if (err != GA_NO_ERROR) return err;
+      disk_put(ctx->kernel_cache_path, key, bin, bin_sz);
+    }
+    m = calloc(1, sizeof(*m));
+    if (m == NULL) {
+      free(bin);
+      return ga_err_sys(ctx->err, "calloc");
+    }
+    ga_ctx_enter(ctx);
+    r = ga_cu.p_cuModuleLoadData(&m->mod, bin);
+    ga_ctx_exit(ctx);
+    free(bin);
+    if (r != CUDA_SUCCESS) {
+      free(m);
+      return ga_err_cuda(ctx->err, "cuModuleLoadData", r);
+    }
+    m->key[0] = key[0];
+    m->key[1] = key[1];
+    m->next = ctx->modules;
+    ctx->modules = m;
+  }
+
+  ga_ctx_enter(ctx);
+  r = ga_cu.p_cuModuleGetFunction(&out->f, m->mod, fname);
+  if (r != CUDA_SUCCESS) err = ga_err_cuda(ctx->err, "cuModuleGetFunction", r);
+  else {
+    ga_cu.p_cuFuncGetAttribute(&out->max_threads, CU_FUNC_ATTRIBUTE_MAX_THREADS_PER_BLOCK, out->f);
+    ga_cu.p_cuFuncGetAttribute(&out->num_regs, CU_FUNC_ATTRIBUTE_NUM_REGS, out->f);
+    ga_cu.p_cuFuncGetAttribute(&out->static_smem, CU_FUNC_ATTRIBUTE_SHARED_SIZE_BYTES, out->f);
+  }
+  ga_ctx_exit(ctx);
+  return err;
+}
+
+void ga_modules_free(gpucontext *ctx) {
+  struct ga_module *m, *n;
+  for (m = ctx->modules; m != NULL; m = n) {
+    n = m->next;
+    ga_cu.p_cuModuleUnload(m->mod);
+    free(m);
+  }
+  ctx->modules = NULL;
+}
+
+int ga_launch(gpucontext *ctx, const ga_function *fn, const unsigned grid[3],
+              const unsigned block[3], size_t shared, void **params) {
+  CUresult r;
+  ga_ctx_enter(ctx);
+  if (shared + (size_t)fn->static_smem > ctx->smem_block) {
+    r = ga_cu.p_cuFuncSetAttribute(fn->f, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
+                                   (int)shared);
+    if (r != CUDA_SUCCESS) {
+      ga_ctx_exit(ctx);
+      return ga_err_cuda(ctx->err, "cuFuncSetAttribute", r);
+    }
+  }
+  r = ga_cu.p_cuLaunchKernel(fn->f, grid[0], grid[1], grid[2], block[0], block[1], block[2],
+                             (unsigned)shared, ctx->s, params, NULL);
+  ga_ctx_exit(ctx);
+  if (r != CUDA_SUCCESS) return ga_err_cuda(ctx->err, "cuLaunchKernel", r);
+  return GA_NO_ERROR;
+}
+
+/* Test and tooling hook: compile a program for sm_100a without any device.
+ * Returns GA_NO_ERROR and the cubin size, or an error with *log (malloc'ed,
+ * may be NULL) holding the numbered source and compiler output. */
+GPUARRAY_PUBLIC int gpuarray_b200_compile_check(const char *src, const char *const *defines,
+                                               const char *cache_dir, size_t *cubin_size,
+                                               char **log) {
+  char *bin = NULL;
+  size_t sz = 0;
+  int err = ga_compile_cubin(ga_global_err, src, defines, cache_dir, &bin, &sz, log);
+  free(bin);
+  if (cubin_size != NULL) *cubin_size = sz;
+  return err;
+}

@@ -1,0 +1,602 @@
+/* Elementwise engine: GpuElemwise_new / _call / _free.
+ *
+ * Host side of the path that the reference implements in
+ * src/gpuarray_elemwise.c. The argument checking, broadcasting and collapsing
+ * rules are the reference's (check_contig :547-576, check_basic :272-383);
+ * what differs is everything after them:
+ *   - kernels are instances of three hand-written sm_100a templates
+ *     (templates/ga_ew_contig.cuh, ga_ew_strided.cuh, ga_ew_transpose.cuh)
+ *     with the user's expression compiled in as an inlined function;
+ *   - variants are built on first use and keyed by what actually changes the
+ *     code (vector width, rank, index width, per-argument access mode), not
+ *     one kernel per rank and address width built eagerly (:672-730);
+ *   - device pointers are passed with the array offset already applied, and
+ *     shape/stride data travels as one kernel parameter block, so a call is a
+ *     single cuLaunchKernel.
+ */
+#include "private.h"
+
+#define GA_EW_THREADS 256
+#define GA_EW_MAX_ND 16
+
+typedef struct ew_variant {
+  int kind;              /* 0 contig, 1 strided, 2 transpose */
+  int ept;
+  int unroll;
+  unsigned int nd;
+  int idx32;
+  unsigned long long modes; /* 2 bits per array */
+  int tp, tq;            /* transpose: tile axes */
+  ga_function fn;
+  struct ew_variant *next;
+} ew_variant;
+
+struct _GpuElemwise {
+  gpucontext *ctx;
+  char *expr;
+  char *preamble;
+  gpuelemwise_arg *args;
+  unsigned int n;        /* arguments */
+  unsigned int narray;
+  int flags;
+  int ept;               /* elements per thread-chunk giving 16-byte accesses */
+  unsigned int min_elsize, max_elsize;
+  ew_variant *variants;
+  /* call-time scratch, sized for `nd_cap` dimensions */
+  unsigned int nd_cap;
+  size_t *dims;
+  ssize_t **strides;     /* narray vectors */
+  unsigned long long *blob;
+  size_t blob_words;
+  void **params;
+};
+
+static int is_array(const gpuelemwise_arg *a) { return ISCLR(a->flags, GE_SCALAR); }
+static int is_output(const gpuelemwise_arg *a) { return ISSET(a->flags, GE_WRITE); }
+
+/* Tuning knobs for experiments: GPUARRAY_B200_EW="threads,unroll,gridcap_per_sm". */
+static void ew_tuning(int *unroll, unsigned *gridcap_per_sm) {
+  static int parsed = 0, t_unroll = 4;
+  static unsigned t_cap = 0;
+  if (!parsed) {
+    const char *env = getenv("GPUARRAY_B200_EW");
+    if (env != NULL) sscanf(env, "%d,%u", &t_unroll, &t_cap);
+    if (t_unroll < 1 || t_unroll > 8) t_unroll = 4;
+    parsed = 1;
+  }
+  *unroll = t_unroll;
+  *gridcap_per_sm = t_cap;
+}
+
+/* ---------------------------------------------------------------- codegen */
+
+static const char *compute_type(const GpuElemwise *ge, const gpuelemwise_arg *a) {
+  if (a->typecode == GA_HALF && ISSET(ge->flags, GE_CONVERT_F16)) return "ga_float";
+  return ga_ctype(a->typecode);
+}
+
+/* Everything up to (not including) the #include of a template. */
+static void gen_prologue(const GpuElemwise *ge, ga_strb *sb, const ew_variant *v) {
+  unsigned int j, k;
+  ga_strb_puts(sb, "#include \"cluda.h\"\n");
+  if (ge->preamble != NULL) ga_strb_puts(sb, ge->preamble);
+  ga_strb_puts(sb, "\n#define GA_EW_ARRAYS(X)");
+  for (j = 0, k = 0; j < ge->n; j++) {
+    const gpuelemwise_arg *a = &ge->args[j];
+    if (!is_array(a)) continue;
+    ga_strb_printf(sb, " \\\n  X(%u, %s, %s, %s, %d, %d, %d)", k, a->name, ga_ctype(a->typecode),
+                   compute_type(ge, a), ISSET(a->flags, GE_READ) ? 1 : 0, is_output(a) ? 1 : 0,
+                   (int)((v->modes >> (2 * k)) & 3));
+    k++;
+  }
+  ga_strb_puts(sb, "\n#define GA_EW_SCALARS(X)");
+  for (j = 0; j < ge->n; j++) {
+    const gpuelemwise_arg *a = &ge->args[j];
+    if (is_array(a)) continue;
+    ga_strb_printf(sb, " \\\n  X(%s, %s)", a->name, ga_ctype(a->typecode));
+  }
+  ga_strb_printf(sb,
+                 "\n#define GA_EW_EPT %d\n#define GA_EW_UNROLL %d\n#define GA_EW_THREADS %d\n"
+                 "#define GA_EW_IDX %s\n#define GA_EW_IDX32 %d\n#define GA_EW_ND %u\n"
+                 "#define GA_EW_NARR %u\n",
+                 v->ept, v->unroll, GA_EW_THREADS, v->idx32 ? "unsigned int" : "size_t",
+                 v->idx32, v->nd ? v->nd : 1, ge->narray ? ge->narray : 1);
+  if (v->kind == 2) ga_strb_printf(sb, "#define GA_EW_TP %d\n#define GA_EW_TQ %d\n", v->tp, v->tq);
+
+  /* The expression sees each argument as a scalar variable of its own name. */
+  ga_strb_puts(sb, "static __device__ __forceinline__ void ga_ew_apply(");
+  for (j = 0; j < ge->n; j++) {
+    const gpuelemwise_arg *a = &ge->args[j];
+    if (is_array(a)) ga_strb_printf(sb, "%s &%s, ", compute_type(ge, a), a->name);
+  }
+  for (j = 0; j < ge->n; j++) {
+    const gpuelemwise_arg *a = &ge->args[j];
+    if (!is_array(a)) ga_strb_printf(sb, "%s %s, ", ga_ctype(a->typecode), a->name);
+  }
+  ga_strb_puts(sb, "int ga__unused) {\n");
+  ga_strb_puts(sb, ge->expr);
+  ga_strb_puts(sb, ";\n}\n");
+}
+
+static const char *const kind_header[] = {"ga_ew_contig.cuh", "ga_ew_strided.cuh",
+                                          "ga_ew_transpose.cuh"};
+static const char *const kind_entry[] = {"ga_ew_contig", "ga_ew_strided", "ga_ew_transpose"};
+
+static char *gen_source(const GpuElemwise *ge, const ew_variant *v) {
+  ga_strb sb;
+  ga_strb_init(&sb);
+  gen_prologue(ge, &sb, v);
+  ga_strb_printf(&sb, "#include \"%s\"\n", kind_header[v->kind]);
+  if (sb.failed) {
+    ga_strb_free(&sb);
+    return NULL;
+  }
+  return sb.s;
+}
+
+static ew_variant *get_variant(GpuElemwise *ge, const ew_variant *want, int *err) {
+  ew_variant *v;
+  char *src, *listing = NULL;
+  for (v = ge->variants; v != NULL; v = v->next)
+    if (v->kind == want->kind && v->ept == want->ept && v->unroll == want->unroll &&
+        v->nd == want->nd && v->idx32 == want->idx32 && v->modes == want->modes &&
+        v->tp == want->tp && v->tq == want->tq)
+      return v;
+  v = malloc(sizeof(*v));
+  if (v == NULL) {
+    *err = ga_err_sys(ge->ctx->err, "malloc");
+    return NULL;
+  }
+  *v = *want;
+  src = gen_source(ge, v);
+  if (src == NULL) {
+    free(v);
+    *err = ga_err_set(ge->ctx->err, GA_MISC_ERROR, "Formatting error creating kernel source");
+    return NULL;
+  }
+  *err = ga_compile(ge->ctx, src, kind_entry[v->kind], NULL, &v->fn,
+                    getenv("GPUARRAY_B200_DEBUG") ? &listing : NULL);
+  if (listing != NULL) {
+    fprintf(stderr, "%s\n", listing);
+    free(listing);
+  }
+  free(src);
+  if (*err != GA_NO_ERROR) {
+    free(v);
+    return NULL;
+  }
+  v->next = ge->variants;
+  ge->variants = v;
+  return v;
+}
+
+/* Test hook: the source that would be compiled for a given variant, without
+ * touching a device. kind 0/1/2; modes packs 2 bits per array. Caller frees. */
+GPUARRAY_PUBLIC char *gpuarray_b200_elemwise_source(const char *preamble, const char *expr,
+                                                    unsigned int n, gpuelemwise_arg *args,
+                                                    int flags, int kind, int ept, int unroll,
+                                                    unsigned int nd, int idx32,
+                                                    unsigned long long modes, int tp, int tq) {
+  GpuElemwise ge;
+  ew_variant v;
+  unsigned int i;
+  memset(&ge, 0, sizeof(ge));
+  memset(&v, 0, sizeof(v));
+  ge.expr = (char *)expr;
+  ge.preamble = (char *)preamble;
+  ge.args = args;
+  ge.n = n;
+  ge.flags = flags;
+  for (i = 0; i < n; i++)
+    if (is_array(&args[i])) ge.narray++;
+  v.kind = kind;
+  v.ept = ept;
+  v.unroll = unroll;
+  v.nd = nd;
+  v.idx32 = idx32;
+  v.modes = modes;
+  v.tp = tp;
+  v.tq = tq;
+  return gen_source(&ge, &v);
+}
+
+/* ------------------------------------------------------------ construction */
+
+static int grow_scratch(GpuElemwise *ge, unsigned int nd) {
+  unsigned int i, cap = ge->nd_cap ? ge->nd_cap : 8;
+  size_t *d;
+  while (cap < nd) cap *= 2;
+  if (cap == ge->nd_cap) return 0;
+  d = realloc(ge->dims, cap * sizeof(size_t));
+  if (d == NULL) return -1;
+  ge->dims = d;
+  for (i = 0; i < ge->narray; i++) {
+    ssize_t *s = realloc(ge->strides[i], cap * sizeof(ssize_t));
+    if (s == NULL) return -1;
+    ge->strides[i] = s;
+  }
+  ge->nd_cap = cap;
+  return 0;
+}
+
+GpuElemwise *GpuElemwise_new(gpucontext *ctx, const char *preamble, const char *expr,
+                             unsigned int n, gpuelemwise_arg *args, unsigned int nd, int flags) {
+  GpuElemwise *ge;
+  unsigned int i;
+  int err = GA_NO_ERROR;
+
+  if (expr == NULL || (n > 0 && args == NULL)) {
+    ga_err_set(ctx->err, GA_VALUE_ERROR, "GpuElemwise_new: NULL expression or arguments");
+    return NULL;
+  }
+  ge = calloc(1, sizeof(*ge));
+  if (ge == NULL) {
+    ga_err_sys(ctx->err, "calloc");
+    return NULL;
+  }
+  ge->ctx = ctx;
+  ge->flags = flags;
+  ge->n = n;
+  ge->expr = strdup(expr);
+  if (preamble != NULL) ge->preamble = strdup(preamble);
+  ge->args = calloc(n ? n : 1, sizeof(gpuelemwise_arg));
+  if (ge->expr == NULL || (preamble != NULL && ge->preamble == NULL) || ge->args == NULL) {
+    ga_err_sys(ctx->err, "strdup");
+    goto fail;
+  }
+  ge->min_elsize = 16;
+  ge->max_elsize = 1;
+  for (i = 0; i < n; i++) {
+    size_t es = gpuarray_get_elsize(args[i].typecode);
+    if (args[i].name == NULL) {
+      ga_err_fmt(ctx->err, GA_VALUE_ERROR, "Argument %u has no name", i);
+      goto fail;
+    }
+    if (!ga_type_is_computable(args[i].typecode)) {
+      ga_err_fmt(ctx->err, GA_UNSUPPORTED_ERROR,
+                 "Argument %u (%s): type %d is not supported (complex and 16-byte integer types "
+                 "have no CUDA representation)", i, args[i].name, args[i].typecode);
+      goto fail;
+    }
+    ge->args[i].typecode = args[i].typecode;
+    ge->args[i].flags = args[i].flags;
+    ge->args[i].name = strdup(args[i].name);
+    if (ge->args[i].name == NULL) {
+      ga_err_sys(ctx->err, "strdup");
+      goto fail;
+    }
+    if (is_array(&args[i])) {
+      ge->narray++;
+      if (es < ge->min_elsize) ge->min_elsize = (unsigned)es;
+      if (es > ge->max_elsize) ge->max_elsize = (unsigned)es;
+    }
+  }
+  if (ge->narray > 30) {
+    ga_err_set(ctx->err, GA_UNSUPPORTED_ERROR, "More than 30 array arguments");
+    goto fail;
+  }
+  if (ge->narray == 0) ge->min_elsize = ge->max_elsize = 4;
+  /* 16 bytes for the narrowest argument, at most 64 for the widest */
+  ge->ept = (int)(16 / ge->min_elsize);
+  while (ge->ept > 1 && (unsigned)ge->ept * ge->max_elsize > 64) ge->ept /= 2;
+
+  ge->strides = calloc(ge->narray ? ge->narray : 1, sizeof(ssize_t *));
+  ge->params = calloc(n + 2, sizeof(void *));
+  if (ge->strides == NULL || ge->params == NULL || grow_scratch(ge, nd > 8 ? nd : 8) != 0) {
+    ga_err_sys(ctx->err, "calloc");
+    goto fail;
+  }
+
+  /* Build the vectorised contiguous kernel now: it validates the expression,
+   * so a bad one is reported here as in the reference (:672-688). */
+  {
+    ew_variant want;
+    unsigned cap;
+    memset(&want, 0, sizeof(want));
+    want.kind = 0;
+    want.ept = ge->ept;
+    ew_tuning(&want.unroll, &cap);
+    want.idx32 = 1;
+    if (get_variant(ge, &want, &err) == NULL) goto fail;
+  }
+  return ge;
+fail:
+  GpuElemwise_free(ge);
+  return NULL;
+}
+
+void GpuElemwise_free(GpuElemwise *ge) {
+  unsigned int i;
+  ew_variant *v, *nv;
+  if (ge == NULL) return;
+  for (v = ge->variants; v != NULL; v = nv) {
+    nv = v->next;
+    free(v);
+  }
+  if (ge->strides != NULL)
+    for (i = 0; i < ge->narray; i++) free(ge->strides[i]);
+  if (ge->args != NULL)
+    for (i = 0; i < ge->n; i++) free((void *)ge->args[i].name);
+  free(ge->strides);
+  free(ge->dims);
+  free(ge->args);
+  free(ge->params);
+  free(ge->blob);
+  free(ge->preamble);
+  free(ge->expr);
+  free(ge);
+}
+
+/* ------------------------------------------------------------------- calls */
+
+static CUdeviceptr array_base(const GpuArray *a) { return a->data->ptr + a->offset; }
+
+/* The contiguous fast path applies when every array has the same shape and
+ * they are all C- or all F-contiguous (reference check_contig). Returns 1 and
+ * the element count if so. */
+static int check_contig(const GpuElemwise *ge, void **args, size_t *n_out) {
+  const GpuArray *first = NULL, *v;
+  unsigned int i, j;
+  int c_ok = 1, f_ok = 1;
+  size_t n = 1;
+  for (i = 0; i < ge->n; i++) {
+    if (!is_array(&ge->args[i])) continue;
+    v = (const GpuArray *)args[i];
+    if (first == NULL) {
+      first = v;
+      for (j = 0; j < v->nd; j++) n *= v->dimensions[j];
+    } else {
+      if (v->nd != first->nd) return 0;
+      for (j = 0; j < v->nd; j++)
+        if (v->dimensions[j] != first->dimensions[j]) return 0;
+    }
+    c_ok &= GpuArray_IS_C_CONTIGUOUS(v) != 0;
+    f_ok &= GpuArray_IS_F_CONTIGUOUS(v) != 0;
+  }
+  if (first == NULL || !(c_ok || f_ok)) return 0;
+  *n_out = n;
+  return 1;
+}
+
+static int call_contig(GpuElemwise *ge, void **args, size_t n) {
+  gpucontext *ctx = ge->ctx;
+  ew_variant want, *v;
+  CUdeviceptr ptrs[32];
+  unsigned int i, k = 0, p = 0, capsm;
+  unsigned grid[3] = {1, 1, 1}, block[3] = {GA_EW_THREADS, 1, 1};
+  int err = GA_NO_ERROR, aligned = 1;
+  size_t nvec, per_block, blocks;
+
+  memset(&want, 0, sizeof(want));
+  want.kind = 0;
+  ew_tuning(&want.unroll, &capsm);
+  for (i = 0; i < ge->n; i++) {
+    if (!is_array(&ge->args[i])) continue;
+    ptrs[k] = array_base((const GpuArray *)args[i]);
+    if (ptrs[k] % 16 != 0) aligned = 0;
+    k++;
+  }
+  want.ept = aligned ? ge->ept : 1;
+  want.idx32 = n < ((size_t)1 << 31);
+  v = get_variant(ge, &want, &err);
+  if (v == NULL) return err;
+
+  ge->params[p++] = &n;
+  for (i = 0, k = 0; i < ge->n; i++)
+    if (is_array(&ge->args[i])) ge->params[p++] = &ptrs[k++];
+  for (i = 0; i < ge->n; i++)
+    if (!is_array(&ge->args[i])) ge->params[p++] = args[i];
+
+  nvec = n / (size_t)v->ept;
+  per_block = (size_t)GA_EW_THREADS * (size_t)v->unroll;
+  blocks = (nvec + per_block - 1) / per_block;
+  if (blocks == 0) blocks = 1;
+  if (capsm != 0 && blocks > (size_t)capsm * ctx->num_sms) blocks = (size_t)capsm * ctx->num_sms;
+  if (blocks > 0x7fffffffu) blocks = 0x7fffffffu;
+  grid[0] = (unsigned)blocks;
+  return ga_launch(ctx, &v->fn, grid, block, 0, ge->params);
+}
+
+static void make_div32(unsigned int d, unsigned int out[4]) {
+  unsigned int l = 0;
+  unsigned long long m;
+  while (l < 32 && ((unsigned long long)1 << l) < d) l++;
+  m = ((((unsigned long long)1 << l) - d) << 32) / d + 1;
+  out[0] = d;
+  out[1] = (unsigned int)m;
+  out[2] = l < 1 ? l : 1;
+  out[3] = l > 0 ? l - 1 : 0;
+}
+
+/* Shape agreement, broadcasting and collapsing (reference check_basic). On
+ * success ge->dims / ge->strides hold the collapsed problem. */
+static int check_basic(GpuElemwise *ge, void **args, int flags, size_t *n_out,
+                       unsigned int *nd_out) {
+  gpucontext *ctx = ge->ctx;
+  const GpuArray *shape_src = NULL, *v;
+  unsigned int i, j, p, nd = 0, seen = 0;
+  size_t n = 1;
+
+  for (i = 0; i < ge->n; i++) {
+    if (!is_array(&ge->args[i])) continue;
+    v = (const GpuArray *)args[i];
+    if (seen == 0) nd = v->nd;
+    else if (v->nd != nd) {
+      if (ISCLR(flags, GE_PADSHAPE))
+        return ga_err_fmt(ctx->err, GA_VALUE_ERROR, "Arg %u has differing nd = %u", i, v->nd);
+      if (v->nd > nd) nd = v->nd;
+    }
+    seen++;
+    if (shape_src == NULL && is_output(&ge->args[i])) shape_src = v;
+  }
+  if (shape_src == NULL) return ga_err_set(ctx->err, GA_VALUE_ERROR, "No output arrays");
+  if (nd > ge->nd_cap && grow_scratch(ge, nd) != 0) return ga_err_sys(ctx->err, "realloc");
+  if (shape_src->nd != nd) {
+    /* an output of lower rank would have to broadcast */
+    return ga_err_fmt(ctx->err, GA_VALUE_ERROR,
+                      "Output has nd = %u but the operation has nd = %u", shape_src->nd, nd);
+  }
+  memcpy(ge->dims, shape_src->dimensions, nd * sizeof(size_t));
+
+  for (i = 0, p = 0; i < ge->n; i++) {
+    unsigned int pad;
+    if (!is_array(&ge->args[i])) continue;
+    v = (const GpuArray *)args[i];
+    pad = nd - v->nd;
+    for (j = 0; j < nd; j++) {
+      size_t vd = j < pad ? 1 : v->dimensions[j - pad];
+      ssize_t vs = j < pad ? 0 : v->strides[j - pad];
+      if (vd != ge->dims[j] &&
+          (ISCLR(flags, GE_BROADCAST) || is_output(&ge->args[i]) || vd != 1))
+        return ga_err_fmt(ctx->err, GA_VALUE_ERROR,
+                          "Mismatched dimension %u for input %u (expected %zu got %zu)", j, i,
+                          ge->dims[j], vd);
+      ge->strides[p][j] = vd == 1 ? 0 : vs;
+    }
+    p++;
+  }
+  for (j = 0; j < nd; j++) n *= ge->dims[j];
+  if (nd > 1) gpuarray_elemwise_collapse(ge->narray, &nd, ge->dims, ge->strides);
+  *n_out = n;
+  *nd_out = nd;
+  return GA_NO_ERROR;
+}
+
+static int ensure_blob(GpuElemwise *ge, size_t words) {
+  if (words > ge->blob_words) {
+    unsigned long long *b = realloc(ge->blob, words * sizeof(*b));
+    if (b == NULL) return -1;
+    ge->blob = b;
+    ge->blob_words = words;
+  }
+  return 0;
+}
+
+static int call_transpose(GpuElemwise *ge, void **args, size_t n, unsigned int nd, int *handled);
+
+static int call_strided(GpuElemwise *ge, void **args, size_t n, unsigned int nd) {
+  gpucontext *ctx = ge->ctx;
+  ew_variant want, *v;
+  CUdeviceptr ptrs[32];
+  unsigned int i, j, k, p = 0, nout, capsm;
+  unsigned grid[3] = {1, 1, 1}, block[3] = {GA_EW_THREADS, 1, 1};
+  int err = GA_NO_ERROR, handled = 0;
+  size_t inner, cpr, rows, nchunks, words, blocks;
+  unsigned long long *w;
+
+  if (nd == 0) return ga_err_set(ctx->err, GA_VALUE_ERROR, "nd == 0");
+  if (nd > GA_EW_MAX_ND)
+    return ga_err_fmt(ctx->err, GA_UNSUPPORTED_ERROR,
+                      "%u dimensions remain after collapsing; at most %d are supported", nd,
+                      GA_EW_MAX_ND);
+
+  err = call_transpose(ge, args, n, nd, &handled);
+  if (handled) return err;
+
+  memset(&want, 0, sizeof(want));
+  want.kind = 1;
+  want.nd = nd;
+  want.ept = ge->ept;
+  want.unroll = 1;
+  ew_tuning(&want.unroll, &capsm);
+  want.unroll = 1;
+  inner = ge->dims[nd - 1];
+  cpr = (inner + (size_t)want.ept - 1) / (size_t)want.ept;
+  rows = n / inner;
+  nchunks = rows * cpr;
+  want.idx32 = n < ((size_t)1 << 31) && nchunks < ((size_t)1 << 31);
+
+  for (i = 0, k = 0; i < ge->n; i++) {
+    const gpuelemwise_arg *a = &ge->args[i];
+    size_t es, vb;
+    ssize_t is;
+    unsigned long long mode = 0;
+    if (!is_array(a)) continue;
+    ptrs[k] = array_base((const GpuArray *)args[i]);
+    es = gpuarray_get_elsize(a->typecode);
+    vb = es * (size_t)want.ept;
+    if (vb > 16) vb = 16;
+    is = ge->strides[k][nd - 1];
+    if (is == 0 && !is_output(a)) mode = 2;
+    else if (is == (ssize_t)es && inner % (size_t)want.ept == 0 && ptrs[k] % vb == 0) {
+      mode = 1;
+      for (j = 0; j + 1 < nd; j++)
+        if (ge->strides[k][j] % (ssize_t)vb != 0) mode = 0;
+    }
+    want.modes |= mode << (2 * k);
+    k++;
+  }
+  v = get_variant(ge, &want, &err);
+  if (v == NULL) return err;
+
+  /* parameter block: see struct ga__ew_layout in ga_ew_strided.cuh */
+  nout = nd > 1 ? nd - 1 : 1;
+  words = 3 + nout + 2 + 2 * nout + (size_t)(ge->narray ? ge->narray : 1) * nd;
+  if (ensure_blob(ge, words) != 0) return ga_err_sys(ctx->err, "realloc");
+  w = ge->blob;
+  memset(w, 0, words * sizeof(*w));
+  w[0] = nchunks;
+  w[1] = inner;
+  w[2] = cpr;
+  for (j = 0; j + 1 < nd; j++) w[3 + j] = ge->dims[j];
+  if (want.idx32) {
+    make_div32((unsigned)cpr, (unsigned int *)&w[3 + nout]);
+    for (j = 0; j + 1 < nd; j++)
+      make_div32((unsigned)ge->dims[j], (unsigned int *)&w[3 + nout + 2 + 2 * j]);
+  }
+  for (k = 0; k < ge->narray; k++)
+    for (j = 0; j < nd; j++)
+      w[3 + nout + 2 + 2 * nout + (size_t)k * nd + j] = (unsigned long long)(long long)ge->strides[k][j];
+
+  ge->params[p++] = w;
+  for (i = 0, k = 0; i < ge->n; i++)
+    if (is_array(&ge->args[i])) ge->params[p++] = &ptrs[k++];
+  for (i = 0; i < ge->n; i++)
+    if (!is_array(&ge->args[i])) ge->params[p++] = args[i];
+
+  blocks = (nchunks + GA_EW_THREADS - 1) / GA_EW_THREADS;
+  if (blocks == 0) blocks = 1;
+  if (capsm != 0 && blocks > (size_t)capsm * ctx->num_sms) blocks = (size_t)capsm * ctx->num_sms;
+  if (blocks > 0x7fffffffu) blocks = 0x7fffffffu;
+  grid[0] = (unsigned)blocks;
+  return ga_launch(ctx, &v->fn, grid, block, 0, ge->params);
+}
+
+/* Placeholder until the tiled-transpose template is wired in. */
+static int call_transpose(GpuElemwise *ge, void **args, size_t n, unsigned int nd, int *handled) {
+  (void)ge; (void)args; (void)n; (void)nd;
+  *handled = 0;
+  return GA_NO_ERROR;
+}
+
+int GpuElemwise_call(GpuElemwise *ge, void **args, int flags) {
+  gpucontext *ctx = ge->ctx;
+  size_t n = 0;
+  unsigned int nd = 0, i;
+  int err;
+
+  for (i = 0; i < ge->n; i++) {
+    if (args[i] == NULL) return ga_err_fmt(ctx->err, GA_VALUE_ERROR, "Argument %u is NULL", i);
+    if (is_array(&ge->args[i])) {
+      const GpuArray *a = (const GpuArray *)args[i];
+      if (a->typecode != ge->args[i].typecode)
+        return ga_err_fmt(ctx->err, GA_VALUE_ERROR,
+                          "Argument %u (%s) has type %d but the operation was built for %d", i,
+                          ge->args[i].name, a->typecode, ge->args[i].typecode);
+      if (GpuArray_context(a) != ctx)
+        return ga_err_fmt(ctx->err, GA_VALUE_ERROR, "Argument %u belongs to another context", i);
+      if (!GpuArray_ISALIGNED(a))
+        return ga_err_fmt(ctx->err, GA_UNALIGNED_ERROR, "Argument %u is not aligned", i);
+      if (is_output(&ge->args[i]) && !GpuArray_ISWRITEABLE(a))
+        return ga_err_fmt(ctx->err, GA_VALUE_ERROR, "Output argument %u is not writeable", i);
+    }
+  }
+  if (check_contig(ge, args, &n)) {
+    if (n == 0) return GA_NO_ERROR;
+    return call_contig(ge, args, n);
+  }
+  err = check_basic(ge, args, flags, &n, &nd);
+  if (err != GA_NO_ERROR) return err;
+  if (n == 0) return GA_NO_ERROR;
+  return call_strided(ge, args, n, nd);
+}

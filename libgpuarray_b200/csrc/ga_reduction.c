@@ -1,0 +1,642 @@
+/* Reduction engine: GpuReduction_new / _call / _free and GpuArray_maxandargmax.
+ *
+ * Host side of what the reference does in src/gpuarray_reduction.c (argument
+ * checks :198-261, axis bookkeeping :268-295 and :616-626, launch-shape search
+ * :673-776, five device allocations per call :782-834) and, for sum / prod /
+ * all / any, in pygpu/reduction.py:137-319. Differences:
+ *   - the axes are first normalised: size-1 axes vanish, kept axes and reduced
+ *     axes are collapsed separately (a kept pair merges only if source and both
+ *     destinations agree; a reduced pair only if memory order and flat-index
+ *     weight agree), and reduced axes are traversed in MEMORY order while every
+ *     element carries its flat index in reduxList order, so any axis list gets
+ *     coalesced traffic and the reference's index/tie semantics;
+ *   - one of three fixed kernel shapes (templates/ga_reduce.cuh) is picked from
+ *     the normalised strides instead of solving for a launch factorisation;
+ *   - shapes, strides and weights travel in one kernel parameter block: no
+ *     allocation or host-to-device copy per call. The only device scratch is
+ *     the partial buffer of two-pass reductions, kept by the operator object.
+ */
+#include "private.h"
+
+#define RD_MAXD 8
+#define RD_THREADS 256
+#define RD_BY 8
+
+enum { SHAPE_ROWS = 0, SHAPE_COLS = 1, SHAPE_GENERAL = 2 };
+
+typedef struct rd_variant {
+  int shape, vec, idx64, tpo, stage2, dst_tc, write_val, write_idx;
+  ga_function fn;
+  struct rd_variant *next;
+} rd_variant;
+
+struct _GpuReduction {
+  gpucontext *ctx;
+  ga_reduce_op op;
+  int src_tc;
+  int kind;              /* 0 accumulate, 1 (value, index) pairs */
+  rd_variant *variants;
+  gpudata *scratch;      /* partials of two-pass reductions */
+  size_t scratch_sz;
+};
+
+/* Normalised problem; field order matches struct ga__rd_layout. */
+typedef struct rd_layout {
+  unsigned long long nf_total, nr_total, nf, nr;
+  unsigned long long fdim[RD_MAXD];
+  long long fsrc[RD_MAXD], fdst0[RD_MAXD], fdst1[RD_MAXD];
+  unsigned long long rdim[RD_MAXD];
+  long long rsrc[RD_MAXD];
+  unsigned long long rmul[RD_MAXD];
+  unsigned long long splits, inner, seg, nseg, units, tiles;
+} rd_layout;
+
+static int op_is_pair(ga_reduce_op op) {
+  return op == GA_REDUCE_MIN || op == GA_REDUCE_MAX || op == GA_REDUCE_ARGMIN ||
+         op == GA_REDUCE_ARGMAX || op == GA_REDUCE_MINANDARGMIN || op == GA_REDUCE_MAXANDARGMAX;
+}
+static int op_is_min(ga_reduce_op op) {
+  return op == GA_REDUCE_MIN || op == GA_REDUCE_ARGMIN || op == GA_REDUCE_MINANDARGMIN;
+}
+static int op_writes_val(ga_reduce_op op) {
+  return op != GA_REDUCE_ARGMIN && op != GA_REDUCE_ARGMAX;
+}
+static int op_writes_idx(ga_reduce_op op) {
+  return op == GA_REDUCE_ARGMIN || op == GA_REDUCE_ARGMAX || op == GA_REDUCE_MINANDARGMIN ||
+         op == GA_REDUCE_MAXANDARGMAX;
+}
+static int tc_is_float(int tc) { return tc == GA_FLOAT || tc == GA_DOUBLE || tc == GA_HALF; }
+static int tc_is_unsigned(int tc) {
+  return tc == GA_BOOL || tc == GA_UBYTE || tc == GA_USHORT || tc == GA_UINT || tc == GA_ULONG ||
+         tc == GA_SIZE;
+}
+static int tc_is_index(int tc) {
+  return tc == GA_LONG || tc == GA_ULONG || tc == GA_SIZE || tc == GA_SSIZE;
+}
+
+/* ---------------------------------------------------------------- codegen */
+
+static const char *extreme_literal(int tc, int lowest) {
+  if (tc_is_float(tc)) return lowest ? "(-INFINITY)" : "INFINITY";
+  if (tc_is_unsigned(tc)) {
+    if (lowest) return "0";
+    switch (gpuarray_get_elsize(tc)) {
+    case 1: return "255";
+    case 2: return "65535";
+    case 4: return "4294967295U";
+    default: return "18446744073709551615ULL";
+    }
+  }
+  switch (gpuarray_get_elsize(tc)) {
+  case 1: return lowest ? "(-128)" : "127";
+  case 2: return lowest ? "(-32768)" : "32767";
+  case 4: return lowest ? "(-2147483647 - 1)" : "2147483647";
+  default: return lowest ? "(-9223372036854775807LL - 1)" : "9223372036854775807LL";
+  }
+}
+
+static char *gen_source(const GpuReduction *gr, const rd_variant *v) {
+  ga_strb sb;
+  const char *src_t = ga_ctype(gr->src_tc);
+  const char *x_t = gr->src_tc == GA_HALF ? "float" : src_t;
+  const char *acc_t, *dst_t = ga_ctype(v->dst_tc);
+  const char *map = "((GA_RD_ACC_T)(x))", *combine = "((a) + (b))", *ident = "0";
+
+  ga_strb_init(&sb);
+  if (gr->kind == 1) acc_t = x_t;
+  else if (gr->op == GA_REDUCE_ALL || gr->op == GA_REDUCE_ANY) acc_t = "ga_ubyte";
+  else acc_t = v->dst_tc == GA_HALF ? "float" : dst_t;
+
+  switch (gr->op) {
+  case GA_REDUCE_SUM: break;
+  case GA_REDUCE_PROD: combine = "((a) * (b))"; ident = "1"; break;
+  case GA_REDUCE_PRODNZ:
+    map = "((x) == 0 ? (GA_RD_ACC_T)1 : (GA_RD_ACC_T)(x))";
+    combine = "((a) * (b))";
+    ident = "1";
+    break;
+  case GA_REDUCE_AND: combine = "((a) & (b))"; ident = "(~(GA_RD_ACC_T)0)"; break;
+  case GA_REDUCE_OR: combine = "((a) | (b))"; break;
+  case GA_REDUCE_XOR: combine = "((a) ^ (b))"; break;
+  case GA_REDUCE_ALL: map = "((x) != 0)"; combine = "((a) && (b))"; ident = "1"; break;
+  case GA_REDUCE_ANY: map = "((x) != 0)"; combine = "((a) || (b))"; break;
+  default: ident = extreme_literal(gr->src_tc, !op_is_min(gr->op)); break;
+  }
+  ga_strb_puts(&sb, "#include \"cluda.h\"\n");
+  ga_strb_printf(&sb, "#define GA_RD_SRC_T %s\n#define GA_RD_X_T %s\n#define GA_RD_ACC_T %s\n"
+                      "#define GA_RD_DST_T %s\n", src_t, x_t, acc_t, dst_t);
+  ga_strb_printf(&sb, "#define GA_RD_LOAD(raw) %s\n",
+                 gr->src_tc == GA_HALF ? "ga_half2float(raw)" : "(raw)");
+  ga_strb_printf(&sb, "#define GA_RD_STORE(a) %s\n",
+                 v->dst_tc == GA_HALF ? "ga_float2half((float)(a))" : "((GA_RD_DST_T)(a))");
+  ga_strb_printf(&sb, "#define GA_RD_MAP(x) %s\n#define GA_RD_COMBINE(a, b) %s\n"
+                      "#define GA_RD_IDENT %s\n#define GA_RD_BETTER(b, a) %s\n",
+                 map, combine, ident, op_is_min(gr->op) ? "((b) < (a))" : "((b) > (a))");
+  ga_strb_printf(&sb, "#define GA_RD_KIND %d\n#define GA_RD_ISFLOAT %d\n#define GA_RD_WRITE_VAL %d\n"
+                      "#define GA_RD_WRITE_IDX %d\n#define GA_RD_IDX_T %s\n#define GA_RD_VEC %d\n"
+                      "#define GA_RD_THREADS %d\n#define GA_RD_TPO %d\n#define GA_RD_STAGE2 %d\n"
+                      "#define GA_RD_BY %d\n#define %s\n#include \"ga_reduce.cuh\"\n",
+                 gr->kind, tc_is_float(gr->src_tc), v->write_val, v->write_idx,
+                 v->idx64 ? "unsigned long long" : "unsigned int", v->vec, RD_THREADS, v->tpo,
+                 v->stage2, RD_BY,
+                 v->shape == SHAPE_ROWS   ? "GA_RD_BUILD_ROWS"
+                 : v->shape == SHAPE_COLS ? "GA_RD_BUILD_COLS"
+                                          : "GA_RD_BUILD_GENERAL");
+  if (sb.failed) {
+    ga_strb_free(&sb);
+    return NULL;
+  }
+  return sb.s;
+}
+
+static const char *const shape_entry[] = {"ga_rd_rows", "ga_rd_cols", "ga_rd_general"};
+
+static rd_variant *get_variant(GpuReduction *gr, const rd_variant *want, int *err) {
+  rd_variant *v;
+  char *src, *listing = NULL;
+  for (v = gr->variants; v != NULL; v = v->next)
+    if (v->shape == want->shape && v->vec == want->vec && v->idx64 == want->idx64 &&
+        v->tpo == want->tpo && v->stage2 == want->stage2 && v->dst_tc == want->dst_tc &&
+        v->write_val == want->write_val && v->write_idx == want->write_idx)
+      return v;
+  v = malloc(sizeof(*v));
+  if (v == NULL) {
+    *err = ga_err_sys(gr->ctx->err, "malloc");
+    return NULL;
+  }
+  *v = *want;
+  src = gen_source(gr, v);
+  if (src == NULL) {
+    free(v);
+    *err = ga_err_set(gr->ctx->err, GA_MISC_ERROR, "Formatting error creating kernel source");
+    return NULL;
+  }
+  *err = ga_compile(gr->ctx, src, shape_entry[v->shape], NULL, &v->fn,
+                    getenv("GPUARRAY_B200_DEBUG") ? &listing : NULL);
+  if (listing != NULL) {
+    fprintf(stderr, "%s\n", listing);
+    free(listing);
+  }
+  free(src);
+  if (*err != GA_NO_ERROR) {
+    free(v);
+    return NULL;
+  }
+  v->next = gr->variants;
+  gr->variants = v;
+  return v;
+}
+
+/* Test hook: source of one reduction kernel variant; caller frees. */
+GPUARRAY_PUBLIC char *gpuarray_b200_reduction_source(int op, int src_tc, int dst_tc, int shape,
+                                                     int vec, int idx64, int tpo, int stage2) {
+  GpuReduction gr;
+  rd_variant v;
+  memset(&gr, 0, sizeof(gr));
+  memset(&v, 0, sizeof(v));
+  gr.op = (ga_reduce_op)op;
+  gr.src_tc = src_tc;
+  gr.kind = op_is_pair(gr.op);
+  v.shape = shape;
+  v.vec = vec;
+  v.idx64 = idx64;
+  v.tpo = tpo;
+  v.stage2 = stage2;
+  v.dst_tc = dst_tc;
+  v.write_val = op_writes_val(gr.op);
+  v.write_idx = op_writes_idx(gr.op);
+  return gen_source(&gr, &v);
+}
+
+/* ------------------------------------------------------------ construction */
+
+int GpuReduction_new(GpuReduction **out, gpucontext *ctx, ga_reduce_op op, unsigned ndf,
+                     unsigned ndr, int s0TypeCode, int flags) {
+  GpuReduction *gr;
+  (void)ndf; (void)ndr; (void)flags;
+  if (out == NULL) return ga_err_set(ctx->err, GA_INVALID_ERROR, "GpuReduction_new: NULL result");
+  *out = NULL;
+  if ((int)op < 0 || op >= GA_REDUCE_ENDSUPPORTED)
+    return ga_err_fmt(ctx->err, GA_INVALID_ERROR, "Unknown reduction operator %d", (int)op);
+  if (!ga_type_is_computable(s0TypeCode) || s0TypeCode == GA_SIZE || s0TypeCode == GA_SSIZE)
+    return ga_err_fmt(ctx->err, GA_UNSUPPORTED_ERROR, "Unsupported source type %d", s0TypeCode);
+  if ((op == GA_REDUCE_AND || op == GA_REDUCE_OR || op == GA_REDUCE_XOR) &&
+      tc_is_float(s0TypeCode))
+    return ga_err_set(ctx->err, GA_UNSUPPORTED_ERROR,
+                      "Bitwise reductions need an integer or bool source");
+  gr = calloc(1, sizeof(*gr));
+  if (gr == NULL) return ga_err_sys(ctx->err, "calloc");
+  gr->ctx = ctx;
+  gr->op = op;
+  gr->src_tc = s0TypeCode;
+  gr->kind = op_is_pair(op);
+  ctx->refcnt++;
+  *out = gr;
+  return GA_NO_ERROR;
+}
+
+void GpuReduction_free(GpuReduction *gr) {
+  rd_variant *v, *nv;
+  gpucontext *ctx;
+  if (gr == NULL) return;
+  ctx = gr->ctx;
+  for (v = gr->variants; v != NULL; v = nv) {
+    nv = v->next;
+    free(v);
+  }
+  if (gr->scratch != NULL) gpudata_release(gr->scratch);
+  free(gr);
+  ga_ctx_unref(ctx);
+}
+
+/* ------------------------------------------------------------ normalisation */
+
+static int check_dst(gpucontext *ctx, const GpuArray *d, const GpuArray *s, const unsigned char *red,
+                     unsigned ndd, const char *what) {
+  unsigned i, k = 0;
+  if (d->nd != ndd)
+    return ga_err_fmt(ctx->err, GA_VALUE_ERROR, "%s has %u dimensions, expected %u", what, d->nd,
+                      ndd);
+  for (i = 0; i < s->nd; i++) {
+    if (red[i]) continue;
+    if (d->dimensions[k] != s->dimensions[i])
+      return ga_err_fmt(ctx->err, GA_VALUE_ERROR,
+                        "%s dimension %u is %zu but source axis %u has %zu", what, k,
+                        d->dimensions[k], i, s->dimensions[i]);
+    k++;
+  }
+  if (GpuArray_context(d) != ctx)
+    return ga_err_fmt(ctx->err, GA_VALUE_ERROR, "%s belongs to another context", what);
+  if (!GpuArray_ISWRITEABLE(d))
+    return ga_err_fmt(ctx->err, GA_VALUE_ERROR, "%s is not writeable", what);
+  if (!GpuArray_ISALIGNED(d))
+    return ga_err_fmt(ctx->err, GA_UNALIGNED_ERROR, "%s is not aligned", what);
+  return GA_NO_ERROR;
+}
+
+static long long ll_abs(long long v) { return v < 0 ? -v : v; }
+
+/* Fills nf/nr, dims, strides, weights and totals of `L`. */
+static int normalise(const GpuReduction *gr, rd_layout *L, const GpuArray *d0, const GpuArray *d1,
+                     const GpuArray *s, const unsigned char *red, unsigned reduxLen,
+                     const int *reduxList) {
+  gpucontext *ctx = gr->ctx;
+  unsigned i, k, n;
+  unsigned long long mul;
+
+  memset(L, 0, sizeof(*L));
+  L->nf_total = 1;
+  L->nr_total = 1;
+
+  /* kept axes, ascending; destination axis k pairs with the k-th kept axis */
+  for (i = 0, k = 0, n = 0; i < s->nd; i++) {
+    long long s0, sd0, sd1;
+    if (red[i]) continue;
+    L->nf_total *= s->dimensions[i];
+    s0 = s->strides[i];
+    sd0 = d0 != NULL ? d0->strides[k] : 0;
+    sd1 = d1 != NULL ? d1->strides[k] : 0;
+    k++;
+    if (s->dimensions[i] == 1) continue;
+    if (n > 0 && L->fsrc[n - 1] == (long long)s->dimensions[i] * s0 &&
+        L->fdst0[n - 1] == (long long)s->dimensions[i] * sd0 &&
+        L->fdst1[n - 1] == (long long)s->dimensions[i] * sd1) {
+      L->fdim[n - 1] *= s->dimensions[i];
+      L->fsrc[n - 1] = s0;
+      L->fdst0[n - 1] = sd0;
+      L->fdst1[n - 1] = sd1;
+      continue;
+    }
+    if (n == RD_MAXD)
+      return ga_err_fmt(ctx->err, GA_UNSUPPORTED_ERROR,
+                        "More than %d kept dimensions remain after collapsing", RD_MAXD);
+    L->fdim[n] = s->dimensions[i];
+    L->fsrc[n] = s0;
+    L->fdst0[n] = sd0;
+    L->fdst1[n] = sd1;
+    n++;
+  }
+  L->nf = n;
+
+  /* reduced axes with their weight in the flat index (last listed fastest) */
+  {
+    unsigned long long dim[64], w[64];
+    long long str[64];
+    unsigned m = 0;
+    mul = 1;
+    for (i = reduxLen; i > 0; i--) {
+      unsigned ax = (unsigned)reduxList[i - 1];
+      size_t dsz = s->dimensions[ax];
+      L->nr_total *= dsz;
+      if (dsz != 1) {
+        if (m == 64)
+          return ga_err_set(ctx->err, GA_UNSUPPORTED_ERROR, "More than 64 reduced axes");
+        dim[m] = dsz;
+        str[m] = s->strides[ax];
+        w[m] = gr->kind == 1 ? mul : 0;
+        m++;
+      }
+      mul *= dsz;
+    }
+    /* traversal order = memory order: largest |stride| outermost (stable insertion sort) */
+    for (i = 1; i < m; i++) {
+      unsigned long long td = dim[i], tw = w[i];
+      long long ts = str[i];
+      unsigned j = i;
+      while (j > 0 && ll_abs(str[j - 1]) < ll_abs(ts)) {
+        dim[j] = dim[j - 1];
+        str[j] = str[j - 1];
+        w[j] = w[j - 1];
+        j--;
+      }
+      dim[j] = td;
+      str[j] = ts;
+      w[j] = tw;
+    }
+    for (i = 0, n = 0; i < m; i++) {
+      if (n > 0 && L->rsrc[n - 1] == (long long)dim[i] * str[i] &&
+          L->rmul[n - 1] == dim[i] * w[i]) {
+        L->rdim[n - 1] *= dim[i];
+        L->rsrc[n - 1] = str[i];
+        L->rmul[n - 1] = w[i];
+        continue;
+      }
+      if (n == RD_MAXD)
+        return ga_err_fmt(ctx->err, GA_UNSUPPORTED_ERROR,
+                          "More than %d reduced dimensions remain after collapsing", RD_MAXD);
+      L->rdim[n] = dim[i];
+      L->rsrc[n] = str[i];
+      L->rmul[n] = w[i];
+      n++;
+    }
+    L->nr = n;
+  }
+  return GA_NO_ERROR;
+}
+
+/* -------------------------------------------------------------------- call */
+
+static int ensure_scratch(GpuReduction *gr, size_t bytes) {
+  int err = GA_NO_ERROR;
+  if (bytes <= gr->scratch_sz) return GA_NO_ERROR;
+  if (gr->scratch != NULL) gpudata_release(gr->scratch);
+  gr->scratch_sz = 0;
+  gr->scratch = gpudata_alloc(gr->ctx, bytes, NULL, 0, &err);
+  if (gr->scratch == NULL) return err;
+  gr->scratch_sz = bytes;
+  return GA_NO_ERROR;
+}
+
+static int all_multiple(const long long *v, unsigned n, long long m) {
+  unsigned i;
+  for (i = 0; i < n; i++)
+    if (v[i] % m != 0) return 0;
+  return 1;
+}
+
+/* Tuning for experiments: GPUARRAY_B200_RD="ctas_per_sm,seg_vectors". */
+static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs) {
+  static int parsed = 0;
+  static unsigned t_ctas = 32, t_seg = 8;
+  if (!parsed) {
+    const char *env = getenv("GPUARRAY_B200_RD");
+    if (env != NULL) sscanf(env, "%u,%u", &t_ctas, &t_seg);
+    if (t_ctas == 0) t_ctas = 32;
+    if (t_seg == 0) t_seg = 8;
+    parsed = 1;
+  }
+  *ctas_per_sm = t_ctas;
+  *seg_vecs = t_seg;
+}
+
+int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const GpuArray *s0,
+                      unsigned reduxLen, const int *reduxList, int flags) {
+  GpuReduction *gr = (GpuReduction *)cgr;
+  gpucontext *ctx;
+  unsigned char red[64];
+  rd_layout L;
+  rd_variant want, *v1, *v2 = NULL;
+  unsigned i, ndd, ctas_per_sm, seg_vecs;
+  unsigned grid[3] = {1, 1, 1}, block[3] = {RD_THREADS, 1, 1};
+  size_t elsize, target;
+  int err = GA_NO_ERROR, need_val, need_idx;
+  CUdeviceptr p_src, p_d0 = 0, p_d1 = 0, p_val = 0, p_idx = 0;
+  void *params[6];
+  (void)flags;
+
+  if (gr == NULL) return GA_INVALID_ERROR;
+  ctx = gr->ctx;
+  if (s0 == NULL) return ga_err_set(ctx->err, GA_INVALID_ERROR, "Source array is NULL");
+  if (s0->nd == 0 || s0->nd > 64 || reduxLen == 0 || reduxLen > s0->nd || reduxList == NULL)
+    return ga_err_set(ctx->err, GA_INVALID_ERROR, "Invalid rank or reduction axis count");
+  if (s0->typecode != gr->src_tc)
+    return ga_err_fmt(ctx->err, GA_VALUE_ERROR,
+                      "Source has type %d but the operator was built for %d", s0->typecode,
+                      gr->src_tc);
+  if (GpuArray_context(s0) != ctx)
+    return ga_err_set(ctx->err, GA_VALUE_ERROR, "Source belongs to another context");
+  if (!GpuArray_ISALIGNED(s0)) return ga_err_set(ctx->err, GA_UNALIGNED_ERROR, "Source is not aligned");
+  memset(red, 0, sizeof(red));
+  for (i = 0; i < reduxLen; i++) {
+    if (reduxList[i] < 0 || (unsigned)reduxList[i] >= s0->nd)
+      return ga_err_fmt(ctx->err, GA_INVALID_ERROR, "Reduction axis %d out of range", reduxList[i]);
+    if (red[reduxList[i]])
+      return ga_err_fmt(ctx->err, GA_INVALID_ERROR, "Reduction axis %d listed twice", reduxList[i]);
+    red[reduxList[i]] = 1;
+  }
+  ndd = s0->nd - reduxLen;
+  need_val = op_writes_val(gr->op);
+  need_idx = op_writes_idx(gr->op);
+  if (need_val && d0 == NULL)
+    return ga_err_set(ctx->err, GA_INVALID_ERROR, "Value destination is NULL");
+  if (need_idx && d1 == NULL)
+    return ga_err_set(ctx->err, GA_INVALID_ERROR, "Index destination is NULL");
+  if (!need_val) d0 = NULL;
+  if (!need_idx) d1 = NULL;
+  if (d0 != NULL) {
+    err = check_dst(ctx, d0, s0, red, ndd, "Value destination");
+    if (err != GA_NO_ERROR) return err;
+    if (gr->kind == 1 && d0->typecode != s0->typecode)
+      return ga_err_set(ctx->err, GA_VALUE_ERROR,
+                        "min/max destination must have the source's type");
+    if (!ga_type_is_computable(d0->typecode) || d0->typecode == GA_SIZE || d0->typecode == GA_SSIZE)
+      return ga_err_fmt(ctx->err, GA_UNSUPPORTED_ERROR, "Unsupported destination type %d",
+                        d0->typecode);
+    if ((gr->op == GA_REDUCE_AND || gr->op == GA_REDUCE_OR || gr->op == GA_REDUCE_XOR) &&
+        tc_is_float(d0->typecode))
+      return ga_err_set(ctx->err, GA_VALUE_ERROR, "Bitwise reductions need an integer destination");
+  }
+  if (d1 != NULL) {
+    err = check_dst(ctx, d1, s0, red, ndd, "Index destination");
+    if (err != GA_NO_ERROR) return err;
+    if (!tc_is_index(d1->typecode))
+      return ga_err_set(ctx->err, GA_VALUE_ERROR, "Index destination must hold 8-byte integers");
+  }
+
+  err = normalise(gr, &L, d0, d1, s0, red, reduxLen, reduxList);
+  if (err != GA_NO_ERROR) return err;
+  if (L.nf_total == 0) return GA_NO_ERROR;
+  if (L.nr_total == 0 && gr->kind == 1)
+    return ga_err_set(ctx->err, GA_VALUE_ERROR, "min/max over zero elements");
+
+  elsize = gpuarray_get_elsize(gr->src_tc);
+  p_src = s0->data->ptr + s0->offset;
+  if (d0 != NULL) p_d0 = d0->data->ptr + d0->offset;
+  if (d1 != NULL) p_d1 = d1->data->ptr + d1->offset;
+  rd_tuning(&ctas_per_sm, &seg_vecs);
+  target = (size_t)ctx->num_sms * ctas_per_sm;
+
+  memset(&want, 0, sizeof(want));
+  want.dst_tc = d0 != NULL ? d0->typecode : gr->src_tc;
+  want.write_val = need_val;
+  want.write_idx = need_idx;
+  want.idx64 = L.nr_total >= 0xffffffffULL;
+  want.vec = 1;
+  want.tpo = 1;
+  L.splits = 1;
+
+  if (L.nr_total > 0 && L.nr >= 1 && L.rsrc[L.nr - 1] == (long long)elsize &&
+      L.rdim[L.nr - 1] >= 512) {
+    /* --- contiguous reduced run --- */
+    unsigned vec = (unsigned)(16 / elsize);
+    unsigned long long rows_outer = L.nr_total / L.rdim[L.nr - 1];
+    want.shape = SHAPE_ROWS;
+    if (vec > 1 && p_src % 16 == 0 && all_multiple(L.fsrc, (unsigned)L.nf, 16) &&
+        all_multiple(L.rsrc, (unsigned)L.nr - 1, 16))
+      want.vec = (int)vec;
+    L.inner = L.rdim[L.nr - 1];
+    L.seg = (unsigned long long)RD_THREADS * vec * seg_vecs;
+    L.nseg = (L.inner + L.seg - 1) / L.seg;
+    L.units = rows_outer * L.nseg;
+    if (L.nf_total < target / 4) {
+      unsigned long long s = (target + L.nf_total - 1) / L.nf_total;
+      if (s > L.units) s = L.units;
+      if (s > 65535) s = 65535;
+      L.splits = s ? s : 1;
+    }
+    {
+      unsigned long long nwork = L.nf_total * L.splits;
+      grid[0] = nwork > 0x7fffffffULL ? 0x7fffffffu : (unsigned)nwork;
+    }
+  } else if (L.nr_total > 0 && L.nf >= 1 && L.fsrc[L.nf - 1] == (long long)elsize &&
+             L.fdim[L.nf - 1] >= 16) {
+    /* --- contiguous kept run --- */
+    unsigned vec = (unsigned)(16 / elsize);
+    unsigned long long ko, nwork, s;
+    if (vec > 4) vec = 4;
+    want.shape = SHAPE_COLS;
+    L.inner = L.fdim[L.nf - 1];
+    while (vec > 1 && !(L.inner % vec == 0 && p_src % (vec * elsize) == 0 &&
+                        all_multiple(L.fsrc, (unsigned)L.nf - 1, (long long)(vec * elsize)) &&
+                        all_multiple(L.rsrc, (unsigned)L.nr, (long long)(vec * elsize))))
+      vec /= 2;
+    want.vec = (int)vec;
+    L.tiles = (L.inner + 32ULL * vec - 1) / (32ULL * vec);
+    ko = L.nf_total / L.inner;
+    nwork = ko * L.tiles;
+    s = (target / 2 + nwork - 1) / nwork;
+    if (s > (L.nr_total + RD_BY * 8 - 1) / (RD_BY * 8)) s = (L.nr_total + RD_BY * 8 - 1) / (RD_BY * 8);
+    if (s > 1024) s = 1024;
+    L.splits = s ? s : 1;
+    grid[0] = nwork > 0x7fffffffULL ? 0x7fffffffu : (unsigned)nwork;
+    grid[1] = (unsigned)L.splits;
+    block[0] = 32;
+    block[1] = RD_BY;
+  } else {
+    /* --- arbitrary strides --- */
+    unsigned long long groups_per_block, blocks;
+    want.shape = SHAPE_GENERAL;
+    if (L.nr_total >= 2048 && L.nf_total < 4096) want.tpo = RD_THREADS;
+    else if (L.nr_total >= 64) want.tpo = 32;
+    groups_per_block = RD_THREADS / (unsigned)want.tpo;
+    blocks = (L.nf_total + groups_per_block - 1) / groups_per_block;
+    if (blocks > (unsigned long long)target * 8) blocks = (unsigned long long)target * 8;
+    grid[0] = (unsigned)(blocks ? blocks : 1);
+  }
+
+  v1 = get_variant(gr, &want, &err);
+  if (v1 == NULL) return err;
+  if (L.splits > 1) {
+    size_t cells = (size_t)L.splits * (size_t)L.nf_total;
+    rd_variant fin = want;
+    err = ensure_scratch(gr, cells * 16);
+    if (err != GA_NO_ERROR) return err;
+    p_val = gr->scratch->ptr;
+    p_idx = gr->scratch->ptr + cells * 8;
+    fin.shape = SHAPE_GENERAL;
+    fin.stage2 = 1;
+    fin.vec = 1;
+    fin.tpo = L.splits >= 256 ? RD_THREADS : (L.splits >= 16 ? 32 : 1);
+    v2 = get_variant(gr, &fin, &err);
+    if (v2 == NULL) return err;
+  }
+
+  params[0] = &L;
+  params[1] = &p_src;
+  params[2] = &p_d0;
+  params[3] = &p_d1;
+  params[4] = &p_val;
+  params[5] = &p_idx;
+  err = ga_launch(ctx, &v1->fn, grid, block, 0, params);
+  if (err != GA_NO_ERROR || v2 == NULL) return err;
+  {
+    unsigned long long gpb = RD_THREADS / (unsigned)v2->tpo;
+    unsigned long long blocks = (L.nf_total + gpb - 1) / gpb;
+    unsigned g2[3] = {1, 1, 1}, b2[3] = {RD_THREADS, 1, 1};
+    if (blocks > (unsigned long long)target * 8) blocks = (unsigned long long)target * 8;
+    g2[0] = (unsigned)(blocks ? blocks : 1);
+    return ga_launch(ctx, &v2->fn, g2, b2, 0, params);
+  }
+}
+
+/* ------------------------------------------------- GpuArray_maxandargmax */
+
+typedef struct mam_entry {
+  int tc;
+  GpuReduction *gr;
+  struct mam_entry *next;
+} mam_entry;
+
+void ga_maxandargmax_cache_free(gpucontext *ctx) {
+  mam_entry *e = (mam_entry *)ctx->maxandargmax_cache, *n;
+  ctx->maxandargmax_cache = NULL;
+  for (; e != NULL; e = n) {
+    n = e->next;
+    GpuReduction_free(e->gr);
+    free(e);
+  }
+}
+
+int GpuArray_maxandargmax(GpuArray *dstMax, GpuArray *dstArgmax, const GpuArray *src,
+                          unsigned reduxLen, const unsigned *reduxList) {
+  gpucontext *ctx;
+  mam_entry *e;
+  int axes[64], err;
+  unsigned i;
+
+  if (dstMax == NULL || dstArgmax == NULL || src == NULL || reduxList == NULL || src->data == NULL)
+    return ga_err_set(ga_global_err, GA_INVALID_ERROR, "GpuArray_maxandargmax: NULL argument");
+  ctx = GpuArray_context(src);
+  if (src->nd == 0 || reduxLen == 0 || reduxLen > src->nd || reduxLen > 64)
+    return ga_err_set(ctx->err, GA_INVALID_ERROR, "Invalid rank or reduction axis count");
+  for (i = 0; i < reduxLen; i++) {
+    if (reduxList[i] >= src->nd)
+      return ga_err_fmt(ctx->err, GA_INVALID_ERROR, "Reduction axis %u out of range", reduxList[i]);
+    axes[i] = (int)reduxList[i];
+  }
+  for (e = (mam_entry *)ctx->maxandargmax_cache; e != NULL; e = e->next)
+    if (e->tc == src->typecode) break;
+  if (e == NULL) {
+    e = calloc(1, sizeof(*e));
+    if (e == NULL) return ga_err_sys(ctx->err, "calloc");
+    err = GpuReduction_new(&e->gr, ctx, GA_REDUCE_MAXANDARGMAX, 0, 0, src->typecode, 0);
+    if (err != GA_NO_ERROR) {
+      free(e);
+      return err;
+    }
+    e->tc = src->typecode;
+    e->next = (mam_entry *)ctx->maxandargmax_cache;
+    ctx->maxandargmax_cache = e;
+  }
+  return GpuReduction_call(e->gr, dstMax, dstArgmax, src, reduxLen, axes, 0);
+}

@@ -1,0 +1,400 @@
+/* Reduction kernels for sm_100a: three traversal shapes over one operator
+ * vocabulary.
+ *
+ * They replace (a) the reference's maxandargmax kernel, where ONE thread
+ * walks the whole reduced extent of its output serially
+ * (src/gpuarray_reduction.c:520-607), and (b) pygpu's reduk template, a block
+ * per output with a shared-memory tree and a div/mod per element
+ * (pygpu/reduction.py:33-134). Here the reduced extent itself is spread over
+ * threads, warps, CTAs and - when there are few outputs - over several CTAs
+ * whose partial results a second tiny launch combines in a fixed order, so
+ * results are deterministic and no thread ever waits on another CTA.
+ *
+ *   ga_rd_rows     the innermost reduced dimension is contiguous in memory:
+ *                  a CTA streams 128-bit loads along it, warp shuffles then
+ *                  one shared-memory hop finish the CTA's share
+ *   ga_rd_cols     the innermost KEPT dimension is contiguous: a thread owns
+ *                  GA_RD_VEC adjacent outputs and walks down the reduced
+ *                  extent; blockDim.y row-lanes and gridDim.y splits share it
+ *   ga_rd_general  any strides: GA_RD_TPO threads per output decode each
+ *                  element's offset; also the second pass over partials
+ *
+ * Operators. GA_RD_KIND 0: acc = COMBINE(acc, MAP(x)) from IDENT (sum, prod,
+ * prodnz, and, or, xor, all, any). GA_RD_KIND 1: (value, flat index) pairs
+ * for min/max/arg*: `b` replaces `a` when BETTER(b.v, a.v) or when the values
+ * compare equal and b has the smaller flat index - the first occurrence in
+ * reduxList order wins, +0.0 and -0.0 tie, and a NaN never wins by
+ * comparison. The single case in which the reference kernel returns a NaN -
+ * the very first reduced element is one (:557-561, :583-586) - is applied
+ * when the final value is written.
+ *
+ * The including translation unit defines (all by the host, ga_reduction.c):
+ *   GA_RD_SRC_T   storage type of a source element
+ *   GA_RD_X_T     type after GA_RD_LOAD (float for ga_half, else SRC_T)
+ *   GA_RD_ACC_T   accumulator (kind 0) or compared value type (kind 1)
+ *   GA_RD_DST_T   storage type of the value destination
+ *   GA_RD_LOAD(raw) GA_RD_STORE(acc) GA_RD_MAP(x) GA_RD_COMBINE(a,b)
+ *   GA_RD_IDENT GA_RD_BETTER(b,a) GA_RD_KIND GA_RD_ISFLOAT
+ *   GA_RD_WRITE_VAL GA_RD_WRITE_IDX GA_RD_IDX_T GA_RD_VEC GA_RD_THREADS
+ *   GA_RD_TPO GA_RD_STAGE2 GA_RD_BY
+ */
+#include "cluda.h"
+
+#define GA_RD_MAXD 8
+typedef unsigned long long ga__u64;
+typedef long long ga__i64;
+
+/* Mirrors the block marshalled by fill_layout() in ga_reduction.c. */
+struct ga__rd_layout {
+  ga__u64 nf_total;          /* number of outputs */
+  ga__u64 nr_total;          /* reduced elements per output */
+  ga__u64 nf, nr;            /* kept / reduced dimension counts */
+  ga__u64 fdim[GA_RD_MAXD];  /* kept extents, outermost first */
+  ga__i64 fsrc[GA_RD_MAXD];  /* byte strides of the kept dims in src */
+  ga__i64 fdst0[GA_RD_MAXD]; /* ... in the value destination */
+  ga__i64 fdst1[GA_RD_MAXD]; /* ... in the index destination */
+  ga__u64 rdim[GA_RD_MAXD];  /* reduced extents in traversal order */
+  ga__i64 rsrc[GA_RD_MAXD];  /* their byte strides in src */
+  ga__u64 rmul[GA_RD_MAXD];  /* their weight in the flat (reduxList-order) index */
+  ga__u64 splits;            /* CTAs (rows) / gridDim.y (cols) sharing one output */
+  ga__u64 inner;             /* rows: contiguous reduced run; cols: contiguous kept run */
+  ga__u64 seg;               /* rows: elements per unit of work */
+  ga__u64 nseg;              /* rows: units per run */
+  ga__u64 units;             /* rows: units per output */
+  ga__u64 tiles;             /* cols: column tiles per contiguous kept run */
+};
+
+struct ga__state {
+  GA_RD_ACC_T v;
+#if GA_RD_KIND == 1
+  GA_RD_IDX_T i;
+#endif
+};
+
+#define GA__IDX_NONE (~(GA_RD_IDX_T)0)
+
+static __device__ __forceinline__ ga__state ga__init() {
+  ga__state s;
+  s.v = (GA_RD_ACC_T)(GA_RD_IDENT);
+#if GA_RD_KIND == 1
+  s.i = GA__IDX_NONE;
+#endif
+  return s;
+}
+
+/* fold one source element (already through GA_RD_LOAD) with flat index f */
+static __device__ __forceinline__ void ga__take(ga__state &s, const GA_RD_X_T x, const GA_RD_IDX_T f) {
+#if GA_RD_KIND == 0
+  s.v = GA_RD_COMBINE(s.v, GA_RD_MAP(x));
+#else
+  if (GA_RD_BETTER(x, s.v) || (x == s.v && f < s.i)) {
+    s.v = x;
+    s.i = f;
+  }
+#endif
+}
+
+static __device__ __forceinline__ void ga__merge(ga__state &a, const ga__state &b) {
+#if GA_RD_KIND == 0
+  a.v = GA_RD_COMBINE(a.v, b.v);
+#else
+  if (GA_RD_BETTER(b.v, a.v) || (b.v == a.v && b.i < a.i)) a = b;
+#endif
+}
+
+template <typename T>
+static __device__ __forceinline__ T ga__shfl_down(const T v, const int delta) {
+  if (sizeof(T) <= 4) {
+    unsigned int w = 0;
+    memcpy(&w, &v, sizeof(T));
+    w = __shfl_down_sync(0xffffffffu, w, delta);
+    T r;
+    memcpy(&r, &w, sizeof(T));
+    return r;
+  } else {
+    unsigned long long w;
+    memcpy(&w, &v, sizeof(T));
+    w = __shfl_down_sync(0xffffffffu, w, delta);
+    T r;
+    memcpy(&r, &w, sizeof(T));
+    return r;
+  }
+}
+
+/* result valid in lane 0; lanes combine in a fixed order */
+static __device__ __forceinline__ ga__state ga__warp_reduce(ga__state s) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    ga__state t;
+    t.v = ga__shfl_down(s.v, d);
+#if GA_RD_KIND == 1
+    t.i = ga__shfl_down(s.i, d);
+#endif
+    ga__merge(s, t);
+  }
+  return s;
+}
+
+/* result valid in thread 0 of the CTA; `sm` holds one state per warp */
+static __device__ __forceinline__ ga__state ga__block_reduce(ga__state s, ga__state *sm,
+                                                             const unsigned tid,
+                                                             const unsigned nthreads) {
+  s = ga__warp_reduce(s);
+  if ((tid & 31u) == 0) sm[tid >> 5] = s;
+  __syncthreads();
+  if (tid < 32) {
+    s = tid < (nthreads >> 5) ? sm[tid] : ga__init();
+    s = ga__warp_reduce(s);
+  }
+  return s;
+}
+
+/* byte offset of output `o` through one stride vector of the kept dims */
+static __device__ __forceinline__ ga__i64 ga__foff(const ga__rd_layout &L, const ga__i64 *str,
+                                                   ga__u64 o) {
+  ga__i64 off = 0;
+  for (int d = (int)L.nf - 1; d > 0; d--) {
+    const ga__u64 q = o / L.fdim[d];
+    off += (ga__i64)(o - q * L.fdim[d]) * str[d];
+    o = q;
+  }
+  if (L.nf > 0) off += (ga__i64)o * str[0];
+  return off;
+}
+
+/* final result of output `o` */
+static __device__ __forceinline__ void ga__emit(const ga__rd_layout &L, const char *src, char *d0,
+                                                char *d1, const ga__u64 o, ga__state s) {
+#if GA_RD_KIND == 1 && GA_RD_ISFLOAT
+  {
+    const GA_RD_SRC_T raw = *reinterpret_cast<const GA_RD_SRC_T *>(src + ga__foff(L, L.fsrc, o));
+    const GA_RD_X_T first = GA_RD_LOAD(raw);
+    if (first != first) {
+      s.v = first;
+      s.i = 0;
+    }
+  }
+#endif
+#if GA_RD_WRITE_VAL
+  *reinterpret_cast<GA_RD_DST_T *>(d0 + ga__foff(L, L.fdst0, o)) = GA_RD_STORE(s.v);
+#endif
+#if GA_RD_KIND == 1 && GA_RD_WRITE_IDX
+  *reinterpret_cast<ga__i64 *>(d1 + ga__foff(L, L.fdst1, o)) = (ga__i64)s.i;
+#endif
+}
+
+static __device__ __forceinline__ void ga__put_partial(const ga__rd_layout &L, GA_RD_ACC_T *pval,
+                                                       GA_RD_IDX_T *pidx, const ga__u64 split,
+                                                       const ga__u64 o, const ga__state &s) {
+  pval[split * L.nf_total + o] = s.v;
+#if GA_RD_KIND == 1
+  pidx[split * L.nf_total + o] = s.i;
+#endif
+}
+
+template <int N>
+struct alignas((sizeof(GA_RD_SRC_T) * N >= 16) ? 16 : sizeof(GA_RD_SRC_T) * N) ga__rd_pack {
+  GA_RD_SRC_T v[N];
+};
+
+/* ------------------------------------------------------------------ rows */
+#if defined(GA_RD_BUILD_ROWS)
+extern "C" __global__ void __launch_bounds__(GA_RD_THREADS)
+ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, char *d1,
+           GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx) {
+  __shared__ ga__state sm[32];
+  const ga__u64 nwork = L.nf_total * L.splits;
+  const int nro = (int)L.nr - 1; /* reduced dims outside the contiguous run */
+  const GA_RD_IDX_T imul = (GA_RD_IDX_T)L.rmul[nro];
+
+  for (ga__u64 w = blockIdx.x; w < nwork; w += gridDim.x) {
+    ga__u64 o = w, split = 0;
+    if (L.splits > 1) {
+      o = w / L.splits;
+      split = w - o * L.splits;
+    }
+    const ga__u64 ub = split * L.units / L.splits, ue = (split + 1) * L.units / L.splits;
+    const char *obase = src + ga__foff(L, L.fsrc, o);
+    ga__state st[GA_RD_VEC];
+#pragma unroll
+    for (int j = 0; j < GA_RD_VEC; j++) st[j] = ga__init();
+
+    for (ga__u64 u = ub; u < ue; u++) {
+      ga__u64 r = u, g = 0;
+      if (L.nseg > 1) {
+        r = u / L.nseg;
+        g = u - r * L.nseg;
+      }
+      ga__i64 roff = 0;
+      GA_RD_IDX_T fbase = 0;
+      for (int d = nro - 1; d >= 0; d--) {
+        const ga__u64 q = r / L.rdim[d], c = r - q * L.rdim[d];
+        r = q;
+        roff += (ga__i64)c * L.rsrc[d];
+        fbase += (GA_RD_IDX_T)c * (GA_RD_IDX_T)L.rmul[d];
+      }
+      const ga__u64 e0 = g * L.seg;
+      const unsigned int len = (unsigned int)((L.inner - e0 < L.seg) ? (L.inner - e0) : L.seg);
+      const GA_RD_SRC_T *p = reinterpret_cast<const GA_RD_SRC_T *>(obase + roff) + e0;
+      fbase += (GA_RD_IDX_T)e0 * imul;
+      const unsigned int nv = len / GA_RD_VEC;
+      const ga__rd_pack<GA_RD_VEC> *pv = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(p);
+#pragma unroll 4
+      for (unsigned int i = threadIdx.x; i < nv; i += GA_RD_THREADS) {
+        const ga__rd_pack<GA_RD_VEC> t = pv[i];
+#pragma unroll
+        for (int j = 0; j < GA_RD_VEC; j++)
+          ga__take(st[j], GA_RD_LOAD(t.v[j]),
+                   fbase + (GA_RD_IDX_T)(i * GA_RD_VEC + (unsigned)j) * imul);
+      }
+      for (unsigned int i = nv * GA_RD_VEC + threadIdx.x; i < len; i += GA_RD_THREADS)
+        ga__take(st[0], GA_RD_LOAD(p[i]), fbase + (GA_RD_IDX_T)i * imul);
+    }
+#pragma unroll
+    for (int j = 1; j < GA_RD_VEC; j++) ga__merge(st[0], st[j]);
+    const ga__state tot = ga__block_reduce(st[0], sm, threadIdx.x, GA_RD_THREADS);
+    if (threadIdx.x == 0) {
+      if (L.splits == 1) ga__emit(L, src, d0, d1, o, tot);
+      else ga__put_partial(L, pval, pidx, split, o, tot);
+    }
+    __syncthreads();
+  }
+}
+#endif
+
+/* ------------------------------------------------------------------ cols */
+#if defined(GA_RD_BUILD_COLS)
+extern "C" __global__ void __launch_bounds__(32 * GA_RD_BY)
+ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, char *d1,
+           GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx) {
+  __shared__ ga__state sm[GA_RD_BY][32 * GA_RD_VEC + 1];
+  const unsigned tx = threadIdx.x, ty = threadIdx.y;
+  const ga__u64 kc = L.inner;                 /* contiguous kept run */
+  const ga__u64 ko_total = L.nf_total / kc;   /* outer kept positions */
+  const ga__u64 nwork = ko_total * L.tiles;
+  const ga__u64 split = blockIdx.y;
+  const ga__u64 jb = split * L.nr_total / L.splits, je = (split + 1) * L.nr_total / L.splits;
+
+  for (ga__u64 w = blockIdx.x; w < nwork; w += gridDim.x) {
+    ga__u64 ko = 0, tile = w;
+    if (ko_total > 1) {
+      ko = w / L.tiles;
+      tile = w - ko * L.tiles;
+    }
+    const ga__u64 col0 = (tile * 32 + tx) * GA_RD_VEC;
+    const bool live = col0 < kc;
+    const ga__u64 o0 = ko * kc + col0; /* first output of this thread */
+    ga__state st[GA_RD_VEC];
+#pragma unroll
+    for (int j = 0; j < GA_RD_VEC; j++) st[j] = ga__init();
+
+    if (live) {
+      /* kept offset: the innermost kept dim is the contiguous one */
+      ga__i64 koff = (ga__i64)col0 * (ga__i64)sizeof(GA_RD_SRC_T);
+      {
+        ga__u64 q = ko;
+        for (int d = (int)L.nf - 2; d >= 0; d--) {
+          const ga__u64 qq = q / L.fdim[d];
+          koff += (ga__i64)(q - qq * L.fdim[d]) * L.fsrc[d];
+          q = qq;
+        }
+      }
+      const char *base = src + koff;
+#pragma unroll 4
+      for (ga__u64 j = jb + ty; j < je; j += GA_RD_BY) {
+        ga__i64 roff;
+        GA_RD_IDX_T f;
+        if (L.nr == 1) {
+          roff = (ga__i64)j * L.rsrc[0];
+          f = (GA_RD_IDX_T)j * (GA_RD_IDX_T)L.rmul[0];
+        } else {
+          ga__u64 r = j;
+          roff = 0;
+          f = 0;
+          for (int d = (int)L.nr - 1; d >= 0; d--) {
+            const ga__u64 q = r / L.rdim[d], c = r - q * L.rdim[d];
+            r = q;
+            roff += (ga__i64)c * L.rsrc[d];
+            f += (GA_RD_IDX_T)c * (GA_RD_IDX_T)L.rmul[d];
+          }
+        }
+        const ga__rd_pack<GA_RD_VEC> t =
+            *reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(base + roff);
+#pragma unroll
+        for (int k = 0; k < GA_RD_VEC; k++) ga__take(st[k], GA_RD_LOAD(t.v[k]), f);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < GA_RD_VEC; k++) sm[ty][tx * GA_RD_VEC + k] = st[k];
+    __syncthreads();
+    if (ty == 0 && live) {
+#pragma unroll
+      for (int k = 0; k < GA_RD_VEC; k++) {
+        ga__state tot = sm[0][tx * GA_RD_VEC + k];
+        for (int y = 1; y < GA_RD_BY; y++) ga__merge(tot, sm[y][tx * GA_RD_VEC + k]);
+        if (L.splits == 1) ga__emit(L, src, d0, d1, o0 + k, tot);
+        else ga__put_partial(L, pval, pidx, split, o0 + k, tot);
+      }
+    }
+    __syncthreads();
+  }
+}
+#endif
+
+/* --------------------------------------------------------------- general */
+#if defined(GA_RD_BUILD_GENERAL)
+/* GA_RD_TPO threads per output (1, 32 or GA_RD_THREADS). With GA_RD_STAGE2
+ * the input is the partial buffers [splits][outputs] of a first pass. */
+extern "C" __global__ void __launch_bounds__(GA_RD_THREADS)
+ga_rd_general(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, char *d1,
+              GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx) {
+#if GA_RD_TPO > 32
+  __shared__ ga__state sm[32];
+#endif
+  const unsigned lane = threadIdx.x % GA_RD_TPO;
+  const ga__u64 group = ((ga__u64)blockIdx.x * GA_RD_THREADS + threadIdx.x) / GA_RD_TPO;
+  const ga__u64 ngroups = (ga__u64)gridDim.x * (GA_RD_THREADS / GA_RD_TPO);
+  /* every group runs the same number of rounds so that CTA-wide barriers match */
+  const ga__u64 rounds = (L.nf_total + ngroups - 1) / ngroups;
+
+  for (ga__u64 it = 0; it < rounds; it++) {
+    const ga__u64 o = group + it * ngroups;
+    const bool live = o < L.nf_total;
+    ga__state st = ga__init();
+    if (live) {
+#if GA_RD_STAGE2
+      for (ga__u64 s = lane; s < L.splits; s += GA_RD_TPO) {
+        ga__state t;
+        t.v = pval[s * L.nf_total + o];
+#if GA_RD_KIND == 1
+        t.i = pidx[s * L.nf_total + o];
+#endif
+        ga__merge(st, t);
+      }
+#else
+      const char *obase = src + ga__foff(L, L.fsrc, o);
+      for (ga__u64 j = lane; j < L.nr_total; j += GA_RD_TPO) {
+        ga__u64 r = j;
+        ga__i64 roff = 0;
+        GA_RD_IDX_T f = 0;
+        for (int d = (int)L.nr - 1; d >= 0; d--) {
+          const ga__u64 q = r / L.rdim[d], c = r - q * L.rdim[d];
+          r = q;
+          roff += (ga__i64)c * L.rsrc[d];
+          f += (GA_RD_IDX_T)c * (GA_RD_IDX_T)L.rmul[d];
+        }
+        const GA_RD_SRC_T raw = *reinterpret_cast<const GA_RD_SRC_T *>(obase + roff);
+        ga__take(st, GA_RD_LOAD(raw), f);
+      }
+#endif
+    }
+#if GA_RD_TPO == 32
+    st = ga__warp_reduce(st);
+#elif GA_RD_TPO > 32
+    st = ga__block_reduce(st, sm, threadIdx.x, GA_RD_THREADS);
+    __syncthreads();
+#endif
+    if (live && lane == 0) ga__emit(L, src, d0, d1, o, st);
+  }
+}
+#endif
