@@ -562,11 +562,125 @@ static int call_strided(GpuElemwise *ge, void **args, size_t n, unsigned int nd)
   return ga_launch(ctx, &v->fn, grid, block, 0, ge->params);
 }
 
-/* Placeholder until the tiled-transpose template is wired in. */
+/* Tiled transpose: taken when some pure input is contiguous along a dimension
+ * P other than the innermost one (Q) and would otherwise be gathered element
+ * by element. Sets *handled when the call was dispatched here. */
 static int call_transpose(GpuElemwise *ge, void **args, size_t n, unsigned int nd, int *handled) {
-  (void)ge; (void)args; (void)n; (void)nd;
+  gpucontext *ctx = ge->ctx;
+  ew_variant want, *v;
+  CUdeviceptr ptrs[32];
+  unsigned int i, j, k, p = 0, q = nd - 1, pdim_ax = nd, nout, best_votes = 0;
+  unsigned grid[3] = {1, 1, 1}, block[3] = {GA_EW_THREADS, 1, 1};
+  unsigned long long *w, tiles_p, tiles_q, nouter, ntiles;
+  size_t words, smem = 0;
+  int err = GA_NO_ERROR, tile;
+  (void)n;
+
   *handled = 0;
-  return GA_NO_ERROR;
+  if (nd < 2 || getenv("GPUARRAY_B200_NO_TRANSPOSE") != NULL) return GA_NO_ERROR;
+  /* vote for the dimension along which gathered inputs are contiguous */
+  for (j = 0; j + 1 < nd; j++) {
+    unsigned votes = 0;
+    for (i = 0, k = 0; i < ge->n; i++) {
+      const gpuelemwise_arg *a = &ge->args[i];
+      ssize_t es;
+      if (!is_array(a)) continue;
+      es = (ssize_t)gpuarray_get_elsize(a->typecode);
+      if (!is_output(a) && ge->strides[k][j] == es && ge->strides[k][q] != es &&
+          ge->strides[k][q] != 0)
+        votes++;
+      k++;
+    }
+    if (votes > best_votes) {
+      best_votes = votes;
+      pdim_ax = j;
+    }
+  }
+  if (best_votes == 0 || ge->dims[pdim_ax] < 16 || ge->dims[q] < 16) return GA_NO_ERROR;
+
+  memset(&want, 0, sizeof(want));
+  want.kind = 2;
+  want.nd = nd;
+  want.ept = ge->ept;
+  want.unroll = 1;
+  want.idx32 = 0;
+  for (i = 0, k = 0; i < ge->n; i++) {
+    const gpuelemwise_arg *a = &ge->args[i];
+    size_t es, vb;
+    ssize_t sq, sp;
+    unsigned long long mode = 0;
+    if (!is_array(a)) continue;
+    ptrs[k] = array_base((const GpuArray *)args[i]);
+    es = gpuarray_get_elsize(a->typecode);
+    vb = es * (size_t)want.ept > 16 ? 16 : es * (size_t)want.ept;
+    sq = ge->strides[k][q];
+    sp = ge->strides[k][pdim_ax];
+    if (!is_output(a) && sp == (ssize_t)es && sq != (ssize_t)es && sq != 0) mode = 3;
+    else if (sq == 0 && !is_output(a)) mode = 2;
+    else if (sq == (ssize_t)es && ge->dims[q] % (size_t)want.ept == 0 && ptrs[k] % vb == 0) {
+      mode = 1;
+      for (j = 0; j + 1 < nd; j++)
+        if (ge->strides[k][j] % (ssize_t)vb != 0) mode = 0;
+    }
+    want.modes |= mode << (2 * k);
+    k++;
+  }
+  /* tile edge: 64 unless the staged tiles would not fit in 48 KiB */
+  for (tile = 64; tile >= 32; tile /= 2) {
+    smem = 0;
+    for (i = 0, k = 0; i < ge->n; i++) {
+      if (!is_array(&ge->args[i])) continue;
+      if (((want.modes >> (2 * k)) & 3) == 3) {
+        size_t es = gpuarray_get_elsize(ge->args[i].typecode);
+        smem += (size_t)tile * ((size_t)tile + (es >= 4 ? 1 : 4 / es)) * es;
+      }
+      k++;
+    }
+    if (smem <= 46 * 1024) break;
+  }
+  if (tile < 32 || tile % want.ept != 0) return GA_NO_ERROR;
+  want.tp = tile;
+  want.tq = tile;
+  v = get_variant(ge, &want, &err);
+  *handled = 1;
+  if (v == NULL) return err;
+
+  nout = nd > 2 ? nd - 2 : 1;
+  words = 5 + nout + 2 * (size_t)ge->narray + (size_t)ge->narray * nout;
+  if (ensure_blob(ge, words) != 0) return ga_err_sys(ctx->err, "realloc");
+  w = ge->blob;
+  memset(w, 0, words * sizeof(*w));
+  tiles_p = (ge->dims[pdim_ax] + (size_t)tile - 1) / (size_t)tile;
+  tiles_q = (ge->dims[q] + (size_t)tile - 1) / (size_t)tile;
+  nouter = 1;
+  for (j = 0, k = 0; j < nd; j++) {
+    if (j == pdim_ax || j == q) continue;
+    w[5 + k++] = ge->dims[j];
+    nouter *= ge->dims[j];
+  }
+  w[0] = ge->dims[pdim_ax];
+  w[1] = ge->dims[q];
+  w[2] = tiles_p;
+  w[3] = tiles_q;
+  w[4] = nouter;
+  for (k = 0; k < ge->narray; k++) {
+    unsigned int oi = 0;
+    w[5 + nout + k] = (unsigned long long)(long long)ge->strides[k][pdim_ax];
+    w[5 + nout + ge->narray + k] = (unsigned long long)(long long)ge->strides[k][q];
+    for (j = 0; j < nd; j++) {
+      if (j == pdim_ax || j == q) continue;
+      w[5 + nout + 2 * (size_t)ge->narray + (size_t)k * nout + oi++] =
+          (unsigned long long)(long long)ge->strides[k][j];
+    }
+  }
+  ge->params[p++] = w;
+  for (i = 0, k = 0; i < ge->n; i++)
+    if (is_array(&ge->args[i])) ge->params[p++] = &ptrs[k++];
+  for (i = 0; i < ge->n; i++)
+    if (!is_array(&ge->args[i])) ge->params[p++] = args[i];
+  ntiles = tiles_p * tiles_q * nouter;
+  grid[0] = ntiles > 0x7fffffffULL ? 0x7fffffffu : (unsigned)ntiles;
+  return ga_launch(ctx, &v->fn, grid, block, 0, ge->params);
 }
 
 int GpuElemwise_call(GpuElemwise *ge, void **args, int flags) {

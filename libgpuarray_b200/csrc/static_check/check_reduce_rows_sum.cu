@@ -1,0 +1,24 @@
+/* Build-time instantiation: float32 SUM along a contiguous reduced run. */
+#define GA_RD_SRC_T ga_float
+#define GA_RD_X_T ga_float
+#define GA_RD_ACC_T ga_float
+#define GA_RD_DST_T ga_float
+#define GA_RD_LOAD(raw) (raw)
+#define GA_RD_STORE(a) ((GA_RD_DST_T)(a))
+#define GA_RD_MAP(x) ((GA_RD_ACC_T)(x))
+#define GA_RD_COMBINE(a, b) ((a) + (b))
+#define GA_RD_IDENT 0
+#define GA_RD_BETTER(b, a) ((b) > (a))
+#define GA_RD_KIND 0
+#define GA_RD_ISFLOAT 1
+#define GA_RD_WRITE_VAL 1
+#define GA_RD_WRITE_IDX 0
+#define GA_RD_IDX_T unsigned int
+#define GA_RD_VEC 4
+#define GA_RD_THREADS 256
+#define GA_RD_TPO 1
+#define GA_RD_STAGE2 0
+#define GA_RD_BY 8
+#define GA_RD_BUILD_ROWS
+#define GA_RD_BUILD_COLS
+#include "ga_reduce.cuh"

@@ -72,6 +72,15 @@ static __device__ __forceinline__ ga_half ga_float2half(float f) {
 #ifdef INFINITY
 #undef INFINITY
 #endif
+#ifdef HUGE_VALF
+#undef HUGE_VALF
+#endif
+#ifdef HUGE_VAL
+#undef HUGE_VAL
+#endif
+#ifdef MAXFLOAT
+#undef MAXFLOAT
+#endif
 #define NAN __int_as_float(0x7fffffff)
 #define INFINITY __int_as_float(0x7f800000)
 #define HUGE_VALF INFINITY
