@@ -1,0 +1,441 @@
+#!/usr/bin/env python
+"""Benchmark of the elementwise / reduction hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload cfg3] [--no-side-configs]
+
+Headline workload (one "step" = one pass of the hot path over one batch):
+GpuReduction MAXANDARGMAX over the last axis of fp32 logits (16384, 32000) per
+GPU, values N(0,1) rounded to 1/64 (ties occur), outputs fp32 max + 8-byte
+first-occurrence index. With N GPUs every rank holds its own (16384, 32000)
+slab of a (16384*N, 32000) array: rows shard with no communication (weak
+scaling). Metric: effective HBM GB/s = algorithmic bytes / device time.
+
+The JSON line also carries: `e2e` (same call with HOST input: pinned
+host->device copy of the slab and device->host read of the results inside the
+timed region), `roofline` (dominant kernel against the measured copy peak),
+`cpu_baseline` (the C oracle port on the host cores, bounded sample), `clocks`
+(nvidia-smi samples during the timed region), `gpu_launches`, and `configs`
+(the other single-GPU workloads of the suite, each timed cold: L2 flushed
+between launches).
+
+`--impl reference` times the reference arm: libgpuarray's CPU path is pygpu on
+a CPU OpenCL device (pocl), which cannot run here (no OpenCL loader, no pocl,
+no mako), so the arm is the C restatement of the reference kernel in
+oracle/oracle_kernels.c with all host threads (OpenMP), on the same workload.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+ROWS, COLS = 16384, 32000
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def make_logits(rank, rows=ROWS):
+    """Seed 2; rank r draws from the r-th jumped copy of the stream."""
+    bg = np.random.PCG64(2)
+    rng = np.random.Generator(bg.jumped(rank) if rank else bg)
+    x = rng.standard_normal((rows, COLS), dtype=np.float32)
+    np.multiply(x, 64, out=x)
+    np.round(x, out=x)
+    np.multiply(x, np.float32(1.0 / 64), out=x)
+    return x
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, dev):
+        self.dev = dev
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.dev), "--query-gpu=" + self.QUERY,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._pump, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [s.strip() for s in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def device_timer(torch, stream):
+    class T:
+        def __init__(self):
+            self.pairs = []
+
+        def span(self):
+            a = torch.cuda.Event(enable_timing=True)
+            b = torch.cuda.Event(enable_timing=True)
+            self.pairs.append((a, b))
+            return a, b
+
+        def total_ms(self):
+            return sum(a.elapsed_time(b) for a, b in self.pairs)
+    return T()
+
+
+# --------------------------------------------------------------- reference arm
+
+def run_reference(args, rank):
+    """CPU arm: the oracle's C port of the reference kernel, all host threads."""
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    O.build()
+    sample_rows = 4096                       # bounded sample: 0.5 GB of the 2.1 GB slab per step
+    x = make_logits(0, sample_rows)
+    for _ in range(args.warmup):
+        O.rowmaxarg_f32(x)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.rowmaxarg_f32(x)
+    dt = (time.perf_counter() - t0) / args.steps
+    nbytes = x.nbytes + sample_rows * 12
+    val = nbytes / dt / 1e9
+    cores = os.cpu_count()
+    print(json.dumps({
+        "impl": "reference", "metric": "maxandargmax effective GB/s", "value": val, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "cfg3 MAXANDARGMAX last axis of fp32 (16384, 32000) logits",
+                   "sample": "first %d rows per step" % sample_rows},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": "%d of 16384 rows per step; pygpu-on-pocl (the reference's "
+                                   "CPU path) is unavailable on this box" % sample_rows},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# -------------------------------------------------------------------- our arm
+
+def side_configs(api, ctx, torch, stream, flush):
+    """The other single-GPU workloads, each launch timed cold (L2 flushed)."""
+    out = {}
+    R, W = api.GE_READ, api.GE_WRITE
+    peak, _ = measured_peak()
+
+    def timed(fn, nbytes, reps=20, launches=1):
+        for _ in range(3):
+            fn()
+        t = device_timer(torch, stream)
+        for _ in range(reps):
+            flush()
+            a, b = t.span()
+            a.record(stream)
+            fn()
+            b.record(stream)
+        ctx.sync()
+        us = t.total_ms() * 1e3 / reps
+        gbs = nbytes / us / 1e3
+        return {"us": round(us, 2), "GB/s": round(gbs, 1), "frac_nominal_8TBs": round(gbs / NOMINAL_HBM_GBS, 3),
+                "frac_measured_peak": round(gbs / peak, 3), "bytes": nbytes, "launches": launches}
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+
+    def dev_array(t):
+        return api.GpuArray.from_pointer(ctx, t.data_ptr(), tuple(t.shape),
+                                         {torch.float32: np.float32, torch.float16: np.float16,
+                                          torch.float64: np.float64}[t.dtype])
+
+    # cfg1: out = a*b + 0.5f, n = 2^24 fp32
+    n = 1 << 24
+    ta = torch.rand(n, device="cuda", generator=g) * 2 - 1
+    tb = torch.rand(n, device="cuda", generator=g) * 2 - 1
+    to = torch.empty(n, device="cuda")
+    torch.cuda.synchronize()
+    ga, gb, go = dev_array(ta), dev_array(tb), dev_array(to)
+    ge = api.GpuElemwise(ctx, "out = a * b + 0.5f", [("a", np.float32, R), ("b", np.float32, R),
+                                                      ("out", np.float32, W)], nd=1)
+    out["cfg1_elemwise_f32_contig"] = timed(lambda: ge(ga, gb, go), 3 * 4 * n)
+
+    # cfg2: SUM of fp32 4096x4096 over axis 1 and axis 0
+    tx = torch.randn(4096, 4096, device="cuda", generator=g)
+    ts = torch.empty(4096, device="cuda")
+    torch.cuda.synchronize()
+    gx, gs = dev_array(tx), dev_array(ts)
+    gsum = api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.float32)
+    out["cfg2_sum_axis1"] = timed(lambda: gsum(gs, None, gx, [1]), 4096 * 4096 * 4 + 4096 * 4)
+    out["cfg2_sum_axis0"] = timed(lambda: gsum(gs, None, gx, [0]), 4096 * 4096 * 4 + 4096 * 4,
+                                  launches=2)
+
+    # cfg4: y = max(x + bias, 0), x an NHWC buffer viewed as NCHW, fp16
+    tbuf = torch.randn(64, 56, 56, 256, device="cuda", generator=g).half()
+    tbias = (torch.rand(1, 256, 1, 1, device="cuda", generator=g) * 0.2 - 0.1).half()
+    ty = torch.empty(64, 256, 56, 56, device="cuda", dtype=torch.float16)
+    torch.cuda.synchronize()
+    gbuf = dev_array(tbuf)
+    gxv = gbuf.transpose((0, 3, 1, 2))
+    gbias, gy = dev_array(tbias), dev_array(ty)
+    ge4 = api.GpuElemwise(ctx, "y = fmaxf(x + bias, 0.0f)",
+                          [("x", np.float16, R), ("bias", np.float16, R), ("y", np.float16, W)],
+                          nd=4, convert_f16=True)
+    out["cfg4_f16_bias_relu_nhwc_to_nchw"] = timed(
+        lambda: ge4(gxv, gbias, gy, flags=api.GE_BROADCAST), 2 * tbuf.numel() * 2 + 512)
+    del ta, tb, to, tx, tbuf, ty
+
+    # cfg5: fp64 (2048, 1024, 1024) = 16 GiB: SUM over everything, MIN and MAX over (0, 2)
+    try:
+        t5 = torch.rand(2048, 1024, 1024, device="cuda", dtype=torch.float64, generator=g)
+        t5.mul_(2).sub_(1)
+        t1 = torch.empty((), device="cuda", dtype=torch.float64)
+        tk = torch.empty(1024, device="cuda", dtype=torch.float64)
+        torch.cuda.synchronize()
+        g5, g1, gk = dev_array(t5), dev_array(t1), dev_array(tk)
+        r_sum = api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.float64)
+        r_min = api.GpuReduction(ctx, api.GA_REDUCE_MIN, np.float64)
+        r_max = api.GpuReduction(ctx, api.GA_REDUCE_MAX, np.float64)
+        nb = t5.numel() * 8
+        out["cfg5_f64_sum_all"] = timed(lambda: r_sum(g1, None, g5, [0, 1, 2]), nb + 8, reps=5,
+                                        launches=2)
+        out["cfg5_f64_min_axes02"] = timed(lambda: r_min(gk, None, g5, [0, 2]), nb + 8192, reps=5,
+                                           launches=2)
+        out["cfg5_f64_max_axes02"] = timed(lambda: r_max(gk, None, g5, [0, 2]), nb + 8192, reps=5,
+                                           launches=2)
+        del t5
+    except Exception as e:       # e.g. not enough free memory next to the headline buffers
+        out["cfg5"] = {"skipped": str(e)[:200]}
+    return out
+
+
+def run_ours(args, rank, world, local_rank):
+    global ROWS
+    ROWS = args.rows
+    import torch
+    import torch.distributed as dist
+    from libgpuarray_b200 import api
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = api.Context(local_rank, kernel_cache=os.path.join(ROOT, ".kernel_cache"))
+    stream = torch.cuda.ExternalStream(ctx.stream, device=local_rank)
+    peak, peak_kind = measured_peak()
+
+    # ---- data: host slab in pinned memory, device copy for the resident run
+    host = torch.empty((ROWS, COLS), dtype=torch.float32, pin_memory=True)
+    host.numpy()[...] = make_logits(rank)
+    gx = api.GpuArray.empty(ctx, (ROWS, COLS), np.float32)
+    gx.write_raw(host.data_ptr(), host.numel() * 4)
+    gmax = api.GpuArray.empty(ctx, (ROWS,), np.float32)
+    garg = api.GpuArray.empty(ctx, (ROWS,), np.uint64)
+    hmax = torch.empty(ROWS, dtype=torch.float32, pin_memory=True)
+    harg = torch.empty(ROWS, dtype=torch.int64, pin_memory=True)
+    ctx.sync()
+    step_bytes = ROWS * COLS * 4 + ROWS * 12
+
+    def step():
+        api.maxandargmax(gmax, garg, gx, [1])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        ctx.sync()
+        torch.cuda.synchronize()
+
+    # ---- resident run
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = api.lib().gpuarray_b200_launch_count()
+    timer = device_timer(torch, stream)
+    barrier()
+    a, b = timer.span()
+    a.record(stream)
+    for _ in range(args.steps):
+        step()
+    b.record(stream)
+    barrier()
+    ms = timer.total_ms()
+    launches = api.lib().gpuarray_b200_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+
+    # quick self-check of the timed result on a few rows (host recomputation)
+    vm, am = gmax.to_numpy(), garg.to_numpy()
+    xs = host.numpy()[:64]
+    assert (vm[:64] == xs.max(1)).all() and (am[:64] == xs.argmax(1)).all(), "result check failed"
+
+    # ---- end-to-end run: host input, host output, every step
+    def e2e_step():
+        gx.write_raw(host.data_ptr(), host.numel() * 4)
+        api.maxandargmax(gmax, garg, gx, [1])
+        gmax.read_raw(hmax.data_ptr(), ROWS * 4)
+        garg.read_raw(harg.data_ptr(), ROWS * 8)
+
+    e2e_steps = max(2, min(args.steps, 10))
+    e2e_ms = float("nan")
+    if not args.no_e2e:
+        e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    ms_per_step = ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+    per_gpu = value / world
+    e2e_value = world * step_bytes / (e2e_ms / e2e_steps * 1e-3) / 1e9
+
+    # ---- CPU baseline (bounded sample, rank 0, N=1 only)
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        from oracle import oracle as O
+        sample_rows = min(4096, ROWS)
+        xs = host.numpy()[:sample_rows]
+        O.rowmaxarg_f32(xs)
+        best = 1e9
+        t_end = time.perf_counter() + 10.0
+        reps = 0
+        while time.perf_counter() < t_end and reps < 200:
+            t0 = time.perf_counter()
+            O.rowmaxarg_f32(xs)
+            best = min(best, time.perf_counter() - t0)
+            reps += 1
+        t0 = time.perf_counter()
+        xs.max(1)
+        xs.argmax(1)
+        t_np = time.perf_counter() - t0
+        sb = xs.nbytes + sample_rows * 12
+        cpu = {"value": sb / best / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+               "sample": "first %d of %d rows, best of %d passes (~10 s)" % (sample_rows, ROWS, reps),
+               "numpy_1core_GBs": sb / t_np / 1e9}
+
+    line = {
+        "metric": "maxandargmax effective HBM GB/s", "value": value, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg3 GpuReduction MAXANDARGMAX, last axis of fp32 (16384, 32000) "
+                               "logits per GPU (rows sharded, no communication)",
+                   "rows_per_gpu": ROWS,
+                   "bytes_per_step_per_gpu": step_bytes,
+                   "l2": "2.1 GB input per launch exceeds the 126 MB L2; no flush needed",
+                   "frac_of_nominal_8TBs_per_gpu": per_gpu / NOMINAL_HBM_GBS},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": ROWS * COLS * 4,
+                "d2h_bytes_per_step": ROWS * 12, "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
+                     "frac": per_gpu / peak, "peak_kind": peak_kind, "kernel": "ga_rd_rows",
+                     "traffic": TRAFFIC_BYTES_PER_LAUNCH},
+        "clocks": clocks,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    if world == 1 and not args.no_side_configs:
+        del gx
+        flush_buf = api.GpuArray.empty(ctx, (256 << 20,), np.uint8)
+
+        def flush():
+            flush_buf.memset(0)
+        try:
+            line["configs"] = side_configs(api, ctx, torch, stream, flush)
+        except Exception as e:
+            line["configs"] = {"error": str(e)[:300]}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one ga_rd_rows launch on this
+# workload, from the ncu capture summarised under profiles/ (None until taken).
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg3")
+    ap.add_argument("--no-side-configs", action="store_true")
+    ap.add_argument("--rows", type=int, default=ROWS,
+                    help="rows per GPU (smaller values are for profiler captures only)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

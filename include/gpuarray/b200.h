@@ -15,6 +15,9 @@ extern "C" {
  * gpucontext_error() gives the matching text. */
 GPUARRAY_PUBLIC int gpuarray_b200_error_code(gpucontext *ctx);
 
+/* Kernels launched by this library in the process so far (all contexts). */
+GPUARRAY_PUBLIC unsigned long long gpuarray_b200_launch_count(void);
+
 /* Compiles CUDA C++ `src` for sm_100a with the library's in-memory headers
  * ("cluda.h", the kernel templates) and NVRTC; needs no GPU. `defines` is a
  * NULL-terminated list of "-DNAME=VALUE" options or NULL; `cache_dir` (may be

@@ -245,6 +245,11 @@ void ga_modules_free(gpucontext *ctx) {
   ctx->modules = NULL;
 }
 
+static unsigned long long launch_counter = 0;
+
+/* Number of kernels this library has launched in the process so far. */
+GPUARRAY_PUBLIC unsigned long long gpuarray_b200_launch_count(void) { return launch_counter; }
+
 int ga_launch(gpucontext *ctx, const ga_function *fn, const unsigned grid[3],
               const unsigned block[3], size_t shared, void **params) {
   CUresult r;
@@ -261,6 +266,7 @@ int ga_launch(gpucontext *ctx, const ga_function *fn, const unsigned grid[3],
                              (unsigned)shared, ctx->s, params, NULL);
   ga_ctx_exit(ctx);
   if (r != CUDA_SUCCESS) return ga_err_cuda(ctx->err, "cuLaunchKernel", r);
+  launch_counter++;
   return GA_NO_ERROR;
 }
 
