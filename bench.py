@@ -16,8 +16,8 @@ host->device copy of the slab and device->host read of the results inside the
 timed region), `roofline` (dominant kernel against the measured copy peak),
 `cpu_baseline` (the C oracle port on the host cores, bounded sample), `clocks`
 (nvidia-smi samples during the timed region), `gpu_launches`, and `configs`
-(the other single-GPU workloads of the suite, each timed cold: L2 flushed
-between launches).
+(the other single-GPU workloads of the suite, each timed on data that is not
+resident in L2).
 
 `--impl reference` times the reference arm: libgpuarray's CPU path is pygpu on
 a CPU OpenCL device (pocl), which cannot run here (no OpenCL loader, no pocl,
@@ -51,7 +51,7 @@ def measured_peak():
         return 6650.0, "fallback"
 
 
-def make_logits(rank, rows=ROWS):
+def make_logits(rank, rows):
     """Seed 2; rank r draws from the r-th jumped copy of the stream."""
     bg = np.random.PCG64(2)
     rng = np.random.Generator(bg.jumped(rank) if rank else bg)
@@ -166,21 +166,25 @@ def run_reference(args, rank):
 
 # -------------------------------------------------------------------- our arm
 
-def side_configs(api, ctx, torch, stream, flush):
-    """The other single-GPU workloads, each launch timed cold (L2 flushed)."""
+def side_configs(api, ctx, torch, stream):
+    """The other single-GPU workloads, each launch timed on data that is not in
+    L2: either the working set of one launch exceeds the 126 MB L2 (cfg1, cfg4,
+    cfg5) or successive launches rotate through distinct inputs totalling more
+    than L2 (cfg2). A write-flush is deliberately not used: it leaves ~126 MB of
+    dirty lines whose write-back would be billed to the next kernel."""
     out = {}
     R, W = api.GE_READ, api.GE_WRITE
     peak, _ = measured_peak()
 
     def timed(fn, nbytes, reps=20, launches=1):
-        for _ in range(3):
-            fn()
+        """fn(i) enqueues launch number i; per-launch CUDA events on the stream."""
+        for i in range(3):
+            fn(i)
         t = device_timer(torch, stream)
-        for _ in range(reps):
-            flush()
+        for i in range(reps):
             a, b = t.span()
             a.record(stream)
-            fn()
+            fn(i)
             b.record(stream)
         ctx.sync()
         us = t.total_ms() * 1e3 / reps
@@ -204,17 +208,25 @@ def side_configs(api, ctx, torch, stream, flush):
     ga, gb, go = dev_array(ta), dev_array(tb), dev_array(to)
     ge = api.GpuElemwise(ctx, "out = a * b + 0.5f", [("a", np.float32, R), ("b", np.float32, R),
                                                       ("out", np.float32, W)], nd=1)
-    out["cfg1_elemwise_f32_contig"] = timed(lambda: ge(ga, gb, go), 3 * 4 * n)
+    out["cfg1_elemwise_f32_contig"] = timed(lambda i: ge(ga, gb, go), 3 * 4 * n)
 
     # cfg2: SUM of fp32 4096x4096 over axis 1 and axis 0
-    tx = torch.randn(4096, 4096, device="cuda", generator=g)
+    nrot = 6                                       # 6 x 64 MiB inputs > 126 MB L2
+    txs = [torch.randn(4096, 4096, device="cuda", generator=g) for _ in range(nrot)]
     ts = torch.empty(4096, device="cuda")
     torch.cuda.synchronize()
-    gx, gs = dev_array(tx), dev_array(ts)
+    gxs, gs = [dev_array(t) for t in txs], dev_array(ts)
     gsum = api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.float32)
-    out["cfg2_sum_axis1"] = timed(lambda: gsum(gs, None, gx, [1]), 4096 * 4096 * 4 + 4096 * 4)
-    out["cfg2_sum_axis0"] = timed(lambda: gsum(gs, None, gx, [0]), 4096 * 4096 * 4 + 4096 * 4,
-                                  launches=2)
+    l0 = api.lib().gpuarray_b200_launch_count()
+    gsum(gs, None, gxs[0], [1])
+    l1 = api.lib().gpuarray_b200_launch_count()
+    gsum(gs, None, gxs[0], [0])
+    l2 = api.lib().gpuarray_b200_launch_count()
+    out["cfg2_sum_axis1"] = timed(lambda i: gsum(gs, None, gxs[i % nrot], [1]),
+                                  4096 * 4096 * 4 + 4096 * 4, launches=int(l1 - l0))
+    out["cfg2_sum_axis0"] = timed(lambda i: gsum(gs, None, gxs[i % nrot], [0]),
+                                  4096 * 4096 * 4 + 4096 * 4, launches=int(l2 - l1))
+    del txs, gxs
 
     # cfg4: y = max(x + bias, 0), x an NHWC buffer viewed as NCHW, fp16
     tbuf = torch.randn(64, 56, 56, 256, device="cuda", generator=g).half()
@@ -228,8 +240,8 @@ def side_configs(api, ctx, torch, stream, flush):
                           [("x", np.float16, R), ("bias", np.float16, R), ("y", np.float16, W)],
                           nd=4, convert_f16=True)
     out["cfg4_f16_bias_relu_nhwc_to_nchw"] = timed(
-        lambda: ge4(gxv, gbias, gy, flags=api.GE_BROADCAST), 2 * tbuf.numel() * 2 + 512)
-    del ta, tb, to, tx, tbuf, ty
+        lambda i: ge4(gxv, gbias, gy, flags=api.GE_BROADCAST), 2 * tbuf.numel() * 2 + 512)
+    del ta, tb, to, tbuf, ty
 
     # cfg5: fp64 (2048, 1024, 1024) = 16 GiB: SUM over everything, MIN and MAX over (0, 2)
     try:
@@ -243,11 +255,11 @@ def side_configs(api, ctx, torch, stream, flush):
         r_min = api.GpuReduction(ctx, api.GA_REDUCE_MIN, np.float64)
         r_max = api.GpuReduction(ctx, api.GA_REDUCE_MAX, np.float64)
         nb = t5.numel() * 8
-        out["cfg5_f64_sum_all"] = timed(lambda: r_sum(g1, None, g5, [0, 1, 2]), nb + 8, reps=5,
+        out["cfg5_f64_sum_all"] = timed(lambda i: r_sum(g1, None, g5, [0, 1, 2]), nb + 8, reps=5,
                                         launches=2)
-        out["cfg5_f64_min_axes02"] = timed(lambda: r_min(gk, None, g5, [0, 2]), nb + 8192, reps=5,
+        out["cfg5_f64_min_axes02"] = timed(lambda i: r_min(gk, None, g5, [0, 2]), nb + 8192, reps=5,
                                            launches=2)
-        out["cfg5_f64_max_axes02"] = timed(lambda: r_max(gk, None, g5, [0, 2]), nb + 8192, reps=5,
+        out["cfg5_f64_max_axes02"] = timed(lambda i: r_max(gk, None, g5, [0, 2]), nb + 8192, reps=5,
                                            launches=2)
         del t5
     except Exception as e:       # e.g. not enough free memory next to the headline buffers
@@ -273,7 +285,7 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- data: host slab in pinned memory, device copy for the resident run
     host = torch.empty((ROWS, COLS), dtype=torch.float32, pin_memory=True)
-    host.numpy()[...] = make_logits(rank)
+    host.numpy()[...] = make_logits(rank, ROWS)
     gx = api.GpuArray.empty(ctx, (ROWS, COLS), np.float32)
     gx.write_raw(host.data_ptr(), host.numel() * 4)
     gmax = api.GpuArray.empty(ctx, (ROWS,), np.float32)
@@ -396,12 +408,8 @@ def run_ours(args, rank, world, local_rank):
         line["cpu_baseline"] = cpu
     if world == 1 and not args.no_side_configs:
         del gx
-        flush_buf = api.GpuArray.empty(ctx, (256 << 20,), np.uint8)
-
-        def flush():
-            flush_buf.memset(0)
         try:
-            line["configs"] = side_configs(api, ctx, torch, stream, flush)
+            line["configs"] = side_configs(api, ctx, torch, stream)
         except Exception as e:
             line["configs"] = {"error": str(e)[:300]}
     print(json.dumps(line))

@@ -39,10 +39,10 @@ GPUARRAY_PUBLIC char *gpuarray_b200_elemwise_source(const char *preamble, const 
 
 /* The kernel source GpuReduction would compile for one variant: `shape`
  * 0 rows, 1 cols, 2 general; `vec` elements per load; `tpo` threads per
- * output (general); `stage2` non-zero for the pass over partial results.
- * malloc'ed; the caller frees. */
+ * output (general); `group` threads sharing a work item (rows: 32 or 256,
+ * 0 = default). malloc'ed; the caller frees. */
 GPUARRAY_PUBLIC char *gpuarray_b200_reduction_source(int op, int src_tc, int dst_tc, int shape,
-                                                     int vec, int idx64, int tpo, int stage2);
+                                                     int vec, int idx64, int tpo, int group);
 
 #ifdef __cplusplus
 }

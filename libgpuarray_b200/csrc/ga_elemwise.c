@@ -26,7 +26,7 @@ typedef struct ew_variant {
   unsigned int nd;
   int idx32;
   unsigned long long modes; /* 2 bits per array */
-  int tp, tq;            /* transpose: tile axes */
+  int tp, tq, pwi;       /* transpose: tile edges, P positions per thread */
   ga_function fn;
   struct ew_variant *next;
 } ew_variant;
@@ -101,7 +101,9 @@ static void gen_prologue(const GpuElemwise *ge, ga_strb *sb, const ew_variant *v
                  "#define GA_EW_NARR %u\n",
                  v->ept, v->unroll, GA_EW_THREADS, v->idx32 ? "unsigned int" : "size_t",
                  v->idx32, v->nd ? v->nd : 1, ge->narray ? ge->narray : 1);
-  if (v->kind == 2) ga_strb_printf(sb, "#define GA_EW_TP %d\n#define GA_EW_TQ %d\n", v->tp, v->tq);
+  if (v->kind == 2)
+    ga_strb_printf(sb, "#define GA_EW_TP %d\n#define GA_EW_TQ %d\n#define GA_EW_PWI %d\n", v->tp,
+                   v->tq, v->pwi > 0 ? v->pwi : 1);
 
   /* The expression sees each argument as a scalar variable of its own name. */
   ga_strb_puts(sb, "static __device__ __forceinline__ void ga_ew_apply(");
@@ -140,7 +142,7 @@ static ew_variant *get_variant(GpuElemwise *ge, const ew_variant *want, int *err
   for (v = ge->variants; v != NULL; v = v->next)
     if (v->kind == want->kind && v->ept == want->ept && v->unroll == want->unroll &&
         v->nd == want->nd && v->idx32 == want->idx32 && v->modes == want->modes &&
-        v->tp == want->tp && v->tq == want->tq)
+        v->tp == want->tp && v->tq == want->tq && v->pwi == want->pwi)
       return v;
   v = malloc(sizeof(*v));
   if (v == NULL) {
@@ -197,6 +199,11 @@ GPUARRAY_PUBLIC char *gpuarray_b200_elemwise_source(const char *preamble, const 
   v.modes = modes;
   v.tp = tp;
   v.tq = tq;
+  v.pwi = 1;
+  for (i = 0; i < n; i++) {
+    size_t es = gpuarray_get_elsize(args[i].typecode);
+    if (is_array(&args[i]) && es < 4 && (int)(4 / es) > v.pwi) v.pwi = (int)(4 / es);
+  }
   return gen_source(&ge, &v);
 }
 
@@ -625,22 +632,54 @@ static int call_transpose(GpuElemwise *ge, void **args, size_t n, unsigned int n
     want.modes |= mode << (2 * k);
     k++;
   }
-  /* tile edge: 64 unless the staged tiles would not fit in 48 KiB */
-  for (tile = 64; tile >= 32; tile /= 2) {
-    smem = 0;
-    for (i = 0, k = 0; i < ge->n; i++) {
-      if (!is_array(&ge->args[i])) continue;
-      if (((want.modes >> (2 * k)) & 3) == 3) {
-        size_t es = gpuarray_get_elsize(ge->args[i].typecode);
-        smem += (size_t)tile * ((size_t)tile + (es >= 4 ? 1 : 4 / es)) * es;
-      }
-      k++;
+  /* P positions per thread: one 32-bit shared-memory word of the narrowest
+   * staged type */
+  want.pwi = 1;
+  for (i = 0, k = 0; i < ge->n; i++) {
+    if (!is_array(&ge->args[i])) continue;
+    if (((want.modes >> (2 * k)) & 3) == 3) {
+      size_t es = gpuarray_get_elsize(ge->args[i].typecode);
+      if (es < 4 && (int)(4 / es) > want.pwi) want.pwi = (int)(4 / es);
     }
-    if (smem <= 46 * 1024) break;
+    k++;
   }
-  if (tile < 32 || tile % want.ept != 0) return GA_NO_ERROR;
-  want.tp = tile;
-  want.tq = tile;
+  /* Tile: as wide along P as the contiguous extent allows (up to 256), so
+   * the staged reads are long contiguous bursts; 64 along Q; shrink until the
+   * staged tiles fit the 48 KiB of static shared memory. */
+  {
+    int tp = 32, tq = 64;
+    while (tp < 256 && (size_t)tp < ge->dims[pdim_ax]) tp *= 2;
+    for (;;) {
+      smem = 0;
+      for (i = 0, k = 0; i < ge->n; i++) {
+        if (!is_array(&ge->args[i])) continue;
+        if (((want.modes >> (2 * k)) & 3) == 3) {
+          size_t es = gpuarray_get_elsize(ge->args[i].typecode);
+          size_t wsz = es > 4 ? 8 : 4, pw = es < 4 ? 4 / es : 1;
+          smem += (size_t)tq * ((size_t)tp / pw + 1) * wsz;
+        }
+        k++;
+      }
+      if (smem <= 40 * 1024) break;
+      if (tp > 32) tp /= 2;
+      else if (tq > 32) tq /= 2;
+      else break;
+    }
+    tile = smem <= 46 * 1024 ? 64 : 0;
+    want.tp = tp;
+    want.tq = tq;
+  }
+  if (tile == 0 || want.tq % want.ept != 0 || want.tp % want.pwi != 0) return GA_NO_ERROR;
+  {
+    /* experiment knob: GPUARRAY_B200_EWT="tp,tq" (tq a multiple of the chunk) */
+    const char *env = getenv("GPUARRAY_B200_EWT");
+    int etp = 0, etq = 0;
+    if (env != NULL && sscanf(env, "%d,%d", &etp, &etq) == 2 && etp >= 8 && etq >= want.ept &&
+        etq % want.ept == 0) {
+      want.tp = etp;
+      want.tq = etq;
+    }
+  }
   v = get_variant(ge, &want, &err);
   *handled = 1;
   if (v == NULL) return err;
@@ -650,8 +689,8 @@ static int call_transpose(GpuElemwise *ge, void **args, size_t n, unsigned int n
   if (ensure_blob(ge, words) != 0) return ga_err_sys(ctx->err, "realloc");
   w = ge->blob;
   memset(w, 0, words * sizeof(*w));
-  tiles_p = (ge->dims[pdim_ax] + (size_t)tile - 1) / (size_t)tile;
-  tiles_q = (ge->dims[q] + (size_t)tile - 1) / (size_t)tile;
+  tiles_p = (ge->dims[pdim_ax] + (size_t)want.tp - 1) / (size_t)want.tp;
+  tiles_q = (ge->dims[q] + (size_t)want.tq - 1) / (size_t)want.tq;
   nouter = 1;
   for (j = 0, k = 0; j < nd; j++) {
     if (j == pdim_ax || j == q) continue;

@@ -25,7 +25,7 @@
 enum { SHAPE_ROWS = 0, SHAPE_COLS = 1, SHAPE_GENERAL = 2 };
 
 typedef struct rd_variant {
-  int shape, vec, idx64, tpo, stage2, dst_tc, write_val, write_idx;
+  int shape, vec, idx64, tpo, dst_tc, write_val, write_idx, group, flat;
   ga_function fn;
   struct rd_variant *next;
 } rd_variant;
@@ -36,8 +36,10 @@ struct _GpuReduction {
   int src_tc;
   int kind;              /* 0 accumulate, 1 (value, index) pairs */
   rd_variant *variants;
-  gpudata *scratch;      /* partials of two-pass reductions */
+  gpudata *scratch;      /* partial results of split reductions */
   size_t scratch_sz;
+  gpudata *tickets;      /* arrival counters, zero between launches */
+  size_t tickets_sz;
 };
 
 /* Normalised problem; field order matches struct ga__rd_layout. */
@@ -49,6 +51,7 @@ typedef struct rd_layout {
   long long rsrc[RD_MAXD];
   unsigned long long rmul[RD_MAXD];
   unsigned long long splits, inner, seg, nseg, units, tiles;
+  unsigned int dv[4];
 } rd_layout;
 
 static int op_is_pair(ga_reduce_op op) {
@@ -134,11 +137,12 @@ static char *gen_source(const GpuReduction *gr, const rd_variant *v) {
                  map, combine, ident, op_is_min(gr->op) ? "((b) < (a))" : "((b) > (a))");
   ga_strb_printf(&sb, "#define GA_RD_KIND %d\n#define GA_RD_ISFLOAT %d\n#define GA_RD_WRITE_VAL %d\n"
                       "#define GA_RD_WRITE_IDX %d\n#define GA_RD_IDX_T %s\n#define GA_RD_VEC %d\n"
-                      "#define GA_RD_THREADS %d\n#define GA_RD_TPO %d\n#define GA_RD_STAGE2 %d\n"
-                      "#define GA_RD_BY %d\n#define %s\n#include \"ga_reduce.cuh\"\n",
+                      "#define GA_RD_THREADS %d\n#define GA_RD_TPO %d\n"
+                      "#define GA_RD_BY %d\n#define GA_RD_GROUP %d\n#define GA_RD_FLAT %d\n#define %s\n"
+                      "#include \"ga_reduce.cuh\"\n",
                  gr->kind, tc_is_float(gr->src_tc), v->write_val, v->write_idx,
                  v->idx64 ? "unsigned long long" : "unsigned int", v->vec, RD_THREADS, v->tpo,
-                 v->stage2, RD_BY,
+                 RD_BY, v->group ? v->group : RD_THREADS, v->flat,
                  v->shape == SHAPE_ROWS   ? "GA_RD_BUILD_ROWS"
                  : v->shape == SHAPE_COLS ? "GA_RD_BUILD_COLS"
                                           : "GA_RD_BUILD_GENERAL");
@@ -156,8 +160,9 @@ static rd_variant *get_variant(GpuReduction *gr, const rd_variant *want, int *er
   char *src, *listing = NULL;
   for (v = gr->variants; v != NULL; v = v->next)
     if (v->shape == want->shape && v->vec == want->vec && v->idx64 == want->idx64 &&
-        v->tpo == want->tpo && v->stage2 == want->stage2 && v->dst_tc == want->dst_tc &&
-        v->write_val == want->write_val && v->write_idx == want->write_idx)
+        v->tpo == want->tpo && v->dst_tc == want->dst_tc &&
+        v->write_val == want->write_val && v->write_idx == want->write_idx &&
+        v->group == want->group && v->flat == want->flat)
       return v;
   v = malloc(sizeof(*v));
   if (v == NULL) {
@@ -189,7 +194,7 @@ static rd_variant *get_variant(GpuReduction *gr, const rd_variant *want, int *er
 
 /* Test hook: source of one reduction kernel variant; caller frees. */
 GPUARRAY_PUBLIC char *gpuarray_b200_reduction_source(int op, int src_tc, int dst_tc, int shape,
-                                                     int vec, int idx64, int tpo, int stage2) {
+                                                     int vec, int idx64, int tpo, int group) {
   GpuReduction gr;
   rd_variant v;
   memset(&gr, 0, sizeof(gr));
@@ -201,7 +206,7 @@ GPUARRAY_PUBLIC char *gpuarray_b200_reduction_source(int op, int src_tc, int dst
   v.vec = vec;
   v.idx64 = idx64;
   v.tpo = tpo;
-  v.stage2 = stage2;
+  v.group = group;
   v.dst_tc = dst_tc;
   v.write_val = op_writes_val(gr.op);
   v.write_idx = op_writes_idx(gr.op);
@@ -245,6 +250,7 @@ void GpuReduction_free(GpuReduction *gr) {
     free(v);
   }
   if (gr->scratch != NULL) gpudata_release(gr->scratch);
+  if (gr->tickets != NULL) gpudata_release(gr->tickets);
   free(gr);
   ga_ctx_unref(ctx);
 }
@@ -376,15 +382,38 @@ static int normalise(const GpuReduction *gr, rd_layout *L, const GpuArray *d0, c
 
 /* -------------------------------------------------------------------- call */
 
-static int ensure_scratch(GpuReduction *gr, size_t bytes) {
+static int ensure_scratch(GpuReduction *gr, size_t bytes, size_t ticket_bytes) {
   int err = GA_NO_ERROR;
-  if (bytes <= gr->scratch_sz) return GA_NO_ERROR;
-  if (gr->scratch != NULL) gpudata_release(gr->scratch);
-  gr->scratch_sz = 0;
-  gr->scratch = gpudata_alloc(gr->ctx, bytes, NULL, 0, &err);
-  if (gr->scratch == NULL) return err;
-  gr->scratch_sz = bytes;
+  if (bytes > gr->scratch_sz) {
+    if (gr->scratch != NULL) gpudata_release(gr->scratch);
+    gr->scratch_sz = 0;
+    gr->scratch = gpudata_alloc(gr->ctx, bytes, NULL, 0, &err);
+    if (gr->scratch == NULL) return err;
+    gr->scratch_sz = bytes;
+  }
+  if (ticket_bytes > gr->tickets_sz) {
+    /* counters start at zero and every launch hands them back at zero */
+    if (gr->tickets != NULL) gpudata_release(gr->tickets);
+    gr->tickets_sz = 0;
+    if (ticket_bytes < 4096) ticket_bytes = 4096;
+    gr->tickets = gpudata_alloc(gr->ctx, ticket_bytes, NULL, 0, &err);
+    if (gr->tickets == NULL) return err;
+    err = gpudata_memset(gr->tickets, 0, 0);
+    if (err != GA_NO_ERROR) return err;
+    gr->tickets_sz = ticket_bytes;
+  }
   return GA_NO_ERROR;
+}
+
+static void make_div32(unsigned int d, unsigned int out[4]) {
+  unsigned int l = 0;
+  unsigned long long m;
+  while (l < 32 && ((unsigned long long)1 << l) < d) l++;
+  m = ((((unsigned long long)1 << l) - d) << 32) / d + 1;
+  out[0] = d;
+  out[1] = (unsigned int)m;
+  out[2] = l < 1 ? l : 1;
+  out[3] = l > 0 ? l - 1 : 0;
 }
 
 static int all_multiple(const long long *v, unsigned n, long long m) {
@@ -394,13 +423,19 @@ static int all_multiple(const long long *v, unsigned n, long long m) {
   return 1;
 }
 
-/* Tuning for experiments: GPUARRAY_B200_RD="ctas_per_sm,seg_vectors". */
-static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs) {
+/* Tuning for experiments: GPUARRAY_B200_RD="ctas_per_sm,seg_vectors,warp_item_bytes". */
+static unsigned rd_cols_ctas_per_sm = 16;
+
+static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_bytes) {
   static int parsed = 0;
-  static unsigned t_ctas = 32, t_seg = 8;
+  static unsigned t_ctas = 32, t_seg = 16, t_warp = 0x7fffffff;
+  *warp_bytes = t_warp;
   if (!parsed) {
     const char *env = getenv("GPUARRAY_B200_RD");
-    if (env != NULL) sscanf(env, "%u,%u", &t_ctas, &t_seg);
+    if (env != NULL)
+      sscanf(env, "%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm);
+    if (rd_cols_ctas_per_sm == 0) rd_cols_ctas_per_sm = 16;
+    *warp_bytes = t_warp;
     if (t_ctas == 0) t_ctas = 32;
     if (t_seg == 0) t_seg = 8;
     parsed = 1;
@@ -415,13 +450,13 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
   gpucontext *ctx;
   unsigned char red[64];
   rd_layout L;
-  rd_variant want, *v1, *v2 = NULL;
-  unsigned i, ndd, ctas_per_sm, seg_vecs;
+  rd_variant want, *v1;
+  unsigned i, ndd, ctas_per_sm, seg_vecs, cta_min_vecs;
   unsigned grid[3] = {1, 1, 1}, block[3] = {RD_THREADS, 1, 1};
   size_t elsize, target;
   int err = GA_NO_ERROR, need_val, need_idx;
-  CUdeviceptr p_src, p_d0 = 0, p_d1 = 0, p_val = 0, p_idx = 0;
-  void *params[6];
+  CUdeviceptr p_src, p_d0 = 0, p_d1 = 0, p_val = 0, p_idx = 0, p_tic = 0;
+  void *params[7];
   (void)flags;
 
   if (gr == NULL) return GA_INVALID_ERROR;
@@ -483,7 +518,7 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
   p_src = s0->data->ptr + s0->offset;
   if (d0 != NULL) p_d0 = d0->data->ptr + d0->offset;
   if (d1 != NULL) p_d1 = d1->data->ptr + d1->offset;
-  rd_tuning(&ctas_per_sm, &seg_vecs);
+  rd_tuning(&ctas_per_sm, &seg_vecs, &cta_min_vecs);
   target = (size_t)ctx->num_sms * ctas_per_sm;
 
   memset(&want, 0, sizeof(want));
@@ -505,18 +540,51 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
         all_multiple(L.rsrc, (unsigned)L.nr - 1, 16))
       want.vec = (int)vec;
     L.inner = L.rdim[L.nr - 1];
-    L.seg = (unsigned long long)RD_THREADS * vec * seg_vecs;
-    L.nseg = (L.inner + L.seg - 1) / L.seg;
-    L.units = rows_outer * L.nseg;
-    if (L.nf_total < target / 4) {
-      unsigned long long s = (target + L.nf_total - 1) / L.nf_total;
-      if (s > L.units) s = L.units;
-      if (s > 65535) s = 65535;
-      L.splits = s ? s : 1;
-    }
     {
-      unsigned long long nwork = L.nf_total * L.splits;
-      grid[0] = nwork > 0x7fffffffULL ? 0x7fffffffu : (unsigned)nwork;
+      /* vectors per contiguous run decide who shares a work item: a CTA for
+       * long runs, a warp for runs of a few KiB; tiny runs are flattened */
+      unsigned long long nvrow = L.inner / (unsigned)want.vec, groups_target, nwork, blocks, share;
+      unsigned gpb;
+      /* few outputs with long runs: whole CTAs, which also keeps the number of
+       * partial results small; otherwise a warp per work item */
+      want.group = (nvrow >= cta_min_vecs ||
+                    (nvrow >= 2048 && L.nf_total < (unsigned long long)ctx->num_sms)) ? RD_THREADS : 32;
+      want.flat = nvrow < 64;
+      gpb = RD_THREADS / (unsigned)want.group;
+      /* enough independent groups keep HBM busy (each has ~8 128-bit loads per
+       * thread in flight); below that, split the reduced extent */
+      groups_target = (unsigned long long)target * gpb;
+      L.seg = L.inner;
+      L.nseg = 1;
+      L.units = rows_outer;
+      if (L.nf_total < (unsigned long long)ctx->num_sms * (want.group == 32 ? 16 : 4)) {
+        unsigned long long s;
+        if (!want.flat) {
+          unsigned long long seg = (unsigned long long)want.group * vec * seg_vecs;
+          if (seg < L.inner) {
+            L.seg = seg;
+            L.nseg = (L.inner + seg - 1) / seg;
+            L.units = rows_outer * L.nseg;
+          }
+        }
+        s = (groups_target + L.nf_total - 1) / L.nf_total;
+        if (s > L.units) s = L.units;
+        if (s > 1u << 20) s = 1u << 20;
+        L.splits = s ? s : 1;
+      }
+      if (L.seg >= 0xffffffffULL) {
+        /* a single run longer than 32-bit indexing: cut it even without splitting */
+        L.seg = (unsigned long long)want.group * vec * seg_vecs * 1024;
+        L.nseg = (L.inner + L.seg - 1) / L.seg;
+        L.units = rows_outer * L.nseg;
+      }
+      make_div32((unsigned int)(nvrow ? nvrow : 1), L.dv);
+      share = (L.units / L.splits + 1) * (nvrow + 1);
+      if (want.flat && share >= 0xffffffffULL)
+        return ga_err_set(ctx->err, GA_XLARGE_ERROR, "Reduction share exceeds 32-bit indexing");
+      nwork = L.nf_total * L.splits;
+      blocks = (nwork + gpb - 1) / gpb;
+      grid[0] = blocks > 0x7fffffffULL ? 0x7fffffffu : (unsigned)blocks;
     }
   } else if (L.nr_total > 0 && L.nf >= 1 && L.fsrc[L.nf - 1] == (long long)elsize &&
              L.fdim[L.nf - 1] >= 16) {
@@ -534,10 +602,11 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
     L.tiles = (L.inner + 32ULL * vec - 1) / (32ULL * vec);
     ko = L.nf_total / L.inner;
     nwork = ko * L.tiles;
-    s = (target / 2 + nwork - 1) / nwork;
+    s = ((unsigned long long)ctx->num_sms * rd_cols_ctas_per_sm + nwork - 1) / nwork;
     if (s > (L.nr_total + RD_BY * 8 - 1) / (RD_BY * 8)) s = (L.nr_total + RD_BY * 8 - 1) / (RD_BY * 8);
     if (s > 1024) s = 1024;
     L.splits = s ? s : 1;
+    L.units = nwork; /* tickets: one per column tile */
     grid[0] = nwork > 0x7fffffffULL ? 0x7fffffffu : (unsigned)nwork;
     grid[1] = (unsigned)L.splits;
     block[0] = 32;
@@ -557,36 +626,23 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
   v1 = get_variant(gr, &want, &err);
   if (v1 == NULL) return err;
   if (L.splits > 1) {
+    /* scratch: values [outputs][splits], indices [outputs][splits], tickets */
     size_t cells = (size_t)L.splits * (size_t)L.nf_total;
-    rd_variant fin = want;
-    err = ensure_scratch(gr, cells * 16);
+    size_t nticket = want.shape == SHAPE_COLS ? (size_t)L.units : (size_t)L.nf_total;
+    err = ensure_scratch(gr, cells * 16, nticket * sizeof(unsigned int));
     if (err != GA_NO_ERROR) return err;
     p_val = gr->scratch->ptr;
     p_idx = gr->scratch->ptr + cells * 8;
-    fin.shape = SHAPE_GENERAL;
-    fin.stage2 = 1;
-    fin.vec = 1;
-    fin.tpo = L.splits >= 256 ? RD_THREADS : (L.splits >= 16 ? 32 : 1);
-    v2 = get_variant(gr, &fin, &err);
-    if (v2 == NULL) return err;
+    p_tic = gr->tickets->ptr;
   }
-
   params[0] = &L;
   params[1] = &p_src;
   params[2] = &p_d0;
   params[3] = &p_d1;
   params[4] = &p_val;
   params[5] = &p_idx;
-  err = ga_launch(ctx, &v1->fn, grid, block, 0, params);
-  if (err != GA_NO_ERROR || v2 == NULL) return err;
-  {
-    unsigned long long gpb = RD_THREADS / (unsigned)v2->tpo;
-    unsigned long long blocks = (L.nf_total + gpb - 1) / gpb;
-    unsigned g2[3] = {1, 1, 1}, b2[3] = {RD_THREADS, 1, 1};
-    if (blocks > (unsigned long long)target * 8) blocks = (unsigned long long)target * 8;
-    g2[0] = (unsigned)(blocks ? blocks : 1);
-    return ga_launch(ctx, &v2->fn, g2, b2, 0, params);
-  }
+  params[6] = &p_tic;
+  return ga_launch(ctx, &v1->fn, grid, block, 0, params);
 }
 
 /* ------------------------------------------------- GpuArray_maxandargmax */

@@ -18,8 +18,9 @@
 #define GA_RD_VEC 4
 #define GA_RD_THREADS 256
 #define GA_RD_TPO 32
-#define GA_RD_STAGE2 1
 #define GA_RD_BY 8
+#define GA_RD_FLAT 0
+#define GA_RD_GROUP 256
 #define GA_RD_BUILD_ROWS
 #define GA_RD_BUILD_GENERAL
 #include "ga_reduce.cuh"

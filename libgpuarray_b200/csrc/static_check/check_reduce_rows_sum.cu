@@ -17,8 +17,9 @@
 #define GA_RD_VEC 4
 #define GA_RD_THREADS 256
 #define GA_RD_TPO 1
-#define GA_RD_STAGE2 0
 #define GA_RD_BY 8
+#define GA_RD_FLAT 0
+#define GA_RD_GROUP 32
 #define GA_RD_BUILD_ROWS
 #define GA_RD_BUILD_COLS
 #include "ga_reduce.cuh"

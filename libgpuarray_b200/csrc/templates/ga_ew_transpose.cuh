@@ -9,16 +9,24 @@
  * orientation the expression is evaluated and outputs are written in), P the
  * dimension along which the "mode 3" inputs are contiguous. Those inputs are
  * read with 128-bit loads along P into shared memory and read back along Q,
- * so both sides of the transpose move full 128-byte lines.
+ * so both sides of the transpose move whole cache lines.
+ *
+ * Shared memory holds 32-bit words (GA_EW_PW = 4 / element size elements per
+ * word for 1- and 2-byte types) in rows of TP/PW + 1 words. The odd pitch
+ * makes both phases free of bank conflicts: staging writes the four words of
+ * a 128-bit load from 8 lanes x 4 rows, evaluation reads one word per row
+ * from 4 row-chunks x 8 word-columns. A thread evaluates the expression on
+ * GA_EW_PWI adjacent P positions x GA_EW_EPT consecutive Q positions and
+ * stores GA_EW_PWI vectors of GA_EW_EPT elements.
  *
  * Per-argument mode (last field of GA_EW_ARRAYS):
  *   3  input contiguous along P: staged through shared memory
  *   1  contiguous along Q and aligned: 128-bit access, GA_EW_EPT elements
- *   2  input with stride 0 along Q: one scalar load per thread chunk
+ *   2  input with stride 0 along Q: one scalar load per P position
  *   0  anything else: scalar access with its own strides
  *
  * Needs the definitions listed in ga_ew_contig.cuh plus GA_EW_ND (>= 2),
- * GA_EW_NARR, GA_EW_TP, GA_EW_TQ.
+ * GA_EW_NARR, GA_EW_TP, GA_EW_TQ, GA_EW_PWI (P positions per thread).
  */
 #include "ga_ew_common.cuh"
 
@@ -32,79 +40,118 @@ struct ga__ewt_layout {
   long long stro[GA_EW_NARR][GA_EWT_NOUT];      /* byte strides of the remaining dims */
 };
 
-/* shared-memory row pitch in elements: odd number of 32-bit words when possible */
-#define GA__PITCH(S) (GA_EW_TP + ((sizeof(S) >= 4) ? 1 : (4 / sizeof(S))))
+/* shared-memory word for storage type S and elements per word */
+template <int BYTES> struct ga__word { typedef unsigned int type; };
+template <> struct ga__word<8> { typedef unsigned long long type; };
+#define GA__W(S) typename ga__word<(sizeof(S) > 4 ? 8 : 4)>::type
+#define GA__WT(S) ga__word<(sizeof(S) > 4 ? 8 : 4)>::type
+#define GA__PW(S) ((sizeof(S) < 4) ? (4 / (int)sizeof(S)) : 1)
+#define GA__PITCHW(S) (GA_EW_TP / GA__PW(S) + 1)
 
 #define GA__P_ARR(k, n, S, C, R, W, M) , char *n##_p
 #define GA__P_SC(n, T) , T n##_s
-#define GA__ARG_ARR(k, n, S, C, R, W, M) n##_c[e],
+#define GA__ARG_ARR(k, n, S, C, R, W, M) n##_c[kk][e],
 #define GA__ARG_SC(n, T) n##_s,
 
 #define GA__SMEM(k, n, S, C, R, W, M) \
-  __shared__ S n##_sm[(M == 3) ? GA_EW_TQ : 1][(M == 3) ? GA__PITCH(S) : 1];
+  __shared__ GA__WT(S) n##_sm[(M == 3) ? GA_EW_TQ : 1][(M == 3) ? GA__PITCHW(S) : 1];
 
 #define GA__BASE(k, n, S, C, R, W, M) long long n##_base = 0;
 #define GA__BASE_STEP(k, n, S, C, R, W, M) n##_base += (long long)pos * L.stro[k][d];
+#define GA__BASE_FIN(k, n, S, C, R, W, M) \
+  char *const n##_t = n##_p + n##_base + (long long)p0 * L.strp[k] + (long long)q0 * L.strq[k];
 
-/* stage a mode-3 input: vectors along P, rows along Q */
+/* stage a mode-3 input: 128-bit loads along P, one row per Q position */
 #define GA__STAGE(k, n, S, C, R, W, M)                                                        \
   if (M == 3) {                                                                               \
-    constexpr int VP = (16 / sizeof(S)) < GA_EW_TP ? (16 / sizeof(S)) : GA_EW_TP;             \
-    constexpr int PV = GA_EW_TP / VP; /* vectors per tile row */                              \
-    const char *g_ = n##_p + n##_base + (long long)p0 * L.strp[k] + (long long)q0 * L.strq[k]; \
-    const bool al_ = (((unsigned long long)g_) % (VP * sizeof(S)) == 0) &&                    \
-                     (L.strq[k] % (long long)(VP * sizeof(S)) == 0);                          \
-    for (int i_ = threadIdx.x; i_ < GA_EW_TQ * PV; i_ += GA_EW_THREADS) {                     \
-      const int q_ = i_ / PV, pv_ = (i_ - q_ * PV) * VP;                                      \
-      if ((unsigned long long)q_ < qn) {                                                      \
-        const S *src_ = reinterpret_cast<const S *>(g_ + (long long)q_ * L.strq[k]) + pv_;    \
-        if (al_ && (unsigned long long)(pv_ + VP) <= pn) {                                    \
-          const ga__pack<S, VP> t_ = *reinterpret_cast<const ga__pack<S, VP> *>(src_);        \
-          _Pragma("unroll") for (int j_ = 0; j_ < VP; j_++) n##_sm[q_][pv_ + j_] = t_.v[j_]; \
-        } else {                                                                              \
-          _Pragma("unroll") for (int j_ = 0; j_ < VP; j_++)                                   \
-            if ((unsigned long long)(pv_ + j_) < pn) n##_sm[q_][pv_ + j_] = src_[j_];         \
+    typedef GA__WT(S) W_;                                                                     \
+    constexpr int VP = 16 / (int)sizeof(S);      /* elements per 128-bit load */              \
+    constexpr int WV = 16 / (int)sizeof(W_);     /* words per 128-bit load */                 \
+    constexpr int PV = (GA_EW_TP + VP - 1) / VP; /* loads per tile row */                     \
+    const long long sq_ = L.strq[k];                                                          \
+    const bool al_ = (((unsigned long long)n##_t) % 16 == 0) && (sq_ % 16 == 0) &&            \
+                     (pn == GA_EW_TP) && (GA_EW_TP % VP == 0);                                \
+    if (al_) {                                                                                \
+      /* all loads of the thread first, then the shared-memory stores */                     \
+      constexpr int NV = (GA_EW_TQ * PV + GA_EW_THREADS - 1) / GA_EW_THREADS;                 \
+      ga__pack<W_, WV> r_[NV];                                                                \
+      _Pragma("unroll") for (int k_ = 0; k_ < NV; k_++) {                                     \
+        const int i_ = threadIdx.x + k_ * GA_EW_THREADS;                                      \
+        const int q_ = i_ / PV, v_ = i_ - q_ * PV;                                            \
+        if (i_ < GA_EW_TQ * PV && q_ < qn)                                                    \
+          r_[k_] = *reinterpret_cast<const ga__pack<W_, WV> *>(                               \
+              n##_t + (long long)q_ * sq_ + v_ * 16);                                         \
+      }                                                                                       \
+      _Pragma("unroll") for (int k_ = 0; k_ < NV; k_++) {                                     \
+        const int i_ = threadIdx.x + k_ * GA_EW_THREADS;                                      \
+        const int q_ = i_ / PV, v_ = i_ - q_ * PV;                                            \
+        if (i_ < GA_EW_TQ * PV && q_ < qn) {                                                  \
+          _Pragma("unroll") for (int j_ = 0; j_ < WV; j_++)                                   \
+            n##_sm[q_][v_ * WV + j_] = r_[k_].v[j_];                                          \
         }                                                                                     \
+      }                                                                                       \
+    } else {                                                                                  \
+      for (int i_ = threadIdx.x; i_ < GA_EW_TQ * GA_EW_TP; i_ += GA_EW_THREADS) {             \
+        const int q_ = i_ / GA_EW_TP, p_ = i_ - q_ * GA_EW_TP;                                \
+        if (q_ < qn && p_ < pn)                                                               \
+          reinterpret_cast<S *>(&n##_sm[q_][0])[p_] =                                         \
+              *reinterpret_cast<const S *>(n##_t + (long long)q_ * sq_ + p_ * (int)sizeof(S)); \
       }                                                                                       \
     }                                                                                         \
   }
 
-#define GA__DECL(k, n, S, C, R, W, M) C n##_c[GA_EW_EPT];
+#define GA__DECL(k, n, S, C, R, W, M) C n##_c[GA_EW_PWI][GA_EW_EPT];
 
 #define GA__LOAD(k, n, S, C, R, W, M)                                                         \
   if (R) {                                                                                    \
     if (M == 3) {                                                                             \
-      _Pragma("unroll") for (int e = 0; e < GA_EW_EPT; e++)                                   \
-        n##_c[e] = ga__conv<C, S>::in(n##_sm[ql + e][pl]);                                    \
+      typedef GA__WT(S) W_;                                                                   \
+      constexpr int PW = GA__PW(S);                                                           \
+      _Pragma("unroll") for (int e = 0; e < GA_EW_EPT; e++) {                                 \
+        _Pragma("unroll") for (int w_ = 0; w_ < GA_EW_PWI / PW; w_++) {                       \
+          const W_ word_ = n##_sm[ql + e][pl / PW + w_];                                      \
+          S tmp_[PW];                                                                         \
+          memcpy(tmp_, &word_, sizeof(W_));                                                   \
+          _Pragma("unroll") for (int j_ = 0; j_ < PW; j_++)                                   \
+            n##_c[w_ * PW + j_][e] = ga__conv<C, S>::in(tmp_[j_]);                            \
+        }                                                                                     \
+      }                                                                                       \
     } else {                                                                                  \
-      const char *b_ = n##_p + n##_base + (long long)(p0 + pl) * L.strp[k];                   \
-      if (M == 1) {                                                                           \
-        ga__load_run<C, S, GA_EW_EPT>(                                                        \
-            reinterpret_cast<const S *>(b_ + (long long)(q0 + ql) * (long long)sizeof(S)),    \
-            n##_c);                                                                           \
-      } else if (M == 2) {                                                                    \
-        const C t_ = ga__conv<C, S>::in(*reinterpret_cast<const S *>(b_));                    \
-        _Pragma("unroll") for (int e = 0; e < GA_EW_EPT; e++) n##_c[e] = t_;                  \
-      } else {                                                                                \
-        _Pragma("unroll") for (int e = 0; e < GA_EW_EPT; e++)                                 \
-          if ((unsigned long long)(ql + e) < qn)                                              \
-            n##_c[e] = ga__conv<C, S>::in(*reinterpret_cast<const S *>(                       \
-                b_ + (long long)(q0 + ql + e) * L.strq[k]));                                  \
+      _Pragma("unroll") for (int kk = 0; kk < GA_EW_PWI; kk++) {                              \
+        if (pl + kk < pn) {                                                                   \
+          const char *b_ = n##_t + (long long)(pl + kk) * L.strp[k];                          \
+          if (M == 1) {                                                                       \
+            ga__load_run<C, S, GA_EW_EPT>(                                                    \
+                reinterpret_cast<const S *>(b_ + ql * (int)sizeof(S)), n##_c[kk]);            \
+          } else if (M == 2) {                                                                \
+            const C t_ = ga__conv<C, S>::in(*reinterpret_cast<const S *>(b_));                \
+            _Pragma("unroll") for (int e = 0; e < GA_EW_EPT; e++) n##_c[kk][e] = t_;          \
+          } else {                                                                            \
+            _Pragma("unroll") for (int e = 0; e < GA_EW_EPT; e++)                             \
+              if (ql + e < qn)                                                                \
+                n##_c[kk][e] = ga__conv<C, S>::in(                                            \
+                    *reinterpret_cast<const S *>(b_ + (long long)(ql + e) * L.strq[k]));      \
+          }                                                                                   \
+        }                                                                                     \
       }                                                                                       \
     }                                                                                         \
   }
 
 #define GA__STORE(k, n, S, C, R, W, M)                                                        \
   if (W) {                                                                                    \
-    char *b_ = n##_p + n##_base + (long long)(p0 + pl) * L.strp[k];                           \
-    if (M == 1) {                                                                             \
-      ga__store_run<C, S, GA_EW_EPT>(                                                         \
-          reinterpret_cast<S *>(b_ + (long long)(q0 + ql) * (long long)sizeof(S)), n##_c);    \
-    } else {                                                                                  \
-      _Pragma("unroll") for (int e = 0; e < GA_EW_EPT; e++)                                   \
-        if ((unsigned long long)(ql + e) < qn)                                                \
-          *reinterpret_cast<S *>(b_ + (long long)(q0 + ql + e) * L.strq[k]) =                 \
-              ga__conv<C, S>::out(n##_c[e]);                                                  \
+    _Pragma("unroll") for (int kk = 0; kk < GA_EW_PWI; kk++) {                                \
+      if (pl + kk < pn) {                                                                     \
+        char *b_ = n##_t + (long long)(pl + kk) * L.strp[k];                                  \
+        if (M == 1) {                                                                         \
+          ga__store_run<C, S, GA_EW_EPT>(reinterpret_cast<S *>(b_ + ql * (int)sizeof(S)),     \
+                                         n##_c[kk]);                                          \
+        } else {                                                                              \
+          _Pragma("unroll") for (int e = 0; e < GA_EW_EPT; e++)                               \
+            if (ql + e < qn)                                                                  \
+              *reinterpret_cast<S *>(b_ + (long long)(ql + e) * L.strq[k]) =                  \
+                  ga__conv<C, S>::out(n##_c[kk][e]);                                          \
+        }                                                                                     \
+      }                                                                                       \
     }                                                                                         \
   }
 
@@ -113,7 +160,9 @@ ga_ew_transpose(const __grid_constant__ ga__ewt_layout L
                 GA_EW_ARRAYS(GA__P_ARR) GA_EW_SCALARS(GA__P_SC)) {
   GA_EW_ARRAYS(GA__SMEM)
   const unsigned long long ntiles = L.tiles_p * L.tiles_q * L.nouter;
-  constexpr int QG = GA_EW_TQ / GA_EW_EPT; /* thread chunks per tile column */
+  constexpr int QG = GA_EW_TQ / GA_EW_EPT; /* Q chunks per tile */
+  constexpr int PG = GA_EW_TP / GA_EW_PWI; /* P groups per tile */
+  constexpr int QL = QG < 4 ? QG : 4;      /* Q chunks side by side inside a warp */
 
   for (unsigned long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
     /* tile coordinates: Q tiles fastest, then P tiles, then the outer index */
@@ -121,8 +170,8 @@ ga_ew_transpose(const __grid_constant__ ga__ewt_layout L
     const unsigned long long q0 = (t - r * L.tiles_q) * GA_EW_TQ;
     unsigned long long o = r / L.tiles_p;
     const unsigned long long p0 = (r - o * L.tiles_p) * GA_EW_TP;
-    const unsigned long long pn = (L.pdim - p0 < GA_EW_TP) ? (L.pdim - p0) : GA_EW_TP;
-    const unsigned long long qn = (L.qdim - q0 < GA_EW_TQ) ? (L.qdim - q0) : GA_EW_TQ;
+    const int pn = (int)((L.pdim - p0 < GA_EW_TP) ? (L.pdim - p0) : GA_EW_TP);
+    const int qn = (int)((L.qdim - q0 < GA_EW_TQ) ? (L.qdim - q0) : GA_EW_TQ);
     GA_EW_ARRAYS(GA__BASE)
 #if GA_EW_ND > 2
 #pragma unroll
@@ -133,17 +182,23 @@ ga_ew_transpose(const __grid_constant__ ga__ewt_layout L
       GA_EW_ARRAYS(GA__BASE_STEP)
     }
 #endif
+    GA_EW_ARRAYS(GA__BASE_FIN)
     GA_EW_ARRAYS(GA__STAGE)
     __syncthreads();
-    for (int it = threadIdx.x; it < GA_EW_TP * QG; it += GA_EW_THREADS) {
-      const int pl = it / QG;
-      const int ql = (it - pl * QG) * GA_EW_EPT;
-      if ((unsigned long long)pl < pn && (unsigned long long)ql < qn) {
+    for (int it = threadIdx.x; it < PG * QG; it += GA_EW_THREADS) {
+      /* lanes: QL chunks along Q x 8 groups along P (see the header comment) */
+      const int a_ = it % QL, b_i = it / QL;
+      const int pl = (b_i % PG) * GA_EW_PWI;
+      const int ql = (a_ + QL * (b_i / PG)) * GA_EW_EPT;
+      if (pl < pn && ql < qn) {
         GA_EW_ARRAYS(GA__DECL)
         GA_EW_ARRAYS(GA__LOAD)
 #pragma unroll
-        for (int e = 0; e < GA_EW_EPT; e++)
-          ga_ew_apply(GA_EW_ARRAYS(GA__ARG_ARR) GA_EW_SCALARS(GA__ARG_SC) 0);
+        for (int kk = 0; kk < GA_EW_PWI; kk++) {
+#pragma unroll
+          for (int e = 0; e < GA_EW_EPT; e++)
+            ga_ew_apply(GA_EW_ARRAYS(GA__ARG_ARR) GA_EW_SCALARS(GA__ARG_SC) 0);
+        }
         GA_EW_ARRAYS(GA__STORE)
       }
     }

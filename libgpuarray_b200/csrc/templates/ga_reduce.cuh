@@ -6,9 +6,12 @@
  * (src/gpuarray_reduction.c:520-607), and (b) pygpu's reduk template, a block
  * per output with a shared-memory tree and a div/mod per element
  * (pygpu/reduction.py:33-134). Here the reduced extent itself is spread over
- * threads, warps, CTAs and - when there are few outputs - over several CTAs
- * whose partial results a second tiny launch combines in a fixed order, so
- * results are deterministic and no thread ever waits on another CTA.
+ * threads, warps, CTAs and - when there are few outputs - over several work
+ * groups per output. Each group publishes its partial result and takes a
+ * ticket; the group that draws the last ticket combines all partials in
+ * split order and writes the output. Nobody waits (no spinning, so nothing
+ * can hang), the combination order is fixed (results are bitwise repeatable)
+ * and the whole reduction is one launch.
  *
  *   ga_rd_rows     the innermost reduced dimension is contiguous in memory:
  *                  a CTA streams 128-bit loads along it, warp shuffles then
@@ -17,7 +20,7 @@
  *                  GA_RD_VEC adjacent outputs and walks down the reduced
  *                  extent; blockDim.y row-lanes and gridDim.y splits share it
  *   ga_rd_general  any strides: GA_RD_TPO threads per output decode each
- *                  element's offset; also the second pass over partials
+ *                  element's offset
  *
  * Operators. GA_RD_KIND 0: acc = COMBINE(acc, MAP(x)) from IDENT (sum, prod,
  * prodnz, and, or, xor, all, any). GA_RD_KIND 1: (value, flat index) pairs
@@ -36,7 +39,7 @@
  *   GA_RD_LOAD(raw) GA_RD_STORE(acc) GA_RD_MAP(x) GA_RD_COMBINE(a,b)
  *   GA_RD_IDENT GA_RD_BETTER(b,a) GA_RD_KIND GA_RD_ISFLOAT
  *   GA_RD_WRITE_VAL GA_RD_WRITE_IDX GA_RD_IDX_T GA_RD_VEC GA_RD_THREADS
- *   GA_RD_TPO GA_RD_STAGE2 GA_RD_BY
+ *   GA_RD_TPO GA_RD_BY GA_RD_GROUP (rows: 32 or GA_RD_THREADS) GA_RD_FLAT
  */
 #include "cluda.h"
 
@@ -62,7 +65,14 @@ struct ga__rd_layout {
   ga__u64 nseg;              /* rows: units per run */
   ga__u64 units;             /* rows: units per output */
   ga__u64 tiles;             /* cols: column tiles per contiguous kept run */
+  unsigned int dv[4];        /* rows: divisor, multiplier, shifts for idx / (inner / VEC) */
 };
+
+/* exact n / d for 32-bit n with the constants the host derived from d */
+static __device__ __forceinline__ unsigned int ga__rd_divide(unsigned int n, const unsigned int *k) {
+  const unsigned int t = __umulhi(k[1], n);
+  return (t + ((n - t) >> k[2])) >> k[3];
+}
 
 struct ga__state {
   GA_RD_ACC_T v;
@@ -183,13 +193,60 @@ static __device__ __forceinline__ void ga__emit(const ga__rd_layout &L, const ch
 #endif
 }
 
+template <typename T>
+static __device__ __forceinline__ T ga__ldcg(const T *p) {
+  T r;
+  if (sizeof(T) == 1) {
+    const unsigned char w = __ldcg(reinterpret_cast<const unsigned char *>(p));
+    memcpy(&r, &w, 1);
+  } else if (sizeof(T) == 2) {
+    const unsigned short w = __ldcg(reinterpret_cast<const unsigned short *>(p));
+    memcpy(&r, &w, 2);
+  } else if (sizeof(T) == 4) {
+    const unsigned int w = __ldcg(reinterpret_cast<const unsigned int *>(p));
+    memcpy(&r, &w, 4);
+  } else {
+    const unsigned long long w = __ldcg(reinterpret_cast<const unsigned long long *>(p));
+    memcpy(&r, &w, 8);
+  }
+  return r;
+}
+
 static __device__ __forceinline__ void ga__put_partial(const ga__rd_layout &L, GA_RD_ACC_T *pval,
                                                        GA_RD_IDX_T *pidx, const ga__u64 split,
                                                        const ga__u64 o, const ga__state &s) {
-  pval[split * L.nf_total + o] = s.v;
+  pval[o * L.splits + split] = s.v; /* [output][split] */
 #if GA_RD_KIND == 1
-  pidx[split * L.nf_total + o] = s.i;
+  pidx[o * L.splits + split] = s.i;
 #endif
+}
+
+/* partial `split` of output `o`, read from L2 (ld.global.cg): other CTAs wrote
+ * it, and the ticket's fence/atomic pair ordered those writes before us */
+static __device__ __forceinline__ ga__state ga__get_partial(const ga__rd_layout &L,
+                                                            const GA_RD_ACC_T *pval,
+                                                            const GA_RD_IDX_T *pidx,
+                                                            const ga__u64 split, const ga__u64 o) {
+  ga__state t;
+  t.v = ga__ldcg(&pval[o * L.splits + split]);
+#if GA_RD_KIND == 1
+  t.i = ga__ldcg(&pidx[o * L.splits + split]);
+#endif
+  return t;
+}
+
+/* One thread of a group calls this after the group's partial is stored.
+ * Returns true for the group that arrived last at `ticket`; that group then
+ * owns every partial of the output. The counter is left at zero for the next
+ * launch. */
+static __device__ __forceinline__ bool ga__take_ticket(unsigned int *ticket,
+                                                       const unsigned int nsplits) {
+  __threadfence();
+  const unsigned int seen = atomicAdd(ticket, 1u);
+  if (seen + 1u != nsplits) return false;
+  *ticket = 0u;
+  __threadfence();
+  return true;
 }
 
 template <int N>
@@ -199,65 +256,167 @@ struct alignas((sizeof(GA_RD_SRC_T) * N >= 16) ? 16 : sizeof(GA_RD_SRC_T) * N) g
 
 /* ------------------------------------------------------------------ rows */
 #if defined(GA_RD_BUILD_ROWS)
+/* byte offset and flat-index base of reduced "row" r (all reduced dims but the
+ * contiguous one), nro = number of those dims */
+static __device__ __forceinline__ void ga__row_decode(const ga__rd_layout &L, const int nro,
+                                                      ga__u64 r, ga__i64 &roff,
+                                                      GA_RD_IDX_T &fbase) {
+  if (nro == 1) {
+    roff = (ga__i64)r * L.rsrc[0];
+    fbase = (GA_RD_IDX_T)r * (GA_RD_IDX_T)L.rmul[0];
+    return;
+  }
+  roff = 0;
+  fbase = 0;
+  for (int d = nro - 1; d >= 0; d--) {
+    const ga__u64 q = r / L.rdim[d], c = r - q * L.rdim[d];
+    r = q;
+    roff += (ga__i64)c * L.rsrc[d];
+    fbase += (GA_RD_IDX_T)c * (GA_RD_IDX_T)L.rmul[d];
+  }
+}
+
+/* GA_RD_GROUP threads (a warp or the whole CTA) share one work item, i.e. one
+ * (output, split) pair, and walk its units (a unit = one contiguous run, or
+ * one segment of a long run) one after the other; inside a unit each thread
+ * strides 128-bit loads, so the inner loop is a pointer, a counter and the
+ * operator. The host picks the group so that a thread sees several vectors
+ * per unit: a CTA for long runs, a warp for runs of a few KiB. With
+ * GA_RD_FLAT (very short runs) the (run, vector) pairs of the whole share are
+ * flattened into one index space instead, so that consecutive iterations of
+ * a thread touch different runs and their loads overlap. */
 extern "C" __global__ void __launch_bounds__(GA_RD_THREADS)
 ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, char *d1,
-           GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx) {
+           GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx, unsigned int *tickets) {
+#if GA_RD_GROUP > 32
   __shared__ ga__state sm[32];
+  __shared__ int sm_last;
+#endif
   const ga__u64 nwork = L.nf_total * L.splits;
   const int nro = (int)L.nr - 1; /* reduced dims outside the contiguous run */
   const GA_RD_IDX_T imul = (GA_RD_IDX_T)L.rmul[nro];
+  const unsigned lane = threadIdx.x % GA_RD_GROUP;
+  const ga__u64 group = ((ga__u64)blockIdx.x * GA_RD_THREADS + threadIdx.x) / GA_RD_GROUP;
+  const ga__u64 ngroups = (ga__u64)gridDim.x * (GA_RD_THREADS / GA_RD_GROUP);
+  const ga__u64 rounds = (nwork + ngroups - 1) / ngroups;
 
-  for (ga__u64 w = blockIdx.x; w < nwork; w += gridDim.x) {
-    ga__u64 o = w, split = 0;
+  for (ga__u64 it = 0; it < rounds; it++) {
+    const ga__u64 w = group + it * ngroups;
+    const bool live = w < nwork;
+    ga__u64 o = live ? w : 0, split = 0;
     if (L.splits > 1) {
-      o = w / L.splits;
-      split = w - o * L.splits;
+      const ga__u64 ww = o;
+      o = ww / L.splits;
+      split = ww - o * L.splits;
     }
-    const ga__u64 ub = split * L.units / L.splits, ue = (split + 1) * L.units / L.splits;
-    const char *obase = src + ga__foff(L, L.fsrc, o);
     ga__state st[GA_RD_VEC];
 #pragma unroll
     for (int j = 0; j < GA_RD_VEC; j++) st[j] = ga__init();
 
-    for (ga__u64 u = ub; u < ue; u++) {
-      ga__u64 r = u, g = 0;
-      if (L.nseg > 1) {
-        r = u / L.nseg;
-        g = u - r * L.nseg;
-      }
-      ga__i64 roff = 0;
-      GA_RD_IDX_T fbase = 0;
-      for (int d = nro - 1; d >= 0; d--) {
-        const ga__u64 q = r / L.rdim[d], c = r - q * L.rdim[d];
-        r = q;
-        roff += (ga__i64)c * L.rsrc[d];
-        fbase += (GA_RD_IDX_T)c * (GA_RD_IDX_T)L.rmul[d];
-      }
-      const ga__u64 e0 = g * L.seg;
-      const unsigned int len = (unsigned int)((L.inner - e0 < L.seg) ? (L.inner - e0) : L.seg);
-      const GA_RD_SRC_T *p = reinterpret_cast<const GA_RD_SRC_T *>(obase + roff) + e0;
-      fbase += (GA_RD_IDX_T)e0 * imul;
-      const unsigned int nv = len / GA_RD_VEC;
-      const ga__rd_pack<GA_RD_VEC> *pv = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(p);
-#pragma unroll 4
-      for (unsigned int i = threadIdx.x; i < nv; i += GA_RD_THREADS) {
-        const ga__rd_pack<GA_RD_VEC> t = pv[i];
+    if (live) {
+      const ga__u64 ub = split * L.units / L.splits, ue = (split + 1) * L.units / L.splits;
+      const char *obase = src + ga__foff(L, L.fsrc, o);
+#if !GA_RD_FLAT
+      for (ga__u64 u = ub; u < ue; u++) {
+        ga__u64 r = u, g = 0;
+        if (L.nseg > 1) {
+          r = u / L.nseg;
+          g = u - r * L.nseg;
+        }
+        ga__i64 roff;
+        GA_RD_IDX_T fbase;
+        ga__row_decode(L, nro, r, roff, fbase);
+        const ga__u64 e0 = g * L.seg;
+        const unsigned int len = (unsigned int)((L.inner - e0 < L.seg) ? (L.inner - e0) : L.seg);
+        const GA_RD_SRC_T *p = reinterpret_cast<const GA_RD_SRC_T *>(obase + roff) + e0;
+        fbase += (GA_RD_IDX_T)e0 * imul;
+        const unsigned int nv = len / GA_RD_VEC;
+        const ga__rd_pack<GA_RD_VEC> *pv = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(p);
+#pragma unroll 8
+        for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
+          const ga__rd_pack<GA_RD_VEC> t = pv[i];
+          const GA_RD_IDX_T f0 = fbase + (GA_RD_IDX_T)(i * GA_RD_VEC) * imul;
 #pragma unroll
-        for (int j = 0; j < GA_RD_VEC; j++)
-          ga__take(st[j], GA_RD_LOAD(t.v[j]),
-                   fbase + (GA_RD_IDX_T)(i * GA_RD_VEC + (unsigned)j) * imul);
+          for (int j = 0; j < GA_RD_VEC; j++)
+            ga__take(st[j], GA_RD_LOAD(t.v[j]), f0 + (GA_RD_IDX_T)j * imul);
+        }
+        for (unsigned int i = nv * GA_RD_VEC + lane; i < len; i += GA_RD_GROUP)
+          ga__take(st[0], GA_RD_LOAD(p[i]), fbase + (GA_RD_IDX_T)i * imul);
       }
-      for (unsigned int i = nv * GA_RD_VEC + threadIdx.x; i < len; i += GA_RD_THREADS)
-        ga__take(st[0], GA_RD_LOAD(p[i]), fbase + (GA_RD_IDX_T)i * imul);
+#else
+      {
+        const unsigned int nvrow = (unsigned int)(L.inner / GA_RD_VEC);
+        const unsigned int tail = (unsigned int)(L.inner - (ga__u64)nvrow * GA_RD_VEC);
+        const unsigned int nrows = (unsigned int)(ue - ub);
+        const unsigned int share = nrows * nvrow;
+#pragma unroll 4
+        for (unsigned int idx = lane; idx < share; idx += GA_RD_GROUP) {
+          const unsigned int ru = ga__rd_divide(idx, L.dv);
+          const unsigned int pv = idx - ru * nvrow;
+          ga__i64 roff;
+          GA_RD_IDX_T fbase;
+          ga__row_decode(L, nro, ub + ru, roff, fbase);
+          const ga__rd_pack<GA_RD_VEC> t = *reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(
+              obase + roff + (ga__i64)pv * (ga__i64)(GA_RD_VEC * sizeof(GA_RD_SRC_T)));
+#pragma unroll
+          for (int j = 0; j < GA_RD_VEC; j++)
+            ga__take(st[j], GA_RD_LOAD(t.v[j]),
+                     fbase + (GA_RD_IDX_T)(pv * GA_RD_VEC + (unsigned)j) * imul);
+        }
+        if (tail != 0) {
+          for (unsigned int idx = lane; idx < nrows * tail; idx += GA_RD_GROUP) {
+            const unsigned int ru = idx / tail;
+            const unsigned int e = nvrow * GA_RD_VEC + (idx - ru * tail);
+            ga__i64 roff;
+            GA_RD_IDX_T fbase;
+            ga__row_decode(L, nro, ub + ru, roff, fbase);
+            const GA_RD_SRC_T *p = reinterpret_cast<const GA_RD_SRC_T *>(obase + roff);
+            ga__take(st[0], GA_RD_LOAD(p[e]), fbase + (GA_RD_IDX_T)e * imul);
+          }
+        }
+      }
+#endif
     }
 #pragma unroll
     for (int j = 1; j < GA_RD_VEC; j++) ga__merge(st[0], st[j]);
+#if GA_RD_GROUP > 32
     const ga__state tot = ga__block_reduce(st[0], sm, threadIdx.x, GA_RD_THREADS);
-    if (threadIdx.x == 0) {
-      if (L.splits == 1) ga__emit(L, src, d0, d1, o, tot);
-      else ga__put_partial(L, pval, pidx, split, o, tot);
+#else
+    const ga__state tot = ga__warp_reduce(st[0]);
+#endif
+    if (L.splits == 1) {
+      if (live && lane == 0) ga__emit(L, src, d0, d1, o, tot);
+#if GA_RD_GROUP > 32
+      __syncthreads();
+#endif
+    } else {
+      /* publish, take a ticket, and let the last group of this output finish */
+      int last = 0;
+      if (live && lane == 0) {
+        ga__put_partial(L, pval, pidx, split, o, tot);
+        last = ga__take_ticket(&tickets[o], (unsigned int)L.splits) ? 1 : 0;
+      }
+#if GA_RD_GROUP > 32
+      if (lane == 0) sm_last = last;
+      __syncthreads();
+      last = sm_last;
+#else
+      last = __shfl_sync(0xffffffffu, last, 0);
+#endif
+      ga__state fin = ga__init();
+      if (last) {
+#pragma unroll 4
+        for (ga__u64 sp = lane; sp < L.splits; sp += GA_RD_GROUP)
+          ga__merge(fin, ga__get_partial(L, pval, pidx, sp, o));
+      }
+#if GA_RD_GROUP > 32
+      fin = ga__block_reduce(fin, sm, threadIdx.x, GA_RD_THREADS);
+      __syncthreads();
+#else
+      fin = ga__warp_reduce(fin);
+#endif
+      if (last && lane == 0) ga__emit(L, src, d0, d1, o, fin);
     }
-    __syncthreads();
   }
 }
 #endif
@@ -266,8 +425,9 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
 #if defined(GA_RD_BUILD_COLS)
 extern "C" __global__ void __launch_bounds__(32 * GA_RD_BY)
 ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, char *d1,
-           GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx) {
-  __shared__ ga__state sm[GA_RD_BY][32 * GA_RD_VEC + 1];
+           GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx, unsigned int *tickets) {
+  __shared__ ga__state sm[GA_RD_BY][GA_RD_VEC][32];
+  __shared__ int sm_last;
   const unsigned tx = threadIdx.x, ty = threadIdx.y;
   const ga__u64 kc = L.inner;                 /* contiguous kept run */
   const ga__u64 ko_total = L.nf_total / kc;   /* outer kept positions */
@@ -300,40 +460,79 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
         }
       }
       const char *base = src + koff;
-#pragma unroll 4
-      for (ga__u64 j = jb + ty; j < je; j += GA_RD_BY) {
-        ga__i64 roff;
-        GA_RD_IDX_T f;
-        if (L.nr == 1) {
-          roff = (ga__i64)j * L.rsrc[0];
-          f = (GA_RD_IDX_T)j * (GA_RD_IDX_T)L.rmul[0];
-        } else {
+      if (L.nr == 1) {
+        /* one reduced dimension: a pointer walking down with a fixed step */
+        const ga__i64 step = (ga__i64)GA_RD_BY * L.rsrc[0];
+        const GA_RD_IDX_T fstep = (GA_RD_IDX_T)GA_RD_BY * (GA_RD_IDX_T)L.rmul[0];
+        const char *p = base + (ga__i64)(jb + ty) * L.rsrc[0];
+        GA_RD_IDX_T f = (GA_RD_IDX_T)(jb + ty) * (GA_RD_IDX_T)L.rmul[0];
+        const unsigned int cnt = (je > jb + ty) ? (unsigned int)((je - jb - ty + GA_RD_BY - 1) / GA_RD_BY) : 0u;
+#pragma unroll 8
+        for (unsigned int n = 0; n < cnt; n++) {
+          const ga__rd_pack<GA_RD_VEC> t = *reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(p);
+#pragma unroll
+          for (int k = 0; k < GA_RD_VEC; k++) ga__take(st[k], GA_RD_LOAD(t.v[k]), f);
+          p += step;
+          f += fstep;
+        }
+      } else {
+#pragma unroll 2
+        for (ga__u64 j = jb + ty; j < je; j += GA_RD_BY) {
           ga__u64 r = j;
-          roff = 0;
-          f = 0;
+          ga__i64 roff = 0;
+          GA_RD_IDX_T f = 0;
           for (int d = (int)L.nr - 1; d >= 0; d--) {
             const ga__u64 q = r / L.rdim[d], c = r - q * L.rdim[d];
             r = q;
             roff += (ga__i64)c * L.rsrc[d];
             f += (GA_RD_IDX_T)c * (GA_RD_IDX_T)L.rmul[d];
           }
-        }
-        const ga__rd_pack<GA_RD_VEC> t =
-            *reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(base + roff);
+          const ga__rd_pack<GA_RD_VEC> t =
+              *reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(base + roff);
 #pragma unroll
-        for (int k = 0; k < GA_RD_VEC; k++) ga__take(st[k], GA_RD_LOAD(t.v[k]), f);
+          for (int k = 0; k < GA_RD_VEC; k++) ga__take(st[k], GA_RD_LOAD(t.v[k]), f);
+        }
       }
     }
 #pragma unroll
-    for (int k = 0; k < GA_RD_VEC; k++) sm[ty][tx * GA_RD_VEC + k] = st[k];
+    for (int k = 0; k < GA_RD_VEC; k++) sm[ty][k][tx] = st[k];
     __syncthreads();
-    if (ty == 0 && live) {
+    /* row-lane ty finishes vector lane k == ty (fixed order over the row lanes) */
+    if (ty < GA_RD_VEC && live) {
+      ga__state tot = sm[0][ty][tx];
 #pragma unroll
-      for (int k = 0; k < GA_RD_VEC; k++) {
-        ga__state tot = sm[0][tx * GA_RD_VEC + k];
-        for (int y = 1; y < GA_RD_BY; y++) ga__merge(tot, sm[y][tx * GA_RD_VEC + k]);
-        if (L.splits == 1) ga__emit(L, src, d0, d1, o0 + k, tot);
-        else ga__put_partial(L, pval, pidx, split, o0 + k, tot);
+      for (int y = 1; y < GA_RD_BY; y++) ga__merge(tot, sm[y][ty][tx]);
+      if (L.splits == 1) ga__emit(L, src, d0, d1, o0 + ty, tot);
+      else ga__put_partial(L, pval, pidx, split, o0 + ty, tot);
+    }
+    if (L.splits > 1) {
+      /* all partials of this tile are stored: one ticket per tile */
+      __syncthreads();
+      if (tx == 0 && ty == 0) sm_last = ga__take_ticket(&tickets[w], (unsigned int)L.splits) ? 1 : 0;
+      __syncthreads();
+      if (sm_last) {
+        /* the row lanes share the splits, then combine as above */
+        ga__state fin[GA_RD_VEC];
+#pragma unroll
+        for (int k = 0; k < GA_RD_VEC; k++) fin[k] = ga__init();
+        if (live) {
+#pragma unroll 4
+          for (ga__u64 sp = ty; sp < L.splits; sp += GA_RD_BY) {
+#pragma unroll
+            for (int k = 0; k < GA_RD_VEC; k++)
+              ga__merge(fin[k], ga__get_partial(L, pval, pidx, sp, o0 + k));
+          }
+        }
+        __syncthreads(); /* sm still holds this tile's first-stage states */
+#pragma unroll
+        for (int k = 0; k < GA_RD_VEC; k++) sm[ty][k][tx] = fin[k];
+        __syncthreads();
+        if (ty < GA_RD_VEC && live) {
+          ga__state tot = sm[0][ty][tx];
+#pragma unroll
+          for (int y = 1; y < GA_RD_BY; y++) ga__merge(tot, sm[y][ty][tx]);
+          ga__emit(L, src, d0, d1, o0 + ty, tot);
+        }
       }
     }
     __syncthreads();
@@ -343,11 +542,10 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
 
 /* --------------------------------------------------------------- general */
 #if defined(GA_RD_BUILD_GENERAL)
-/* GA_RD_TPO threads per output (1, 32 or GA_RD_THREADS). With GA_RD_STAGE2
- * the input is the partial buffers [splits][outputs] of a first pass. */
+/* GA_RD_TPO threads per output (1, 32 or GA_RD_THREADS). */
 extern "C" __global__ void __launch_bounds__(GA_RD_THREADS)
 ga_rd_general(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, char *d1,
-              GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx) {
+              GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx, unsigned int *tickets) {
 #if GA_RD_TPO > 32
   __shared__ ga__state sm[32];
 #endif
@@ -362,16 +560,6 @@ ga_rd_general(const __grid_constant__ ga__rd_layout L, const char *src, char *d0
     const bool live = o < L.nf_total;
     ga__state st = ga__init();
     if (live) {
-#if GA_RD_STAGE2
-      for (ga__u64 s = lane; s < L.splits; s += GA_RD_TPO) {
-        ga__state t;
-        t.v = pval[s * L.nf_total + o];
-#if GA_RD_KIND == 1
-        t.i = pidx[s * L.nf_total + o];
-#endif
-        ga__merge(st, t);
-      }
-#else
       const char *obase = src + ga__foff(L, L.fsrc, o);
       for (ga__u64 j = lane; j < L.nr_total; j += GA_RD_TPO) {
         ga__u64 r = j;
@@ -386,7 +574,6 @@ ga_rd_general(const __grid_constant__ ga__rd_layout L, const char *src, char *d0
         const GA_RD_SRC_T raw = *reinterpret_cast<const GA_RD_SRC_T *>(obase + roff);
         ga__take(st, GA_RD_LOAD(raw), f);
       }
-#endif
     }
 #if GA_RD_TPO == 32
     st = ga__warp_reduce(st);

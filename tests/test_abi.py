@@ -119,7 +119,7 @@ def test_elementwise_templates_compile_for_sm100a(api, case):
     L.gpuarray_b200_elemwise_source.restype = ctypes.c_void_p
     A = (api._ElemwiseArg * len(args))(*[api._ElemwiseArg(n.encode(), t, f) for n, t, f in args])
     p = L.gpuarray_b200_elemwise_source(b"", expr.encode(), len(args), A, flags, kind, ept, unroll,
-                                        nd, idx32, ctypes.c_ulonglong(modes), 1, 2)
+                                        nd, idx32, ctypes.c_ulonglong(modes), 64, 64)
     src = ctypes.string_at(p)
     assert src.startswith(b'#include "cluda.h"')
     err, size, log = _compile(api, src)
@@ -133,8 +133,8 @@ def test_reduction_templates_compile_for_sm100a(api, op, shape):
     L.gpuarray_b200_reduction_source.restype = ctypes.c_void_p
     src_tc = api.GA_INT if op in (9, 10, 11) else api.GA_FLOAT
     dst_tc = api.GA_BOOL if op in (12, 13) else src_tc
-    vec, tpo, st2 = {0: (4, 1, 0), 1: (4, 1, 0), 2: (1, 32, 1)}[shape]
-    p = L.gpuarray_b200_reduction_source(op, src_tc, dst_tc, shape, vec, 0, tpo, st2)
+    vec, tpo, group = {0: (4, 1, 32), 1: (4, 1, 0), 2: (1, 32, 0)}[shape]
+    p = L.gpuarray_b200_reduction_source(op, src_tc, dst_tc, shape, vec, 0, tpo, group)
     err, size, log = _compile(api, ctypes.string_at(p))
     assert err == 0 and size > 0, log
 
