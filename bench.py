@@ -76,7 +76,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.dev), "--query-gpu=" + self.QUERY,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._pump, daemon=True)
             self.t.start()
@@ -176,18 +176,25 @@ def side_configs(api, ctx, torch, stream):
     R, W = api.GE_READ, api.GE_WRITE
     peak, _ = measured_peak()
 
+    stall_buf = api.GpuArray.empty(ctx, (2 << 30,), np.uint8)
+
     def timed(fn, nbytes, reps=20, launches=1):
-        """fn(i) enqueues launch number i; per-launch CUDA events on the stream."""
+        """fn(i) enqueues launch number i. The `reps` launches run back to back
+        between two CUDA events on the library's stream; a ~1 ms memset is
+        enqueued first so that the host is ahead of the device and launch
+        latency of the short kernels is not billed to them."""
         for i in range(3):
             fn(i)
-        t = device_timer(torch, stream)
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            stall_buf.memset(0)
+        a.record(stream)
         for i in range(reps):
-            a, b = t.span()
-            a.record(stream)
             fn(i)
-            b.record(stream)
+        b.record(stream)
         ctx.sync()
-        us = t.total_ms() * 1e3 / reps
+        us = a.elapsed_time(b) * 1e3 / reps
         gbs = nbytes / us / 1e3
         return {"us": round(us, 2), "GB/s": round(gbs, 1), "frac_nominal_8TBs": round(gbs / NOMINAL_HBM_GBS, 3),
                 "frac_measured_peak": round(gbs / peak, 3), "bytes": nbytes, "launches": launches}
@@ -256,14 +263,64 @@ def side_configs(api, ctx, torch, stream):
         r_max = api.GpuReduction(ctx, api.GA_REDUCE_MAX, np.float64)
         nb = t5.numel() * 8
         out["cfg5_f64_sum_all"] = timed(lambda i: r_sum(g1, None, g5, [0, 1, 2]), nb + 8, reps=5,
-                                        launches=2)
+                                        launches=1)
         out["cfg5_f64_min_axes02"] = timed(lambda i: r_min(gk, None, g5, [0, 2]), nb + 8192, reps=5,
-                                           launches=2)
+                                           launches=1)
         out["cfg5_f64_max_axes02"] = timed(lambda i: r_max(gk, None, g5, [0, 2]), nb + 8192, reps=5,
-                                           launches=2)
+                                           launches=1)
         del t5
     except Exception as e:       # e.g. not enough free memory next to the headline buffers
         out["cfg5"] = {"skipped": str(e)[:200]}
+    return out
+
+
+def cfg5_sharded(api, ctx, torch, dist, stream, rank, world):
+    """fp64 (2048, 1024, 1024): each rank owns 2048/world leading planes, reduces
+    them to a partial of the final shape and one gpucomm all-reduce (NCCL on the
+    same stream) finishes. Time = max over ranks of (kernel + all-reduce)."""
+    planes = 2048 // world
+    g = torch.Generator(device="cuda").manual_seed(4 + rank)
+    t5 = torch.rand(planes, 1024, 1024, device="cuda", dtype=torch.float64, generator=g)
+    t5.mul_(2).sub_(1)
+    torch.cuda.synchronize()
+    g5 = api.GpuArray.from_pointer(ctx, t5.data_ptr(), (planes, 1024, 1024), np.float64)
+    cid = [api.GpuComm.gen_clique_id(ctx) if rank == 0 else None]
+    dist.broadcast_object_list(cid, src=0)
+    comm = api.GpuComm(ctx, cid[0], world, rank)
+    p1 = api.GpuArray.empty(ctx, (), np.float64)
+    o1 = api.GpuArray.empty(ctx, (), np.float64)
+    pk = api.GpuArray.empty(ctx, (1024,), np.float64)
+    ok = api.GpuArray.empty(ctx, (1024,), np.float64)
+    ops = {"sum_all": (api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.float64), [0, 1, 2], p1, o1, api.GA_SUM),
+           "min_axes02": (api.GpuReduction(ctx, api.GA_REDUCE_MIN, np.float64), [0, 2], pk, ok, api.GA_MIN),
+           "max_axes02": (api.GpuReduction(ctx, api.GA_REDUCE_MAX, np.float64), [0, 2], pk, ok, api.GA_MAX)}
+    out = {}
+    total_bytes = 2048 * 1024 * 1024 * 8
+    for name, (gr, axes, part, res, cop) in ops.items():
+        def step():
+            gr(part, None, g5, axes)
+            comm.all_reduce(part, res, cop)
+        for _ in range(3):
+            step()
+        ctx.sync()
+        dist.barrier()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        reps = 10
+        a.record(stream)
+        for _ in range(reps):
+            step()
+        b.record(stream)
+        ctx.sync()
+        t = torch.tensor([a.elapsed_time(b) / reps], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t[0]) * 1e3
+        out["cfg5_f64_%s_sharded" % name] = {
+            "us": round(us, 2), "GB/s": round(total_bytes / us / 1e3, 1),
+            "frac_nominal_8TBs_x_gpus": round(total_bytes / us / 1e3 / (NOMINAL_HBM_GBS * world), 3),
+            "planes_per_gpu": planes, "collective": "gpucomm_all_reduce (NCCL)"}
+    ctx.sync()
+    comm.free()
     return out
 
 
@@ -304,13 +361,15 @@ def run_ours(args, rank, world, local_rank):
         ctx.sync()
         torch.cuda.synchronize()
 
-    # ---- resident run
+    # ---- resident run. The clock sampler covers a window of about a second in
+    # which this same step loops; the K timed steps are the first of them.
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        time.sleep(0.25)
     launches0 = api.lib().gpuarray_b200_launch_count()
     timer = device_timer(torch, stream)
     barrier()
@@ -322,7 +381,14 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     ms = timer.total_ms()
     launches = api.lib().gpuarray_b200_launch_count() - launches0
+    if rank == 0:
+        t_end = time.perf_counter() + 1.0
+        while time.perf_counter() < t_end:
+            for _ in range(20):
+                step()
+            ctx.sync()
     clocks = sampler.stop() if rank == 0 else None
+    barrier()
 
     # quick self-check of the timed result on a few rows (host recomputation)
     vm, am = gmax.to_numpy(), garg.to_numpy()
@@ -347,6 +413,10 @@ def run_ours(args, rank, world, local_rank):
         barrier()
         e2e_ms = (time.perf_counter() - t0) * 1e3
 
+    sharded = None
+    if world > 1 and args.cfg5_sharded:
+        del gx
+        sharded = cfg5_sharded(api, ctx, torch, dist, stream, rank, world)
     if world > 1:
         t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -406,6 +476,8 @@ def run_ours(args, rank, world, local_rank):
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    if sharded is not None:
+        line["configs"] = sharded
     if world == 1 and not args.no_side_configs:
         del gx
         try:
@@ -434,6 +506,9 @@ def main():
                     help="rows per GPU (smaller values are for profiler captures only)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cfg5-sharded", action="store_true",
+                    help="with N > 1: also time fp64 (2048,1024,1024) SUM / MIN / MAX with the "
+                         "reduced leading axis sharded and one gpucomm all-reduce per result")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -75,7 +75,7 @@ class _ElemwiseArg(ctypes.Structure):
 
 
 class _CliqueId(ctypes.Structure):
-    _fields_ = [("internal", ctypes.c_char * GA_COMM_ID_BYTES)]
+    _fields_ = [("internal", ctypes.c_ubyte * GA_COMM_ID_BYTES)]
 
 
 _lib = None
@@ -528,12 +528,13 @@ class GpuComm:
     def gen_clique_id(ctx):
         cid = _CliqueId()
         _check(ctx.ptr, lib().gpucomm_gen_clique_id(ctx.ptr, ctypes.byref(cid)))
-        return bytes(cid.internal)
+        return ctypes.string_at(ctypes.addressof(cid), GA_COMM_ID_BYTES)
 
     def __init__(self, ctx, clique_id, ndev, rank):
         self.ctx = ctx
         cid = _CliqueId()
-        ctypes.memmove(cid.internal, clique_id, GA_COMM_ID_BYTES)
+        assert len(clique_id) == GA_COMM_ID_BYTES
+        ctypes.memmove(ctypes.addressof(cid), clique_id, GA_COMM_ID_BYTES)
         p = ctypes.c_void_p()
         _check(ctx.ptr, lib().gpucomm_new(ctypes.byref(p), ctx.ptr, cid, ndev, rank))
         self.ptr = p

@@ -432,8 +432,12 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
   const ga__u64 kc = L.inner;                 /* contiguous kept run */
   const ga__u64 ko_total = L.nf_total / kc;   /* outer kept positions */
   const ga__u64 nwork = ko_total * L.tiles;
+  /* The splits interleave: split s takes the row blocks s, s + S, s + 2S, ...
+   * (a block = GA_RD_BY consecutive reduced positions), so the CTAs running
+   * at any moment read one moving window of adjacent rows - sequential DRAM
+   * pages - instead of S windows that are far apart. */
   const ga__u64 split = blockIdx.y;
-  const ga__u64 jb = split * L.nr_total / L.splits, je = (split + 1) * L.nr_total / L.splits;
+  const ga__u64 nblk = (L.nr_total + GA_RD_BY - 1) / GA_RD_BY;
 
   for (ga__u64 w = blockIdx.x; w < nwork; w += gridDim.x) {
     ga__u64 ko = 0, tile = w;
@@ -460,15 +464,20 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
         }
       }
       const char *base = src + koff;
+      const unsigned int cnt =
+          (nblk > split) ? (unsigned int)((nblk - split + L.splits - 1) / L.splits) : 0u;
       if (L.nr == 1) {
         /* one reduced dimension: a pointer walking down with a fixed step */
-        const ga__i64 step = (ga__i64)GA_RD_BY * L.rsrc[0];
-        const GA_RD_IDX_T fstep = (GA_RD_IDX_T)GA_RD_BY * (GA_RD_IDX_T)L.rmul[0];
-        const char *p = base + (ga__i64)(jb + ty) * L.rsrc[0];
-        GA_RD_IDX_T f = (GA_RD_IDX_T)(jb + ty) * (GA_RD_IDX_T)L.rmul[0];
-        const unsigned int cnt = (je > jb + ty) ? (unsigned int)((je - jb - ty + GA_RD_BY - 1) / GA_RD_BY) : 0u;
+        const ga__u64 j0 = split * GA_RD_BY + ty;
+        const ga__u64 jstep = L.splits * GA_RD_BY;
+        const ga__i64 step = (ga__i64)jstep * L.rsrc[0];
+        const GA_RD_IDX_T fstep = (GA_RD_IDX_T)jstep * (GA_RD_IDX_T)L.rmul[0];
+        const char *p = base + (ga__i64)j0 * L.rsrc[0];
+        GA_RD_IDX_T f = (GA_RD_IDX_T)j0 * (GA_RD_IDX_T)L.rmul[0];
+        /* only the last block can be ragged */
+        const unsigned int full = (cnt > 0 && j0 + (ga__u64)(cnt - 1) * jstep >= L.nr_total) ? cnt - 1 : cnt;
 #pragma unroll 8
-        for (unsigned int n = 0; n < cnt; n++) {
+        for (unsigned int n = 0; n < full; n++) {
           const ga__rd_pack<GA_RD_VEC> t = *reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(p);
 #pragma unroll
           for (int k = 0; k < GA_RD_VEC; k++) ga__take(st[k], GA_RD_LOAD(t.v[k]), f);
@@ -476,8 +485,9 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
           f += fstep;
         }
       } else {
-#pragma unroll 2
-        for (ga__u64 j = jb + ty; j < je; j += GA_RD_BY) {
+        for (unsigned int n = 0; n < cnt; n++) {
+          const ga__u64 j = ((ga__u64)n * L.splits + split) * GA_RD_BY + ty;
+          if (j >= L.nr_total) break;
           ga__u64 r = j;
           ga__i64 roff = 0;
           GA_RD_IDX_T f = 0;
