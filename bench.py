@@ -367,7 +367,8 @@ def run_ours(args, rank, world, local_rank):
         step()
     barrier()
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    sample = rank == 0 and not args.no_clocks
+    if sample:
         sampler.start()
         time.sleep(0.25)
     launches0 = api.lib().gpuarray_b200_launch_count()
@@ -381,13 +382,13 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     ms = timer.total_ms()
     launches = api.lib().gpuarray_b200_launch_count() - launches0
-    if rank == 0:
+    if sample:
         t_end = time.perf_counter() + 1.0
         while time.perf_counter() < t_end:
             for _ in range(20):
                 step()
             ctx.sync()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop() if sample else None
     barrier()
 
     # quick self-check of the timed result on a few rows (host recomputation)
@@ -471,7 +472,7 @@ def run_ours(args, rank, world, local_rank):
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
                      "frac": per_gpu / peak, "peak_kind": peak_kind, "kernel": "ga_rd_rows",
-                     "traffic": TRAFFIC_BYTES_PER_LAUNCH},
+                     "traffic": TRAFFIC_BYTES_PER_LAUNCH if ROWS == 16384 else None},
         "clocks": clocks,
     }
     if cpu is not None:
@@ -489,9 +490,10 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one ga_rd_rows launch on this
-# workload, from the ncu capture summarised under profiles/ (None until taken).
-TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one 16384-row ga_rd_rows
+# launch: 4 x the 4096-row ncu capture summarised in
+# profiles/ga_rd_rows_cfg3_maxandargmax.md (traffic is proportional to rows).
+TRAFFIC_BYTES_PER_LAUNCH = 2126280704
 
 
 def main():
@@ -506,6 +508,8 @@ def main():
                     help="rows per GPU (smaller values are for profiler captures only)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-clocks", action="store_true",
+                    help="skip the nvidia-smi sampling window (profiler captures)")
     ap.add_argument("--cfg5-sharded", action="store_true",
                     help="with N > 1: also time fp64 (2048,1024,1024) SUM / MIN / MAX with the "
                          "reduced leading axis sharded and one gpucomm all-reduce per result")

@@ -424,7 +424,7 @@ static int all_multiple(const long long *v, unsigned n, long long m) {
 }
 
 /* Tuning for experiments: GPUARRAY_B200_RD="ctas_per_sm,seg_vectors,warp_item_bytes". */
-static unsigned rd_cols_ctas_per_sm = 16;
+static unsigned rd_cols_ctas_per_sm = 3;
 
 static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_bytes) {
   static int parsed = 0;
@@ -434,7 +434,7 @@ static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_
     const char *env = getenv("GPUARRAY_B200_RD");
     if (env != NULL)
       sscanf(env, "%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm);
-    if (rd_cols_ctas_per_sm == 0) rd_cols_ctas_per_sm = 16;
+    if (rd_cols_ctas_per_sm == 0) rd_cols_ctas_per_sm = 3;
     *warp_bytes = t_warp;
     if (t_ctas == 0) t_ctas = 32;
     if (t_seg == 0) t_seg = 8;
@@ -541,23 +541,30 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
       want.vec = (int)vec;
     L.inner = L.rdim[L.nr - 1];
     {
-      /* vectors per contiguous run decide who shares a work item: a CTA for
-       * long runs, a warp for runs of a few KiB; tiny runs are flattened */
       unsigned long long nvrow = L.inner / (unsigned)want.vec, groups_target, nwork, blocks, share;
       unsigned gpb;
-      /* few outputs with long runs: whole CTAs, which also keeps the number of
-       * partial results small; otherwise a warp per work item */
-      want.group = (nvrow >= cta_min_vecs ||
-                    (nvrow >= 2048 && L.nf_total < (unsigned long long)ctx->num_sms)) ? RD_THREADS : 32;
+      /* Who shares a work item, and whether the reduced extent is split:
+       *  - plenty of outputs: a warp per output, no split;
+       *  - a moderate number of outputs with long runs: a CTA per output;
+       *  - few outputs: split the reduced extent (CTAs when the runs are long
+       *    and the outputs very few, which also keeps the partial count low). */
+      int need_split = 0;
       want.flat = nvrow < 64;
+      if (nvrow >= cta_min_vecs) want.group = RD_THREADS;
+      else if (L.nf_total >= (unsigned long long)ctx->num_sms * 16) want.group = 32;
+      else if (L.nf_total >= (unsigned long long)ctx->num_sms * 4 && nvrow >= 1024)
+        want.group = RD_THREADS;
+      else {
+        need_split = 1;
+        want.group = (nvrow >= 2048 && L.nf_total < (unsigned long long)ctx->num_sms) ? RD_THREADS : 32;
+      }
+      if (want.group == RD_THREADS && want.flat) want.flat = 0;
       gpb = RD_THREADS / (unsigned)want.group;
-      /* enough independent groups keep HBM busy (each has ~8 128-bit loads per
-       * thread in flight); below that, split the reduced extent */
       groups_target = (unsigned long long)target * gpb;
       L.seg = L.inner;
       L.nseg = 1;
       L.units = rows_outer;
-      if (L.nf_total < (unsigned long long)ctx->num_sms * (want.group == 32 ? 16 : 4)) {
+      if (need_split) {
         unsigned long long s;
         if (!want.flat) {
           unsigned long long seg = (unsigned long long)want.group * vec * seg_vecs;

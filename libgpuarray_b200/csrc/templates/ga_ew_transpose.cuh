@@ -48,6 +48,23 @@ template <> struct ga__word<8> { typedef unsigned long long type; };
 #define GA__PW(S) ((sizeof(S) < 4) ? (4 / (int)sizeof(S)) : 1)
 #define GA__PITCHW(S) (GA_EW_TP / GA__PW(S) + 1)
 
+/* Which (row, 128-bit vector) of the tile a staging slot touches. A warp
+ * covers 4 rows x 8 vectors when the row has a multiple of 8 vectors: its
+ * four 32-bit stores per lane then hit 32 distinct banks (rows are an odd
+ * number of words apart), and each row still receives 128 contiguous bytes. */
+template <int PV>
+static __device__ __forceinline__ void ga__stage_map(const int i, int &q, int &v) {
+  if (PV % 8 == 0 && GA_EW_TQ % 4 == 0) {
+    const int lane = i & 31, blk = i >> 5;
+    const int rq = blk / (PV / 8), vb = blk - rq * (PV / 8);
+    q = rq * 4 + (lane >> 3);
+    v = vb * 8 + (lane & 7);
+  } else {
+    q = i / PV;
+    v = i - q * PV;
+  }
+}
+
 #define GA__P_ARR(k, n, S, C, R, W, M) , char *n##_p
 #define GA__P_SC(n, T) , T n##_s
 #define GA__ARG_ARR(k, n, S, C, R, W, M) n##_c[kk][e],
@@ -77,14 +94,16 @@ template <> struct ga__word<8> { typedef unsigned long long type; };
       ga__pack<W_, WV> r_[NV];                                                                \
       _Pragma("unroll") for (int k_ = 0; k_ < NV; k_++) {                                     \
         const int i_ = threadIdx.x + k_ * GA_EW_THREADS;                                      \
-        const int q_ = i_ / PV, v_ = i_ - q_ * PV;                                            \
+        int q_, v_;                                                                           \
+        ga__stage_map<PV>(i_, q_, v_);                                                        \
         if (i_ < GA_EW_TQ * PV && q_ < qn)                                                    \
           r_[k_] = *reinterpret_cast<const ga__pack<W_, WV> *>(                               \
               n##_t + (long long)q_ * sq_ + v_ * 16);                                         \
       }                                                                                       \
       _Pragma("unroll") for (int k_ = 0; k_ < NV; k_++) {                                     \
         const int i_ = threadIdx.x + k_ * GA_EW_THREADS;                                      \
-        const int q_ = i_ / PV, v_ = i_ - q_ * PV;                                            \
+        int q_, v_;                                                                           \
+        ga__stage_map<PV>(i_, q_, v_);                                                        \
         if (i_ < GA_EW_TQ * PV && q_ < qn) {                                                  \
           _Pragma("unroll") for (int j_ = 0; j_ < WV; j_++)                                   \
             n##_sm[q_][v_ * WV + j_] = r_[k_].v[j_];                                          \
