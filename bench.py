@@ -166,7 +166,7 @@ def run_reference(args, rank):
 
 # -------------------------------------------------------------------- our arm
 
-def side_configs(api, ctx, torch, stream):
+def side_configs(api, ctx, torch, stream, once=False):
     """The other single-GPU workloads, each launch timed on data that is not in
     L2: either the working set of one launch exceeds the 126 MB L2 (cfg1, cfg4,
     cfg5) or successive launches rotate through distinct inputs totalling more
@@ -183,11 +183,15 @@ def side_configs(api, ctx, torch, stream):
         between two CUDA events on the library's stream; a ~1 ms memset is
         enqueued first so that the host is ahead of the device and launch
         latency of the short kernels is not billed to them."""
-        for i in range(3):
+        if once:
+            warm, reps = 0, 1
+        else:
+            warm = 3
+        for i in range(warm):
             fn(i)
         a = torch.cuda.Event(enable_timing=True)
         b = torch.cuda.Event(enable_timing=True)
-        for _ in range(3):
+        for _ in range(0 if once else 3):
             stall_buf.memset(0)
         a.record(stream)
         for i in range(reps):
@@ -252,7 +256,8 @@ def side_configs(api, ctx, torch, stream):
 
     # cfg5: fp64 (2048, 1024, 1024) = 16 GiB: SUM over everything, MIN and MAX over (0, 2)
     try:
-        t5 = torch.rand(2048, 1024, 1024, device="cuda", dtype=torch.float64, generator=g)
+        planes = 128 if once else 2048
+        t5 = torch.rand(planes, 1024, 1024, device="cuda", dtype=torch.float64, generator=g)
         t5.mul_(2).sub_(1)
         t1 = torch.empty((), device="cuda", dtype=torch.float64)
         tk = torch.empty(1024, device="cuda", dtype=torch.float64)
@@ -482,7 +487,7 @@ def run_ours(args, rank, world, local_rank):
     if world == 1 and not args.no_side_configs:
         del gx
         try:
-            line["configs"] = side_configs(api, ctx, torch, stream)
+            line["configs"] = side_configs(api, ctx, torch, stream, once=args.side_once)
         except Exception as e:
             line["configs"] = {"error": str(e)[:300]}
     print(json.dumps(line))
@@ -508,6 +513,8 @@ def main():
                     help="rows per GPU (smaller values are for profiler captures only)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--side-once", action="store_true",
+                    help="profiler captures: run every side config exactly once, cfg5 on 128 planes")
     ap.add_argument("--no-clocks", action="store_true",
                     help="skip the nvidia-smi sampling window (profiler captures)")
     ap.add_argument("--cfg5-sharded", action="store_true",

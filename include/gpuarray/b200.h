@@ -44,6 +44,24 @@ GPUARRAY_PUBLIC char *gpuarray_b200_elemwise_source(const char *preamble, const 
 GPUARRAY_PUBLIC char *gpuarray_b200_reduction_source(int op, int src_tc, int dst_tc, int shape,
                                                      int vec, int idx64, int tpo, int group);
 
+/* Sum of n contiguous float32 values on the current device WITHOUT allocating
+ * anything: no cudaMalloc / cudaFree, no library workspace. (No counterpart in
+ * the reference, whose reductions allocate per call.) It is for callers that
+ * are not allowed to allocate when they need the result - code living inside
+ * another framework's memory pool, latency-critical loops, hosts that must not
+ * touch the driver's allocator between stream-ordered work. The partial sums
+ * and the arrival ticket of the split reduction live in a 64 KiB block that is
+ * part of the library image on every GPU that loads it.
+ *   src, dst     device pointers (src 16-byte aligned); dst receives one float
+ *   n            at most GPUARRAY_B200_NOALLOC_MAX_ELEMS, else GA_XLARGE_ERROR
+ *   cuda_stream  a CUstream / cudaStream_t (NULL: the default stream)
+ * The first call on a device resolves the block's device address; make it
+ * before any stream capture. Calls share the block: do not let two of them
+ * overlap on the GPU. Returns a GA_* code; text via gpucontext_error(NULL, 0). */
+#define GPUARRAY_B200_NOALLOC_MAX_ELEMS (1ULL << 32)
+GPUARRAY_PUBLIC int gpuarray_b200_sum_f32_noalloc(const float *src, size_t n, float *dst,
+                                                  void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

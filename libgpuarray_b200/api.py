@@ -157,6 +157,7 @@ def lib():
         sig("gpucomm_all_reduce", ci, vp, sz, vp, sz, sz, ci, ci, vp)
         sig("GpuArray_all_reduce", ci, A, A, ci, vp)
     sig("gpuarray_b200_error_code", ci, vp)
+    sig("gpuarray_b200_sum_f32_noalloc", ci, vp, sz, vp, vp)
     sig("gpuarray_b200_launch_count", ctypes.c_ulonglong)
     sig("gpuarray_b200_compile_check", ci, ctypes.c_char_p, vp, ctypes.c_char_p,
         ctypes.POINTER(sz), ctypes.POINTER(ctypes.c_char_p))
