@@ -620,10 +620,91 @@ int GpuArray_concatenate(GpuArray *r, const GpuArray **as, size_t n, unsigned in
   return err;
 }
 
+/* a[k, ...] = v[i[k], ...]: gather along axis 0 (reference
+ * src/gpuarray_array.c:425-546). `a` and `i` are C-contiguous, `v` may have
+ * any strides. With check_error the error word is read back (a host
+ * synchronisation) and an out-of-range index gives GA_VALUE_ERROR. */
 int GpuArray_take1(GpuArray *a, const GpuArray *v, const GpuArray *i, int check_error) {
-  (void)v; (void)i; (void)check_error;
-  return ga_err_set(GpuArray_context(a)->err, GA_UNSUPPORTED_ERROR,
-                    "take1 (gather) is outside the elementwise/reduction engine");
+  gpucontext *ctx = GpuArray_context(a);
+  ga_strb sb;
+  ga_function fn;
+  unsigned long long blob[2 + 2 * 16];
+  unsigned grid[3] = {1, 1, 1}, block[3] = {256, 1, 1};
+  CUdeviceptr p_r, p_v, p_i, p_e;
+  void *params[5];
+  size_t n0, n1 = 1;
+  unsigned int j;
+  int err, kerr = 0;
+
+  if (!GpuArray_ISWRITEABLE(a))
+    return ga_err_set(ctx->err, GA_VALUE_ERROR, "Destination array not writeable");
+  if (!GpuArray_ISALIGNED(a) || !GpuArray_ISALIGNED(v) || !GpuArray_ISALIGNED(i))
+    return ga_err_set(ctx->err, GA_UNALIGNED_ERROR, "Not all arrays are aligned");
+  if (!GpuArray_IS_C_CONTIGUOUS(a))
+    return ga_err_set(ctx->err, GA_INVALID_ERROR, "Destination array (a) not C-contiguous");
+  if (!GpuArray_IS_C_CONTIGUOUS(i))
+    return ga_err_set(ctx->err, GA_INVALID_ERROR, "Index array (i) not C-contiguous");
+  if (v->nd == 0 || a->nd == 0 || i->nd != 1 || a->nd != v->nd || v->nd > 16)
+    return ga_err_fmt(ctx->err, GA_INVALID_ERROR,
+                      "Dimension mismatch. v->nd = %u, a->nd = %u, i->nd = %u", v->nd, a->nd, i->nd);
+  if (a->dimensions[0] != i->dimensions[0])
+    return ga_err_fmt(ctx->err, GA_INVALID_ERROR,
+                      "Dimension mismatch. a->dimensions[0] = %zu, i->dimensions[0] = %zu",
+                      a->dimensions[0], i->dimensions[0]);
+  for (j = 1; j < v->nd; j++) {
+    if (a->dimensions[j] != v->dimensions[j])
+      return ga_err_fmt(ctx->err, GA_INVALID_ERROR,
+                        "Dimension mismatch. a->dimensions[%u] = %zu, v->dimensions[%u] = %zu", j,
+                        a->dimensions[j], j, v->dimensions[j]);
+    n1 *= v->dimensions[j];
+  }
+  n0 = i->dimensions[0];
+  if (!ga_type_is_computable(a->typecode) || !ga_type_is_computable(v->typecode) ||
+      !ga_type_is_computable(i->typecode) || i->typecode == GA_FLOAT || i->typecode == GA_DOUBLE ||
+      i->typecode == GA_HALF)
+    return ga_err_set(ctx->err, GA_UNSUPPORTED_ERROR, "Unsupported element or index type");
+  if (n0 == 0 || n1 == 0) return GA_NO_ERROR;
+
+  ga_strb_init(&sb);
+  ga_strb_printf(&sb,
+                 "#include \"cluda.h\"\n#define GA_TK_R_T %s\n#define GA_TK_V_T %s\n"
+                 "#define GA_TK_I_T %s\n#define GA_TK_ND %u\n#include \"ga_take1.cuh\"\n",
+                 ga_ctype(a->typecode), ga_ctype(v->typecode), ga_ctype(i->typecode), v->nd);
+  if (sb.failed) {
+    ga_strb_free(&sb);
+    return ga_err_set(ctx->err, GA_MEMORY_ERROR, "Out of memory");
+  }
+  err = ga_compile(ctx, ga_strb_cstr(&sb), "ga_take1", NULL, &fn, NULL);
+  ga_strb_free(&sb);
+  if (err != GA_NO_ERROR) return err;
+
+  blob[0] = n0;
+  blob[1] = n1;
+  for (j = 0; j < v->nd; j++) {
+    blob[2 + j] = v->dimensions[j];
+    blob[2 + v->nd + j] = (unsigned long long)(long long)v->strides[j];
+  }
+  p_r = a->data->ptr + a->offset;
+  p_v = v->data->ptr + v->offset;
+  p_i = i->data->ptr + i->offset;
+  p_e = ctx->errbuf->ptr;
+  params[0] = blob;
+  params[1] = &p_r;
+  params[2] = &p_v;
+  params[3] = &p_i;
+  params[4] = &p_e;
+  grid[0] = (unsigned)((n1 + 255) / 256 > 65535 ? 65535 : (n1 + 255) / 256);
+  grid[1] = (unsigned)(n0 > 65535 ? 65535 : n0);
+  err = ga_launch(ctx, &fn, grid, block, 0, params);
+  if (err == GA_NO_ERROR && check_error) {
+    err = gpudata_read(&kerr, ctx->errbuf, 0, sizeof(int));
+    if (err == GA_NO_ERROR && kerr != 0) {
+      kerr = 0;
+      gpudata_write(ctx->errbuf, 0, &kerr, sizeof(int));
+      err = ga_err_set(ctx->err, GA_VALUE_ERROR, "Index out of bounds");
+    }
+  }
+  return err;
 }
 
 const char *GpuArray_error(const GpuArray *a, int err) {

@@ -242,6 +242,7 @@ GpuElemwise *GpuElemwise_new(gpucontext *ctx, const char *preamble, const char *
     return NULL;
   }
   ge->ctx = ctx;
+  ctx->refcnt++; /* the operator keeps its context alive */
   ge->flags = flags;
   ge->n = n;
   ge->expr = strdup(expr);
@@ -331,7 +332,11 @@ void GpuElemwise_free(GpuElemwise *ge) {
   free(ge->blob);
   free(ge->preamble);
   free(ge->expr);
-  free(ge);
+  {
+    gpucontext *ctx = ge->ctx;
+    free(ge);
+    if (ctx != NULL) ga_ctx_unref(ctx);
+  }
 }
 
 /* ------------------------------------------------------------------- calls */

@@ -1,0 +1,123 @@
+"""GpuArray entry points around the hot path (views, copies, gather): the
+callers' side of the engine. Views are pure host bookkeeping; every typed or
+strided copy below runs the elementwise engine ("dst = src"), as the
+reference's ga_extcopy does (src/gpuarray_array.c:42-86)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_views_match_numpy(api, ctx, rng):
+    x = rng.standard_normal((6, 7, 8)).astype(np.float32)
+    g = api.GpuArray.from_numpy(ctx, x)
+    assert (g[1:5, ::-2, 3].to_numpy() == x[1:5, ::-2, 3]).all()
+    assert (g.transpose((2, 0, 1)).to_numpy() == x.transpose(2, 0, 1)).all()
+    assert (g.transpose().to_numpy() == x.T).all()
+    assert (g.reshape((42, 8)).to_numpy() == x.reshape(42, 8)).all()
+    r = g.reshape((6, 56), nocopy=True)
+    assert r.ga.data == g.ga.data                      # a view, not a copy
+    t = g.transpose((1, 0, 2))
+    with pytest.raises(api.GpuArrayException) as ei:
+        t.reshape((42, 8), nocopy=True)
+    assert ei.value.code == api.GA_COPY_ERROR
+    assert (t.reshape((42, 8)).to_numpy() == x.transpose(1, 0, 2).reshape(42, 8)).all()
+    f = api.GpuArray.from_numpy(ctx, x, order="F")
+    assert f.flags & api.GA_F_CONTIGUOUS and not (f.flags & api.GA_C_CONTIGUOUS)
+    assert (f.to_numpy() == x).all()
+    assert (f.copy("C").to_numpy() == x).all()
+
+
+def test_setarray_broadcasts(api, ctx, rng):
+    a = api.GpuArray.from_numpy(ctx, np.zeros((4, 5, 6), np.float32))
+    v = rng.standard_normal((5, 1)).astype(np.float32)
+    gv = api.GpuArray.from_numpy(ctx, v)
+    api._check(ctx.ptr, api.lib().GpuArray_setarray(ctypes.byref(a.ga), ctypes.byref(gv.ga)))
+    assert (a.to_numpy() == np.broadcast_to(v, (4, 5, 6))).all()
+
+
+def test_split_and_concatenate(api, ctx, rng):
+    L = api.lib()
+    x = rng.integers(0, 100, (7, 9)).astype(np.int32)
+    g = api.GpuArray.from_numpy(ctx, x)
+    parts = [api.GpuArray(ctx) for _ in range(3)]
+    ptrs = (ctypes.POINTER(api._GpuArrayStruct) * 3)(*[ctypes.pointer(p.ga) for p in parts])
+    cuts = (ctypes.c_size_t * 2)(2, 5)
+    L.GpuArray_split.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p,
+                                 ctypes.c_uint]
+    api._check(ctx.ptr, L.GpuArray_split(ptrs, ctypes.byref(g.ga), 2, cuts, 1))
+    for p in parts:
+        p._live = True
+    assert [p.shape for p in parts] == [(7, 2), (7, 3), (7, 4)]
+    assert (parts[1].to_numpy() == x[:, 2:5]).all()
+    out = api.GpuArray(ctx)
+    L.GpuArray_concatenate.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t,
+                                       ctypes.c_uint, ctypes.c_int]
+    order = (ctypes.POINTER(api._GpuArrayStruct) * 3)(ctypes.pointer(parts[2].ga),
+                                                      ctypes.pointer(parts[0].ga),
+                                                      ctypes.pointer(parts[1].ga))
+    api._check(ctx.ptr, L.GpuArray_concatenate(ctypes.byref(out.ga), order, 3, 1, api.GA_LONG))
+    out._live = True
+    want = np.concatenate([x[:, 5:], x[:, :2], x[:, 2:5]], axis=1).astype(np.int64)
+    assert out.dtype == np.int64 and (out.to_numpy() == want).all()
+
+
+def test_take1_gathers_rows(api, ctx, rng):
+    L = api.lib()
+    L.GpuArray_take1.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int]
+    v = rng.standard_normal((11, 4, 5)).astype(np.float32)
+    gv = api.GpuArray.from_numpy(ctx, v).transpose((0, 2, 1))      # strided source
+    idx = np.array([3, -1, 0, 10, 3, -11], dtype=np.int64)
+    gi = api.GpuArray.from_numpy(ctx, idx)
+    out = api.GpuArray.empty(ctx, (6, 5, 4), np.float32)
+    api._check(ctx.ptr, L.GpuArray_take1(ctypes.byref(out.ga), ctypes.byref(gv.ga),
+                                         ctypes.byref(gi.ga), 1))
+    assert (out.to_numpy() == v.transpose(0, 2, 1)[idx]).all()
+    bad = api.GpuArray.from_numpy(ctx, np.array([0, 11, 1, 2, 3, 4], dtype=np.int64))
+    err = L.GpuArray_take1(ctypes.byref(out.ga), ctypes.byref(gv.ga), ctypes.byref(bad.ga), 1)
+    assert err == api.GA_VALUE_ERROR
+    # the error word was handed back at zero: the next checked call succeeds
+    api._check(ctx.ptr, L.GpuArray_take1(ctypes.byref(out.ga), ctypes.byref(gv.ga),
+                                         ctypes.byref(gi.ga), 1))
+
+
+def test_user_kernel_through_gpukernel(api, ctx, rng):
+    """GpuKernel_init / _sched / _call with a caller-written kernel, as pygpu.GpuKernel does."""
+    L = api.lib()
+
+    class GpuKernel(ctypes.Structure):
+        _fields_ = [("k", ctypes.c_void_p), ("args", ctypes.c_void_p)]
+    src = (b'#include "cluda.h"\nKERNEL void axpy(GLOBAL_MEM ga_float *y, GLOBAL_MEM const ga_float *x, '
+           b'ga_float a, ga_size n) {\n  for (ga_size i = GID_0 * LDIM_0 + LID_0; i < n; i += LDIM_0 * GDIM_0) '
+           b'y[i] += a * x[i];\n}\n')
+    k = GpuKernel()
+    strs = (ctypes.c_char_p * 1)(src)
+    types = (ctypes.c_int * 4)(api.GA_BUFFER, api.GA_BUFFER, api.GA_FLOAT, api.GA_SIZE)
+    L.GpuKernel_init.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p,
+                                 ctypes.c_void_p, ctypes.c_char_p, ctypes.c_uint, ctypes.c_void_p,
+                                 ctypes.c_int, ctypes.c_void_p]
+    api._check(ctx.ptr, L.GpuKernel_init(ctypes.byref(k), ctx.ptr, 1, strs, None, b"axpy", 4, types,
+                                         0, None))
+    n = 100003
+    x = rng.standard_normal(n).astype(np.float32)
+    y = rng.standard_normal(n).astype(np.float32)
+    gx, gy = api.GpuArray.from_numpy(ctx, x), api.GpuArray.from_numpy(ctx, y)
+    a = ctypes.c_float(2.5)
+    cn = ctypes.c_size_t(n)
+    L.GpuKernel_setarg.argtypes = [ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p]
+    for i, p in enumerate((gy.ga.data, gx.ga.data, ctypes.addressof(a), ctypes.addressof(cn))):
+        api._check(ctx.ptr, L.GpuKernel_setarg(ctypes.byref(k), i, p))
+    gs, ls = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    L.GpuKernel_sched.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
+    api._check(ctx.ptr, L.GpuKernel_sched(ctypes.byref(k), n, ctypes.byref(gs), ctypes.byref(ls)))
+    assert ls.value % 32 == 0 and 0 < ls.value <= 512 and gs.value >= 1
+    L.GpuKernel_call.argtypes = [ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p, ctypes.c_void_p,
+                                 ctypes.c_size_t, ctypes.c_void_p]
+    api._check(ctx.ptr, L.GpuKernel_call(ctypes.byref(k), 1, ctypes.byref(gs), ctypes.byref(ls), 0,
+                                         None))
+    # y += a*x is one fused multiply-add: round(y + 2.5*x) computed exactly in fp64
+    want = (y.astype(np.float64) + 2.5 * x.astype(np.float64)).astype(np.float32)
+    assert (gy.to_numpy() == want).all()
+    L.GpuKernel_clear(ctypes.byref(k))
