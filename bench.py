@@ -150,7 +150,7 @@ def run_reference(args, rank):
     nbytes = x.nbytes + sample_rows * 12
     val = nbytes / dt / 1e9
     cores = os.cpu_count()
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": "maxandargmax effective GB/s", "value": val, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
@@ -161,7 +161,7 @@ def run_reference(args, rank):
                          "sample": "%d of 16384 rows per step; pygpu-on-pocl (the reference's "
                                    "CPU path) is unavailable on this box" % sample_rows},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }))
+    })
 
 
 # -------------------------------------------------------------------- our arm
@@ -490,7 +490,7 @@ def run_ours(args, rank, world, local_rank):
             line["configs"] = side_configs(api, ctx, torch, stream, once=args.side_once)
         except Exception as e:
             line["configs"] = {"error": str(e)[:300]}
-    print(json.dumps(line))
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -501,7 +501,25 @@ def run_ours(args, rank, world, local_rank):
 TRAFFIC_BYTES_PER_LAUNCH = 2126280704
 
 
+_REAL_STDOUT = None
+
+
+def emit(obj):
+    """The one JSON line goes to the real stdout; everything else that libraries
+    print there (NCCL's version banner, for instance) was diverted to stderr."""
+    data = (json.dumps(obj) + "\n").encode()
+    if _REAL_STDOUT is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT, data)
+
+
 def main():
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
