@@ -560,7 +560,10 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
       }
       if (want.group == RD_THREADS && want.flat) want.flat = 0;
       gpb = RD_THREADS / (unsigned)want.group;
-      groups_target = (unsigned long long)target * gpb;
+      /* measured on B200: whole-CTA groups run best as a few long-lived CTAs
+       * per SM, warp groups as many (a full complement of resident warps) */
+      groups_target = want.group == RD_THREADS ? (unsigned long long)ctx->num_sms * 4
+                                               : (unsigned long long)target * gpb;
       L.seg = L.inner;
       L.nseg = 1;
       L.units = rows_outer;
