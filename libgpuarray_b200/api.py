@@ -81,13 +81,27 @@ class _CliqueId(ctypes.Structure):
 _lib = None
 
 
+def _already_loaded():
+    """Path of a libgpuarray this process has mapped already (say through pygpu's
+    extension modules), so that both users share one copy of the library's state."""
+    try:
+        with open("/proc/self/maps") as f:
+            for line in f:
+                path = line.rstrip("\n").split(" ")[-1]
+                if os.path.basename(path).startswith("libgpuarray.so"):
+                    return path
+    except OSError:
+        pass
+    return None
+
+
 def lib():
     """The loaded shared library with argument types declared. Raises OSError
     when it has not been built (python -m libgpuarray_b200.build)."""
     global _lib
     if _lib is not None:
         return _lib
-    L = ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
+    L = ctypes.CDLL(_already_loaded() or LIB_PATH, mode=ctypes.RTLD_GLOBAL)
     vp, ci, cu, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_size_t
     A = ctypes.POINTER(_GpuArrayStruct)
     psz, pss = ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_ssize_t)
@@ -188,9 +202,19 @@ class Context:
         self.ptr = p
         self.dev = dev
 
+    @classmethod
+    def borrow(cls, pointer):
+        """Wraps a gpucontext* owned by someone else (e.g. pygpu's GpuContext.ptr)."""
+        self = cls.__new__(cls)
+        self.ptr = ctypes.c_void_p(pointer)
+        self.dev = None
+        self._borrowed = True
+        return self
+
     def close(self):
         if self.ptr is not None:
-            lib().gpucontext_deref(self.ptr)
+            if not getattr(self, "_borrowed", False):
+                lib().gpucontext_deref(self.ptr)
             self.ptr = None
 
     def __del__(self):

@@ -1,0 +1,117 @@
+"""pygpu's reduction front end on top of GpuReduction_*.
+
+The reference implements ndgpuarray.sum/prod/all/any in Python: `reduce1`
+(pygpu/reduction.py:294-319) renders a mako template into a `reduk` kernel.
+This module provides the same two callables, `reduce1` and the
+`ReductionKernel(context, dtype_out, neutral, reduce_expr, redux)` subset that
+takes one array and no map expression, but runs them through the library's
+C reduction engine. `install()` puts them in place of pygpu's own, which lifts
+the template's limits (32-bit sizes, no float16, one block for full
+reductions) and removes the mako dependency:
+
+    import pygpu
+    from libgpuarray_b200 import pygpu_compat
+    pygpu_compat.install()
+    x.sum(axis=1)        # ndgpuarray method -> GpuReduction_call
+
+pygpu arrays are handed over without copies: `GpuContext.ptr` is the
+gpucontext*, `GpuArray.gpudata` the device address of element [0,...,0].
+"""
+import numpy as np
+
+from . import api
+
+_OPS = {"+": api.GA_REDUCE_SUM, "*": api.GA_REDUCE_PROD, "&&": api.GA_REDUCE_ALL,
+        "||": api.GA_REDUCE_ANY, "&": api.GA_REDUCE_AND, "|": api.GA_REDUCE_OR,
+        "^": api.GA_REDUCE_XOR}
+_EXPRS = {"a+b": api.GA_REDUCE_SUM, "a*b": api.GA_REDUCE_PROD, "a&&b": api.GA_REDUCE_ALL,
+          "a||b": api.GA_REDUCE_ANY, "max(a,b)": api.GA_REDUCE_MAX, "min(a,b)": api.GA_REDUCE_MIN,
+          "a&b": api.GA_REDUCE_AND, "a|b": api.GA_REDUCE_OR, "a^b": api.GA_REDUCE_XOR}
+_contexts = {}
+_operators = {}
+
+
+def _ctx(pygpu_context):
+    key = int(pygpu_context.ptr)
+    if key not in _contexts:
+        _contexts[key] = api.Context.borrow(key)
+    return _contexts[key]
+
+
+def _wrap(ctx, a):
+    return api.GpuArray.from_pointer(ctx, int(a.gpudata), a.shape, a.dtype, strides=a.strides,
+                                     nbytes=max(int(a.size) * a.dtype.itemsize, 1))
+
+
+def _run(opcode, ary, redux, out_type, out):
+    import pygpu
+    out_type = np.dtype(out_type)
+    axes = [i for i, r in enumerate(redux) if r]
+    if not axes:
+        raise ValueError("Reduction is along no axes")
+    kept = tuple(d for d, r in zip(ary.shape, redux) if not r)
+    if out is None:
+        out = pygpu.gpuarray.empty(kept, dtype=out_type, context=ary.context, cls=type(ary))
+    else:
+        if out.shape != kept or out.dtype != out_type:
+            raise TypeError("Out array is not of expected type (expected %s %s, got %s %s)" %
+                            (kept, out_type, out.shape, out.dtype))
+    ctx = _ctx(ary.context)
+    key = (int(ary.context.ptr), opcode, ary.dtype.str)
+    if key not in _operators:
+        _operators[key] = api.GpuReduction(ctx, opcode, ary.dtype)
+    if ary.size == 0 and opcode in (api.GA_REDUCE_MAX, api.GA_REDUCE_MIN):
+        raise ValueError("min/max of an empty array")
+    _operators[key](_wrap(ctx, out), None, _wrap(ctx, ary), axes)
+    return out
+
+
+def reduce1(ary, op, neutral, out_type, axis=None, out=None, oper=None):
+    """Same signature and axis handling as pygpu.reduction.reduce1."""
+    nd = ary.ndim
+    if axis is None:
+        redux = [True] * nd
+    else:
+        redux = [False] * nd
+        if not isinstance(axis, (list, tuple)):
+            axis = (axis,)
+        for ax in axis:
+            if ax < 0:
+                ax += nd
+            if ax < 0 or ax >= nd:
+                raise ValueError("axis out of bounds")
+            redux[ax] = True
+    opcode = _EXPRS.get(oper.replace(" ", "")) if oper is not None else _OPS.get(op)
+    if opcode is None:
+        raise NotImplementedError("reduction operator %r" % (oper or op))
+    return _run(opcode, ary, redux, out_type, out)
+
+
+class ReductionKernel(object):
+    """The one-array, no-map subset of pygpu.reduction.ReductionKernel."""
+
+    def __init__(self, context, dtype_out, neutral, reduce_expr, redux, map_expr=None,
+                 arguments=None, preamble="", init_nd=None):
+        if map_expr is not None and map_expr.replace(" ", "") not in ("a[i]",):
+            raise NotImplementedError("map expressions need pygpu's template kernel")
+        self.opcode = _EXPRS.get(reduce_expr.replace(" ", ""))
+        if self.opcode is None:
+            raise NotImplementedError("reduce expression %r" % reduce_expr)
+        if not any(redux):
+            raise ValueError("Reduction is along no axes")
+        self.redux = list(redux)
+        self.dtype_out = np.dtype(dtype_out)
+
+    def __call__(self, ary, out=None, **kwargs):
+        if len(self.redux) != ary.ndim:
+            raise ValueError("redux mask does not match the array rank")
+        return _run(self.opcode, ary, self.redux, self.dtype_out, out)
+
+
+def install():
+    """Replaces pygpu's template-based reduction entry points by these."""
+    import pygpu.reduction
+    import pygpu._array
+    pygpu.reduction.reduce1 = reduce1
+    pygpu.reduction.ReductionKernel = ReductionKernel
+    pygpu._array.reduce1 = reduce1

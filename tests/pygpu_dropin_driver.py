@@ -73,7 +73,7 @@ def run_callable(f, args, stats, name):
         stats["fail"] += 1
         # the innermost function of the reference's test file names the case
         frames = [fr.name for fr in traceback.extract_tb(sys.exc_info()[2])
-                  if fr.filename.endswith("test_elemwise.py")]
+                  if "pygpu/tests/test_" in fr.filename]
         key = frames[-1] if frames else name
         stats["failed_names"][key] = stats["failed_names"].get(key, 0) + 1
         stats["failures"].append("%s%r\n%s" % (name, args if len(repr(args)) < 200 else "(...)",
@@ -111,8 +111,46 @@ def part2(modname):
     return stats
 
 
+def part3():
+    """ndgpuarray.sum/prod/all/any through GpuReduction_* (pygpu_compat.install)."""
+    import pygpu
+    from pygpu import ndgpuarray
+    from libgpuarray_b200 import pygpu_compat
+    pygpu_compat.install()
+    ctx = pygpu.init(os.environ.get("DEVICE", "cuda0"))
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((37, 500, 6)).astype(np.float32)
+    g = pygpu.array(x, context=ctx, cls=ndgpuarray)
+    for axis in (None, 0, 1, 2, (0, 2), (1, 2)):
+        want = x.astype(np.float64).sum(axis=axis)
+        got = np.asarray(g.sum(axis=axis)).astype(np.float64)
+        scale = np.abs(x.astype(np.float64)).sum(axis=axis)
+        assert (np.abs(got - want) <= 1e-6 * np.log2(x.size) * scale).all(), axis
+    assert np.asarray(g.T.sum(axis=0)).shape == (500, 37)            # strided view
+    h = pygpu.array(x.astype(np.float16), context=ctx, cls=ndgpuarray)  # float16 works here
+    assert np.allclose(np.asarray(h.sum(axis=1)).astype(np.float32),
+                       x.astype(np.float16).astype(np.float32).sum(axis=1), rtol=2e-2, atol=0.5)
+    i8 = rng.integers(-3, 4, (20, 30)).astype(np.int8)
+    gi = pygpu.array(i8, context=ctx, cls=ndgpuarray)
+    r = gi.sum(axis=1)
+    assert r.dtype == np.dtype("int") and (np.asarray(r) == i8.sum(axis=1, dtype="int")).all()
+    assert (np.asarray(gi.prod(axis=0)) == i8.prod(axis=0, dtype="int")).all()
+    b = rng.random((50, 60)) < 0.97
+    gb = pygpu.array(b, context=ctx, cls=ndgpuarray)
+    assert (np.asarray(gb.all(axis=1)) == b.all(axis=1)).all()
+    assert (np.asarray(gb.any(axis=0)) == b.any(axis=0)).all()
+    assert bool(np.asarray(gb.any())) == bool(b.any())
+    print("part3 ok")
+
+
 if __name__ == "__main__":
+    mods = [m for m in sys.argv[1:] if not m.startswith("--")]
     part1()
-    for m in sys.argv[1:]:
+    if "--reductions" in sys.argv:
+        part3()
+        import pygpu.tests.test_reduction as tr
+        from libgpuarray_b200 import pygpu_compat
+        tr.ReductionKernel = pygpu_compat.ReductionKernel
+    for m in mods:
         part2(m)
     sys.exit(0)
