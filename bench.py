@@ -176,7 +176,7 @@ def side_configs(api, ctx, torch, stream, once=False):
     R, W = api.GE_READ, api.GE_WRITE
     peak, _ = measured_peak()
 
-    stall_buf = api.GpuArray.empty(ctx, (2 << 30,), np.uint8)
+    stall_buf = api.GpuArray.empty(ctx, (4096 if once else 2 << 30,), np.uint8)
 
     def timed(fn, nbytes, reps=20, launches=1):
         """fn(i) enqueues launch number i. The `reps` launches run back to back
