@@ -25,7 +25,7 @@
 enum { SHAPE_ROWS = 0, SHAPE_COLS = 1, SHAPE_GENERAL = 2 };
 
 typedef struct rd_variant {
-  int shape, vec, idx64, tpo, dst_tc, write_val, write_idx, group, flat;
+  int shape, vec, idx64, tpo, dst_tc, write_val, write_idx, group, flat, mu, onerun;
   ga_function fn;
   struct rd_variant *next;
 } rd_variant;
@@ -138,11 +138,12 @@ static char *gen_source(const GpuReduction *gr, const rd_variant *v) {
   ga_strb_printf(&sb, "#define GA_RD_KIND %d\n#define GA_RD_ISFLOAT %d\n#define GA_RD_WRITE_VAL %d\n"
                       "#define GA_RD_WRITE_IDX %d\n#define GA_RD_IDX_T %s\n#define GA_RD_VEC %d\n"
                       "#define GA_RD_THREADS %d\n#define GA_RD_TPO %d\n"
-                      "#define GA_RD_BY %d\n#define GA_RD_GROUP %d\n#define GA_RD_FLAT %d\n#define %s\n"
+                      "#define GA_RD_BY %d\n#define GA_RD_GROUP %d\n#define GA_RD_FLAT %d\n"
+                      "#define GA_RD_MU %d\n#define GA_RD_ONERUN %d\n#define %s\n"
                       "#include \"ga_reduce.cuh\"\n",
                  gr->kind, tc_is_float(gr->src_tc), v->write_val, v->write_idx,
                  v->idx64 ? "unsigned long long" : "unsigned int", v->vec, RD_THREADS, v->tpo,
-                 RD_BY, v->group ? v->group : RD_THREADS, v->flat,
+                 RD_BY, v->group ? v->group : RD_THREADS, v->flat, v->mu ? v->mu : 1, v->onerun,
                  v->shape == SHAPE_ROWS   ? "GA_RD_BUILD_ROWS"
                  : v->shape == SHAPE_COLS ? "GA_RD_BUILD_COLS"
                                           : "GA_RD_BUILD_GENERAL");
@@ -162,7 +163,8 @@ static rd_variant *get_variant(GpuReduction *gr, const rd_variant *want, int *er
     if (v->shape == want->shape && v->vec == want->vec && v->idx64 == want->idx64 &&
         v->tpo == want->tpo && v->dst_tc == want->dst_tc &&
         v->write_val == want->write_val && v->write_idx == want->write_idx &&
-        v->group == want->group && v->flat == want->flat)
+        v->group == want->group && v->flat == want->flat && v->mu == want->mu &&
+        v->onerun == want->onerun)
       return v;
   v = malloc(sizeof(*v));
   if (v == NULL) {
@@ -206,7 +208,10 @@ GPUARRAY_PUBLIC char *gpuarray_b200_reduction_source(int op, int src_tc, int dst
   v.vec = vec;
   v.idx64 = idx64;
   v.tpo = tpo;
-  v.group = group;
+  v.group = group & 0xffff; /* bits 16-19: runs at once, bit 20: one-run mode, bit 21: flattened */
+  v.mu = (group >> 16) & 0xf;
+  v.onerun = (group >> 20) & 1;
+  v.flat = (group >> 21) & 1;
   v.dst_tc = dst_tc;
   v.write_val = op_writes_val(gr.op);
   v.write_idx = op_writes_idx(gr.op);
@@ -423,8 +428,11 @@ static int all_multiple(const long long *v, unsigned n, long long m) {
   return 1;
 }
 
-/* Tuning for experiments: GPUARRAY_B200_RD="ctas_per_sm,seg_vectors,warp_item_bytes". */
+/* Tuning for experiments: GPUARRAY_B200_RD="ctas_per_sm,seg_vectors,cta_min_vectors,
+ * cols_ctas_per_sm,onerun_ctas_per_sm,onerun_loads_per_lane,onerun_outputs_at_once". The
+ * defaults are the best of sweeps on a B200. */
 static unsigned rd_cols_ctas_per_sm = 3;
+static unsigned rd_onerun_ctas_per_sm = 3, rd_onerun_lpl = 4, rd_onerun_mu = 0;
 
 static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_bytes) {
   static int parsed = 0;
@@ -433,7 +441,8 @@ static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_
   if (!parsed) {
     const char *env = getenv("GPUARRAY_B200_RD");
     if (env != NULL)
-      sscanf(env, "%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm);
+      sscanf(env, "%u,%u,%u,%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm,
+             &rd_onerun_ctas_per_sm, &rd_onerun_lpl, &rd_onerun_mu);
     if (rd_cols_ctas_per_sm == 0) rd_cols_ctas_per_sm = 3;
     *warp_bytes = t_warp;
     if (t_ctas == 0) t_ctas = 32;
@@ -531,7 +540,7 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
   L.splits = 1;
 
   if (L.nr_total > 0 && L.nr >= 1 && L.rsrc[L.nr - 1] == (long long)elsize &&
-      L.rdim[L.nr - 1] >= 512) {
+      L.rdim[L.nr - 1] >= 2) {
     /* --- contiguous reduced run --- */
     unsigned vec = (unsigned)(16 / elsize);
     unsigned long long rows_outer = L.nr_total / L.rdim[L.nr - 1];
@@ -549,16 +558,47 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
        *  - few outputs: split the reduced extent (CTAs when the runs are long
        *    and the outputs very few, which also keeps the partial count low). */
       int need_split = 0;
-      want.flat = nvrow < 64;
+      /* loads one lane of a warp issues per run: short runs need help to keep
+       * enough bytes in flight (see the kernel's comment) */
+      unsigned long long nload = nvrow + (L.inner % (unsigned)want.vec != 0);
+      if (rows_outer == 1 && nload <= 256) {
+        unsigned g = 1, lpl;
+        while (g < 32 && g * rd_onerun_lpl < nload) g *= 2;
+        lpl = (unsigned)((nload + g - 1) / g);
+        want.onerun = 1;
+        want.group = (int)g;
+        want.mu = rd_onerun_mu ? (int)rd_onerun_mu : lpl <= 2 ? 4 : 2;
+        L.seg = L.inner;
+        L.nseg = 1;
+        L.units = 1;
+        gpb = RD_THREADS / g;
+        blocks = (L.nf_total + (unsigned long long)gpb * (unsigned)want.mu - 1) /
+                 ((unsigned long long)gpb * (unsigned)want.mu);
+        if (rd_onerun_ctas_per_sm && blocks > (unsigned long long)ctx->num_sms * rd_onerun_ctas_per_sm)
+          blocks = (unsigned long long)ctx->num_sms * rd_onerun_ctas_per_sm;
+        grid[0] = (unsigned)blocks;
+        goto rows_done;
+      }
+      want.flat = nvrow < 16;
+      want.mu = want.flat ? 1 : nload <= 64 ? 4 : nload <= 256 ? 2 : 1;
       if (nvrow >= cta_min_vecs) want.group = RD_THREADS;
       else if (L.nf_total >= (unsigned long long)ctx->num_sms * 16) want.group = 32;
       else if (L.nf_total >= (unsigned long long)ctx->num_sms * 4 && nvrow >= 1024)
         want.group = RD_THREADS;
       else {
+        /* warps, unless long runs would leave them either too few or with
+         * shares too short to be worth a ticket (see the cap below) */
+        unsigned long long s_w = ((unsigned long long)target * (RD_THREADS / 32) + L.nf_total - 1) /
+                                 L.nf_total;
+        unsigned long long cap_w = L.nr_total * elsize / (24u << 10);
+        if (cap_w < 1) cap_w = 1;
+        if (s_w > cap_w) s_w = cap_w;
         need_split = 1;
-        want.group = (nvrow >= 2048 && L.nf_total < (unsigned long long)ctx->num_sms) ? RD_THREADS : 32;
+        want.group = (nvrow >= 2048 && (L.nf_total < (unsigned long long)ctx->num_sms ||
+                                        L.nf_total * s_w < (unsigned long long)ctx->num_sms * 16))
+                         ? RD_THREADS : 32;
       }
-      if (want.group == RD_THREADS && want.flat) want.flat = 0;
+      if (want.group == RD_THREADS) want.flat = 0, want.mu = 1;
       gpb = RD_THREADS / (unsigned)want.group;
       /* measured on B200: whole-CTA groups run best as a few long-lived CTAs
        * per SM, warp groups as many (a full complement of resident warps) */
@@ -578,11 +618,18 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
           }
         }
         s = (groups_target + L.nf_total - 1) / L.nf_total;
+        if (want.group == 32) {
+          /* measured on B200: a warp's share should stay above ~24 KiB, or the
+           * ramp of each share and the ticketed finish outweigh the parallelism */
+          unsigned long long cap = L.nr_total * elsize / (24u << 10);
+          if (cap < 1) cap = 1;
+          if (s > cap) s = cap;
+        }
         if (s > L.units) s = L.units;
         if (s > 1u << 20) s = 1u << 20;
         L.splits = s ? s : 1;
       }
-      if (L.seg >= 0xffffffffULL) {
+      if (L.seg >= 0x7fffffffULL) {
         /* a single run longer than 32-bit indexing: cut it even without splitting */
         L.seg = (unsigned long long)want.group * vec * seg_vecs * 1024;
         L.nseg = (L.inner + L.seg - 1) / L.seg;
@@ -595,6 +642,7 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
       nwork = L.nf_total * L.splits;
       blocks = (nwork + gpb - 1) / gpb;
       grid[0] = blocks > 0x7fffffffULL ? 0x7fffffffu : (unsigned)blocks;
+    rows_done:;
     }
   } else if (L.nr_total > 0 && L.nf >= 1 && L.fsrc[L.nf - 1] == (long long)elsize &&
              L.fdim[L.nf - 1] >= 16) {

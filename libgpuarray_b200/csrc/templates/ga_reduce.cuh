@@ -43,6 +43,13 @@
  */
 #include "cluda.h"
 
+#ifndef GA_RD_MU
+#define GA_RD_MU 1 /* rows: runs (or, with GA_RD_ONERUN, outputs) a group loads from at once */
+#endif
+#ifndef GA_RD_ONERUN
+#define GA_RD_ONERUN 0 /* rows: every output is one short contiguous run and nothing is split */
+#endif
+
 #define GA_RD_MAXD 8
 typedef unsigned long long ga__u64;
 typedef long long ga__i64;
@@ -131,10 +138,12 @@ static __device__ __forceinline__ T ga__shfl_down(const T v, const int delta) {
   }
 }
 
-/* result valid in lane 0; lanes combine in a fixed order */
-static __device__ __forceinline__ ga__state ga__warp_reduce(ga__state s) {
+/* W adjacent lanes (W a power of two, aligned) combine in a fixed order; the
+ * result is valid in the first of them */
+template <int W>
+static __device__ __forceinline__ ga__state ga__lanes_reduce(ga__state s) {
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) {
+  for (int d = W / 2; d > 0; d >>= 1) {
     ga__state t;
     t.v = ga__shfl_down(s.v, d);
 #if GA_RD_KIND == 1
@@ -143,6 +152,11 @@ static __device__ __forceinline__ ga__state ga__warp_reduce(ga__state s) {
     ga__merge(s, t);
   }
   return s;
+}
+
+/* result valid in lane 0 */
+static __device__ __forceinline__ ga__state ga__warp_reduce(ga__state s) {
+  return ga__lanes_reduce<32>(s);
 }
 
 /* result valid in thread 0 of the CTA; `sm` holds one state per warp */
@@ -163,6 +177,16 @@ static __device__ __forceinline__ ga__state ga__block_reduce(ga__state s, ga__st
 static __device__ __forceinline__ ga__i64 ga__foff(const ga__rd_layout &L, const ga__i64 *str,
                                                    ga__u64 o) {
   ga__i64 off = 0;
+  if (L.nf_total <= 0xffffffffULL) { /* 32-bit division is several times cheaper */
+    unsigned int o32 = (unsigned int)o;
+    for (int d = (int)L.nf - 1; d > 0; d--) {
+      const unsigned int fd = (unsigned int)L.fdim[d], q = o32 / fd;
+      off += (ga__i64)(o32 - q * fd) * str[d];
+      o32 = q;
+    }
+    if (L.nf > 0) off += (ga__i64)o32 * str[0];
+    return off;
+  }
   for (int d = (int)L.nf - 1; d > 0; d--) {
     const ga__u64 q = o / L.fdim[d];
     off += (ga__i64)(o - q * L.fdim[d]) * str[d];
@@ -210,6 +234,40 @@ static __device__ __forceinline__ T ga__ldcg(const T *p) {
     memcpy(&r, &w, 8);
   }
   return r;
+}
+
+/* N bytes from L2, N a multiple of the alignment of p, in the widest pieces */
+template <int N>
+static __device__ __forceinline__ void ga__ldcg_block(void *dst, const void *p) {
+  if (N % 16 == 0) {
+#pragma unroll
+    for (int i = 0; i < N / 16; i++) {
+      const uint4 w = __ldcg(reinterpret_cast<const uint4 *>(p) + i);
+      memcpy(static_cast<char *>(dst) + 16 * i, &w, 16);
+    }
+  } else if (N % 8 == 0) {
+#pragma unroll
+    for (int i = 0; i < N / 8; i++) {
+      const uint2 w = __ldcg(reinterpret_cast<const uint2 *>(p) + i);
+      memcpy(static_cast<char *>(dst) + 8 * i, &w, 8);
+    }
+  } else if (N % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < N / 4; i++) {
+      const unsigned int w = __ldcg(reinterpret_cast<const unsigned int *>(p) + i);
+      memcpy(static_cast<char *>(dst) + 4 * i, &w, 4);
+    }
+  } else if (N % 2 == 0) {
+#pragma unroll
+    for (int i = 0; i < N / 2; i++) {
+      const unsigned short w = __ldcg(reinterpret_cast<const unsigned short *>(p) + i);
+      memcpy(static_cast<char *>(dst) + 2 * i, &w, 2);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; i++)
+      static_cast<unsigned char *>(dst)[i] = __ldcg(reinterpret_cast<const unsigned char *>(p) + i);
+  }
 }
 
 static __device__ __forceinline__ void ga__put_partial(const ga__rd_layout &L, GA_RD_ACC_T *pval,
@@ -284,8 +342,21 @@ static __device__ __forceinline__ void ga__row_decode(const ga__rd_layout &L, co
  * per unit: a CTA for long runs, a warp for runs of a few KiB. With
  * GA_RD_FLAT (very short runs) the (run, vector) pairs of the whole share are
  * flattened into one index space instead, so that consecutive iterations of
- * a thread touch different runs and their loads overlap. */
-extern "C" __global__ void __launch_bounds__(GA_RD_THREADS)
+ * a thread touch different runs and their loads overlap.
+ *
+ * Runs of a few hundred elements leave a thread with one or two loads per run,
+ * too few to cover DRAM latency. Two remedies, both chosen by the host:
+ * GA_RD_MU > 1 makes a group load from GA_RD_MU runs of its output at once;
+ * GA_RD_ONERUN (each output is a single short run, nothing split) lets groups
+ * be part of a warp (GA_RD_GROUP = 1..32 lanes, sized so that a lane still
+ * sees about two vectors of the run) and has each group work on GA_RD_MU
+ * outputs at once, one accumulator per output. */
+#if GA_RD_MU > 1
+#define GA__RD_ROWS_BOUNDS __launch_bounds__(GA_RD_THREADS, 3) /* room for the extra loads in flight */
+#else
+#define GA__RD_ROWS_BOUNDS __launch_bounds__(GA_RD_THREADS)
+#endif
+extern "C" __global__ void GA__RD_ROWS_BOUNDS
 ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, char *d1,
            GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx, unsigned int *tickets) {
 #if GA_RD_GROUP > 32
@@ -300,6 +371,53 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
   const ga__u64 ngroups = (ga__u64)gridDim.x * (GA_RD_THREADS / GA_RD_GROUP);
   const ga__u64 rounds = (nwork + ngroups - 1) / ngroups;
 
+#if GA_RD_ONERUN
+  {
+    const unsigned int len = (unsigned int)L.inner, nv = len / GA_RD_VEC;
+    for (ga__u64 it = 0; it < rounds; it += GA_RD_MU) {
+      ga__state st[GA_RD_MU];
+      const char *base[GA_RD_MU];
+      ga__u64 w[GA_RD_MU];
+      bool live[GA_RD_MU];
+#pragma unroll
+      for (int k = 0; k < GA_RD_MU; k++) {
+        /* neighbouring groups take neighbouring outputs; a slot past the end
+         * re-reads the last output and drops the result */
+        w[k] = group + (it + (ga__u64)k) * ngroups;
+        live[k] = w[k] < nwork;
+        if (!live[k]) w[k] = nwork - 1;
+        st[k] = ga__init();
+        base[k] = src + ga__foff(L, L.fsrc, w[k]);
+      }
+#pragma unroll 2
+      for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
+        ga__rd_pack<GA_RD_VEC> t[GA_RD_MU];
+#pragma unroll
+        for (int k = 0; k < GA_RD_MU; k++)
+          t[k] = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(base[k])[i];
+#pragma unroll
+        for (int k = 0; k < GA_RD_MU; k++)
+#pragma unroll
+          for (int j = 0; j < GA_RD_VEC; j++)
+            ga__take(st[k], GA_RD_LOAD(t[k].v[j]),
+                     (GA_RD_IDX_T)(i * GA_RD_VEC + (unsigned)j) * imul);
+      }
+      for (unsigned int i = nv * GA_RD_VEC + lane; i < len; i += GA_RD_GROUP) {
+#pragma unroll
+        for (int k = 0; k < GA_RD_MU; k++)
+          ga__take(st[k], GA_RD_LOAD(reinterpret_cast<const GA_RD_SRC_T *>(base[k])[i]),
+                   (GA_RD_IDX_T)i * imul);
+      }
+#pragma unroll
+      for (int k = 0; k < GA_RD_MU; k++) st[k] = ga__lanes_reduce<GA_RD_GROUP>(st[k]);
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < GA_RD_MU; k++)
+          if (live[k]) ga__emit(L, src, d0, d1, w[k], st[k]);
+      }
+    }
+  }
+#else
   for (ga__u64 it = 0; it < rounds; it++) {
     const ga__u64 w = group + it * ngroups;
     const bool live = w < nwork;
@@ -317,7 +435,42 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
       const ga__u64 ub = split * L.units / L.splits, ue = (split + 1) * L.units / L.splits;
       const char *obase = src + ga__foff(L, L.fsrc, o);
 #if !GA_RD_FLAT
-      for (ga__u64 u = ub; u < ue; u++) {
+      ga__u64 u = ub;
+#if GA_RD_MU > 1
+      if (L.nseg == 1) {
+        const unsigned int len = (unsigned int)L.inner, nv = len / GA_RD_VEC;
+        for (; u + GA_RD_MU <= ue; u += GA_RD_MU) {
+          const char *rp[GA_RD_MU];
+          GA_RD_IDX_T fb[GA_RD_MU];
+#pragma unroll
+          for (int k = 0; k < GA_RD_MU; k++) {
+            ga__i64 roff;
+            ga__row_decode(L, nro, u + (ga__u64)k, roff, fb[k]);
+            rp[k] = obase + roff;
+          }
+#pragma unroll 2
+          for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
+            ga__rd_pack<GA_RD_VEC> t[GA_RD_MU];
+#pragma unroll
+            for (int k = 0; k < GA_RD_MU; k++)
+              t[k] = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(rp[k])[i];
+#pragma unroll
+            for (int k = 0; k < GA_RD_MU; k++)
+#pragma unroll
+              for (int j = 0; j < GA_RD_VEC; j++)
+                ga__take(st[j], GA_RD_LOAD(t[k].v[j]),
+                         fb[k] + (GA_RD_IDX_T)(i * GA_RD_VEC + (unsigned)j) * imul);
+          }
+          for (unsigned int i = nv * GA_RD_VEC + lane; i < len; i += GA_RD_GROUP) {
+#pragma unroll
+            for (int k = 0; k < GA_RD_MU; k++)
+              ga__take(st[0], GA_RD_LOAD(reinterpret_cast<const GA_RD_SRC_T *>(rp[k])[i]),
+                       fb[k] + (GA_RD_IDX_T)i * imul);
+          }
+        }
+      }
+#endif
+      for (; u < ue; u++) {
         ga__u64 r = u, g = 0;
         if (L.nseg > 1) {
           r = u / L.nseg;
@@ -332,6 +485,17 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
         fbase += (GA_RD_IDX_T)e0 * imul;
         const unsigned int nv = len / GA_RD_VEC;
         const ga__rd_pack<GA_RD_VEC> *pv = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(p);
+#if GA_RD_MU > 1
+        /* leftover runs of a multi-run variant: short by construction */
+#pragma unroll 4
+        for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
+          const ga__rd_pack<GA_RD_VEC> t = pv[i];
+          const GA_RD_IDX_T f0 = fbase + (GA_RD_IDX_T)(i * GA_RD_VEC) * imul;
+#pragma unroll
+          for (int j = 0; j < GA_RD_VEC; j++)
+            ga__take(st[j], GA_RD_LOAD(t.v[j]), f0 + (GA_RD_IDX_T)j * imul);
+        }
+#else
 #pragma unroll 8
         for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
           const ga__rd_pack<GA_RD_VEC> t = pv[i];
@@ -340,6 +504,7 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
           for (int j = 0; j < GA_RD_VEC; j++)
             ga__take(st[j], GA_RD_LOAD(t.v[j]), f0 + (GA_RD_IDX_T)j * imul);
         }
+#endif
         for (unsigned int i = nv * GA_RD_VEC + lane; i < len; i += GA_RD_GROUP)
           ga__take(st[0], GA_RD_LOAD(p[i]), fbase + (GA_RD_IDX_T)i * imul);
       }
@@ -418,6 +583,7 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
       if (last && lane == 0) ga__emit(L, src, d0, d1, o, fin);
     }
   }
+#endif /* !GA_RD_ONERUN */
 }
 #endif
 
@@ -512,8 +678,14 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
       ga__state tot = sm[0][ty][tx];
 #pragma unroll
       for (int y = 1; y < GA_RD_BY; y++) ga__merge(tot, sm[y][ty][tx]);
-      if (L.splits == 1) ga__emit(L, src, d0, d1, o0 + ty, tot);
-      else ga__put_partial(L, pval, pidx, split, o0 + ty, tot);
+      if (L.splits == 1) {
+        ga__emit(L, src, d0, d1, o0 + ty, tot);
+      } else { /* partials as [split][output]: neighbouring threads, neighbouring cells */
+        pval[split * L.nf_total + o0 + ty] = tot.v;
+#if GA_RD_KIND == 1
+        pidx[split * L.nf_total + o0 + ty] = tot.i;
+#endif
+      }
     }
     if (L.splits > 1) {
       /* all partials of this tile are stored: one ticket per tile */
@@ -528,9 +700,22 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
         if (live) {
 #pragma unroll 4
           for (ga__u64 sp = ty; sp < L.splits; sp += GA_RD_BY) {
+            /* the thread's GA_RD_VEC outputs are adjacent cells: one wide load */
+            GA_RD_ACC_T pv[GA_RD_VEC];
+            ga__ldcg_block<(int)(GA_RD_VEC * sizeof(GA_RD_ACC_T))>(pv, &pval[sp * L.nf_total + o0]);
+#if GA_RD_KIND == 1
+            GA_RD_IDX_T pi[GA_RD_VEC];
+            ga__ldcg_block<(int)(GA_RD_VEC * sizeof(GA_RD_IDX_T))>(pi, &pidx[sp * L.nf_total + o0]);
+#endif
 #pragma unroll
-            for (int k = 0; k < GA_RD_VEC; k++)
-              ga__merge(fin[k], ga__get_partial(L, pval, pidx, sp, o0 + k));
+            for (int k = 0; k < GA_RD_VEC; k++) {
+              ga__state t;
+              t.v = pv[k];
+#if GA_RD_KIND == 1
+              t.i = pi[k];
+#endif
+              ga__merge(fin[k], t);
+            }
           }
         }
         __syncthreads(); /* sm still holds this tile's first-stage states */

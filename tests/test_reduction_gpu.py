@@ -240,6 +240,58 @@ def test_kernel_paths(api, ctx, oracle, rng, shape, axes, name):
                  out_dtype=np.bool_ if name == "any" else None)
 
 
+SHAPES_SHORT_RUNS = [
+    # one short contiguous run per output: part of a warp per output, several outputs at once
+    ((1000, 2), [1]), ((999, 3), [1]), ((777, 4), [1]), ((1500, 8), [1]), ((700, 16), [1]),
+    ((1201, 32), [1]), ((33, 49), [1]), ((260, 64), [1]), ((300, 100), [1]), ((130, 256), [1]),
+    ((67, 511), [1]), ((70, 512), [1]), ((35, 1000), [1]), ((40, 1024), [1]), ((5, 7, 48), [2]),
+    ((6, 5, 7, 7), [2, 3]), ((1, 20), [1]), ((9000, 12), [1]),
+    # several short runs per output: a warp loads from a few runs at once
+    ((50, 6, 256), [0, 2]), ((41, 5, 100), [0, 2]), ((23, 4, 64), [2, 0]), ((37, 3, 20), [0, 2]),
+    ((64, 9, 7, 7), [0, 2, 3]), ((19, 2, 600), [0, 2]), ((300, 2, 8), [0, 2]),
+]
+
+
+# float32 on every shape; the other element sizes (2, 8 and 1 bytes: other vector
+# widths and group sizes) on every third shape, which keeps the number of kernels
+# the suite has to compile in check
+SHORT_RUN_CASES = [(sh, ax, np.float32) for sh, ax in SHAPES_SHORT_RUNS] + \
+                  [(sh, ax, dt) for i, (sh, ax) in enumerate(SHAPES_SHORT_RUNS)
+                   for dt in (np.float16, np.float64, np.int8) if i % 3 == 0]
+
+
+@pytest.mark.parametrize("shape,axes,dt", SHORT_RUN_CASES)
+def test_short_contiguous_runs(api, ctx, oracle, rng, shape, axes, dt):
+    x = make_data(rng, dt, shape)
+    sum_out = np.int64 if dt == np.int8 else None
+    check_reduce(api, ctx, oracle, "sum", x, axes, out_dtype=sum_out)
+    check_reduce(api, ctx, oracle, "maxandargmax", x, axes)
+    check_reduce(api, ctx, oracle, "argmin", x, axes)
+    if len(shape) == 2:
+        # rows that do not start on a 16-byte boundary, and a padded row pitch
+        check_reduce(api, ctx, oracle, "sum", x, axes, out_dtype=sum_out, layout="window")
+        check_reduce(api, ctx, oracle, "maxandargmax", x, axes, layout="window")
+        wide = np.zeros((shape[0], shape[1] + 8), np.dtype(dt))
+        wide[:, :shape[1]] = x
+        g = api.GpuArray.from_numpy(ctx, wide)[:, :shape[1]]
+        d0 = api.GpuArray.empty(ctx, (shape[0],), np.dtype(dt))
+        d1 = api.GpuArray.empty(ctx, (shape[0],), np.int64)
+        api.GpuReduction(ctx, api.GA_REDUCE_MAXANDARGMAX, np.dtype(dt))(d0, d1, g, [1])
+        want_v, want_i = oracle.minmaxarg(x, [1])
+        assert d0.to_numpy().tobytes() == want_v.tobytes() and (d1.to_numpy() == want_i).all()
+
+
+def test_short_runs_nan_first_and_ties(api, ctx, oracle):
+    x = np.full((500, 24), 1.5, np.float32)
+    x[7, 0] = np.nan          # NaN as first element is kept, elsewhere it never wins
+    x[8, 5] = np.nan
+    x[9, 23] = 3.0
+    x[10, :] = -0.0
+    x[10, 3] = 0.0
+    for name in ("maxandargmax", "minandargmin"):
+        check_reduce(api, ctx, oracle, name, x, [1])
+
+
 @pytest.mark.parametrize("shape,axes", [((5, 4100), [1]), ((2100, 36), [0]), ((30, 7, 600), [0, 2])])
 def test_kernel_paths_fp64_and_fp16(api, ctx, oracle, rng, shape, axes):
     for dt in (np.float64, np.float16):
