@@ -677,6 +677,7 @@ int GpuArray_take1(GpuArray *a, const GpuArray *v, const GpuArray *i, int check_
   err = ga_compile(ctx, ga_strb_cstr(&sb), "ga_take1", NULL, &fn, NULL);
   ga_strb_free(&sb);
   if (err != GA_NO_ERROR) return err;
+  fn.dependent_ok = 1;
 
   blob[0] = n0;
   blob[1] = n1;

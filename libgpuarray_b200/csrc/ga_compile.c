@@ -223,6 +223,7 @@ int ga_compile(gpucontext *ctx, const char *src, const char *fname, const char *
     ctx->modules = m;
   }
 
+  out->dependent_ok = 0;
   ga_ctx_enter(ctx);
   r = ga_cu.p_cuModuleGetFunction(&out->f, m->mod, fname);
   if (r != CUDA_SUCCESS) err = ga_err_cuda(ctx->err, "cuModuleGetFunction", r);
@@ -250,6 +251,16 @@ static unsigned long long launch_counter = 0;
 /* Number of kernels this library has launched in the process so far. */
 GPUARRAY_PUBLIC unsigned long long gpuarray_b200_launch_count(void) { return launch_counter; }
 
+/* GPUARRAY_B200_NO_PDL=1 falls back to fully serialized launches. */
+static int dependent_launch_enabled(void) {
+  static int state = -1;
+  if (state < 0) {
+    const char *env = getenv("GPUARRAY_B200_NO_PDL");
+    state = !(env != NULL && env[0] != '\0' && env[0] != '0');
+  }
+  return state;
+}
+
 int ga_launch(gpucontext *ctx, const ga_function *fn, const unsigned grid[3],
               const unsigned block[3], size_t shared, void **params) {
   CUresult r;
@@ -262,8 +273,27 @@ int ga_launch(gpucontext *ctx, const ga_function *fn, const unsigned grid[3],
       return ga_err_cuda(ctx->err, "cuFuncSetAttribute", r);
     }
   }
-  r = ga_cu.p_cuLaunchKernel(fn->f, grid[0], grid[1], grid[2], block[0], block[1], block[2],
-                             (unsigned)shared, ctx->s, params, NULL);
+  if (fn->dependent_ok && dependent_launch_enabled()) {
+    /* programmatic dependent launch: the kernel may become resident while the
+     * previous kernel of the stream drains; it waits for it before touching
+     * memory (ga__grid_dependency_sync in the templates) */
+    CUlaunchConfig cfg;
+    CUlaunchAttribute attr;
+    memset(&cfg, 0, sizeof(cfg));
+    memset(&attr, 0, sizeof(attr));
+    attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+    attr.value.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDimX = grid[0]; cfg.gridDimY = grid[1]; cfg.gridDimZ = grid[2];
+    cfg.blockDimX = block[0]; cfg.blockDimY = block[1]; cfg.blockDimZ = block[2];
+    cfg.sharedMemBytes = (unsigned)shared;
+    cfg.hStream = ctx->s;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    r = ga_cu.p_cuLaunchKernelEx(&cfg, fn->f, params, NULL);
+  } else {
+    r = ga_cu.p_cuLaunchKernel(fn->f, grid[0], grid[1], grid[2], block[0], block[1], block[2],
+                               (unsigned)shared, ctx->s, params, NULL);
+  }
   ga_ctx_exit(ctx);
   if (r != CUDA_SUCCESS) return ga_err_cuda(ctx->err, "cuLaunchKernel", r);
   launch_counter++;

@@ -167,6 +167,7 @@ static ew_variant *get_variant(GpuElemwise *ge, const ew_variant *want, int *err
     free(v);
     return NULL;
   }
+  v->fn.dependent_ok = 1;
   v->next = ge->variants;
   ge->variants = v;
   return v;

@@ -189,6 +189,7 @@ static rd_variant *get_variant(GpuReduction *gr, const rd_variant *want, int *er
     free(v);
     return NULL;
   }
+  v->fn.dependent_ok = 1;
   v->next = gr->variants;
   gr->variants = v;
   return v;

@@ -98,7 +98,7 @@ GA_HIDDEN uint64_t ga_hash64(const void *data, size_t len, uint64_t seed);
   X(cuMemcpyHtoDAsync) X(cuMemcpyDtoHAsync) X(cuMemcpyDtoDAsync) X(cuMemcpyPeerAsync) \
   X(cuMemsetD8Async)                                                               \
   X(cuModuleLoadData) X(cuModuleUnload) X(cuModuleGetFunction)                     \
-  X(cuFuncGetAttribute) X(cuFuncSetAttribute) X(cuLaunchKernel)                    \
+  X(cuFuncGetAttribute) X(cuFuncSetAttribute) X(cuLaunchKernel) X(cuLaunchKernelEx) \
   X(cuOccupancyMaxActiveBlocksPerMultiprocessor)                                   \
   X(cuEventCreate) X(cuEventRecord) X(cuEventSynchronize) X(cuEventElapsedTime)    \
   X(cuEventDestroy)                                                                \
@@ -205,6 +205,8 @@ typedef struct ga_function {
   int max_threads;                 /* CU_FUNC_ATTRIBUTE_MAX_THREADS_PER_BLOCK */
   int num_regs;
   int static_smem;
+  int dependent_ok;                /* the kernel calls ga__grid_dependency_sync() before it
+                                      touches memory: may launch with serialization relaxed */
 } ga_function;
 
 /* Names of the in-library header files handed to NVRTC ("cluda.h", the

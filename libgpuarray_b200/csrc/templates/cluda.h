@@ -161,4 +161,15 @@ static __device__ __forceinline__ ga_half atom_xchg_eg(ga_half *p, ga_half v) {
 #define atom_add_el(a, b) atom_add_eg(a, b)
 #define atom_xchg_el(a, b) atom_xchg_eg(a, b)
 
+/* Programmatic dependent launch (sm_90 and later). A kernel that the library
+ * launches with stream serialization relaxed may become resident while its
+ * predecessor in the stream is still draining; it must call this before its
+ * first access to global memory, which then waits until the predecessor has
+ * completed and its writes are visible. Releasing right after lets the
+ * successor do the same with us. Both are no-ops under an ordinary launch. */
+static __device__ __forceinline__ void ga__grid_dependency_sync() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 #endif /* CLUDA_H */

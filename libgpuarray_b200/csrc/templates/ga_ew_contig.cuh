@@ -35,6 +35,7 @@
 
 extern "C" __global__ void __launch_bounds__(GA_EW_THREADS)
 ga_ew_contig(const size_t n GA_EW_ARRAYS(GA__P_ARR) GA_EW_SCALARS(GA__P_SC)) {
+  ga__grid_dependency_sync();
   const GA_EW_IDX nvec = (GA_EW_IDX)(n / GA_EW_EPT);
   const GA_EW_IDX nthr = (GA_EW_IDX)gridDim.x * GA_EW_THREADS;
   const GA_EW_IDX tid = (GA_EW_IDX)blockIdx.x * GA_EW_THREADS + threadIdx.x;

@@ -74,6 +74,7 @@ struct ga__ew_layout {
 extern "C" __global__ void __launch_bounds__(GA_EW_THREADS)
 ga_ew_strided(const __grid_constant__ ga__ew_layout L
               GA_EW_ARRAYS(GA__P_ARR) GA_EW_SCALARS(GA__P_SC)) {
+  ga__grid_dependency_sync();
   const GA_EW_IDX nchunks = (GA_EW_IDX)L.nchunks;
   const GA_EW_IDX W_ = (GA_EW_IDX)L.inner;
   const GA_EW_IDX nthr = (GA_EW_IDX)gridDim.x * GA_EW_THREADS;

@@ -178,6 +178,7 @@ extern "C" __global__ void __launch_bounds__(GA_EW_THREADS)
 ga_ew_transpose(const __grid_constant__ ga__ewt_layout L
                 GA_EW_ARRAYS(GA__P_ARR) GA_EW_SCALARS(GA__P_SC)) {
   GA_EW_ARRAYS(GA__SMEM)
+  ga__grid_dependency_sync();
   const unsigned long long ntiles = L.tiles_p * L.tiles_q * L.nouter;
   constexpr int QG = GA_EW_TQ / GA_EW_EPT; /* Q chunks per tile */
   constexpr int PG = GA_EW_TP / GA_EW_PWI; /* P groups per tile */

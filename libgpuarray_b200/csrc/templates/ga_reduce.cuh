@@ -359,6 +359,7 @@ static __device__ __forceinline__ void ga__row_decode(const ga__rd_layout &L, co
 extern "C" __global__ void GA__RD_ROWS_BOUNDS
 ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, char *d1,
            GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx, unsigned int *tickets) {
+  ga__grid_dependency_sync();
 #if GA_RD_GROUP > 32
   __shared__ ga__state sm[32];
   __shared__ int sm_last;
@@ -592,6 +593,7 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
 extern "C" __global__ void __launch_bounds__(32 * GA_RD_BY)
 ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, char *d1,
            GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx, unsigned int *tickets) {
+  ga__grid_dependency_sync();
   __shared__ ga__state sm[GA_RD_BY][GA_RD_VEC][32];
   __shared__ int sm_last;
   const unsigned tx = threadIdx.x, ty = threadIdx.y;
@@ -741,6 +743,7 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
 extern "C" __global__ void __launch_bounds__(GA_RD_THREADS)
 ga_rd_general(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, char *d1,
               GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx, unsigned int *tickets) {
+  ga__grid_dependency_sync();
 #if GA_RD_TPO > 32
   __shared__ ga__state sm[32];
 #endif

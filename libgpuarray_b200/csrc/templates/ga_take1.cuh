@@ -19,6 +19,7 @@ struct ga__tk_layout {
 extern "C" __global__ void __launch_bounds__(256)
 ga_take1(const __grid_constant__ ga__tk_layout L, GA_TK_R_T *r, const char *v,
          const GA_TK_I_T *ind, int *err) {
+  ga__grid_dependency_sync();
   for (unsigned long long i0 = blockIdx.y; i0 < L.n0; i0 += gridDim.y) {
     long long row = (long long)ind[i0];
     if (row < 0) row += (long long)L.dims[0];

@@ -404,3 +404,38 @@ def test_guard_bands_untouched(api, ctx, rng):
     back = g.to_numpy()
     assert (back[:1000] == 0x7B).all() and (back[1999:] == 0x7B).all()
     assert (back[1000:1999] == a.to_numpy() + 1).all()
+
+
+def test_back_to_back_producer_consumer_chains(api, ctx, rng):
+    """Kernels are launched with stream serialization relaxed (programmatic
+    dependent launch): each may become resident while its predecessor drains
+    and waits for it before touching memory. A chain in which every kernel
+    consumes what the previous one produced must still see complete inputs."""
+    n = (1 << 22) + 77
+    a = rng.integers(-1000, 1000, n).astype(np.int32)
+    bufs = [api.GpuArray.from_numpy(ctx, a), api.GpuArray.empty(ctx, (n,), np.int32)]
+    inc = api.GpuElemwise(ctx, "o = a + k", [("a", np.int32, api.GE_READ), ("k", np.int32, api.GE_SCALAR),
+                                              ("o", np.int32, api.GE_WRITE)], nd=1)
+    tot = api.GpuArray.empty(ctx, (), np.int64)
+    rsum = api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.int32)
+    sums = []
+    steps = 40
+    for i in range(steps):
+        inc(bufs[i % 2], np.int32(i + 1), bufs[(i + 1) % 2])
+        if i % 8 == 7:                       # a split reduction in the middle of the chain
+            rsum(tot, None, bufs[(i + 1) % 2], [0])
+            sums.append((i, tot.to_numpy().copy()))
+    final = bufs[steps % 2].to_numpy()
+    assert (final == a + sum(range(1, steps + 1))).all()
+    for i, got in sums:
+        assert int(got) == int(a.astype(np.int64).sum()) + n * sum(range(1, i + 2))
+    # the same split reduction back to back on different inputs: the arrival
+    # counters are handed from one launch to the next
+    xs = [rng.integers(-5, 6, (3, 300000)).astype(np.int32) for _ in range(6)]
+    gx = [api.GpuArray.from_numpy(ctx, x) for x in xs]
+    outs = [api.GpuArray.empty(ctx, (3,), np.int64) for _ in xs]
+    for _ in range(3):
+        for g, o in zip(gx, outs):
+            rsum(o, None, g, [1])
+    for x, o in zip(xs, outs):
+        assert (o.to_numpy() == x.sum(axis=1, dtype=np.int64)).all()
