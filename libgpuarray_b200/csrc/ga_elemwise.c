@@ -24,7 +24,7 @@ typedef struct ew_variant {
   int ept;
   int unroll;
   unsigned int nd;
-  int idx32;
+  int idx32;             /* bit 0: 32-bit element indices; bit 1: 32-bit byte offsets too */
   unsigned long long modes; /* 2 bits per array */
   int tp, tq, pwi;       /* transpose: tile edges, P positions per thread */
   ga_function fn;
@@ -54,18 +54,32 @@ struct _GpuElemwise {
 static int is_array(const gpuelemwise_arg *a) { return ISCLR(a->flags, GE_SCALAR); }
 static int is_output(const gpuelemwise_arg *a) { return ISSET(a->flags, GE_WRITE); }
 
-/* Tuning knobs for experiments: GPUARRAY_B200_EW="threads,unroll,gridcap_per_sm". */
+/* Tuning knobs for experiments: GPUARRAY_B200_EW="unroll,gridcap_per_sm"
+ * (unroll 0 = the default rule). */
 static void ew_tuning(int *unroll, unsigned *gridcap_per_sm) {
-  static int parsed = 0, t_unroll = 4;
+  static int parsed = 0, t_unroll = 0;
   static unsigned t_cap = 0;
   if (!parsed) {
     const char *env = getenv("GPUARRAY_B200_EW");
     if (env != NULL) sscanf(env, "%d,%u", &t_unroll, &t_cap);
-    if (t_unroll < 1 || t_unroll > 8) t_unroll = 4;
+    if (t_unroll < 0 || t_unroll > 8) t_unroll = 0;
     parsed = 1;
   }
   *unroll = t_unroll;
   *gridcap_per_sm = t_cap;
+}
+
+/* Vectors a thread of the contiguous kernel has in flight. Measured on B200:
+ * four for 4- and 8-byte elements; two when a vector holds 8 or 16 narrow
+ * elements, whose unpacked values otherwise cost too many registers (uint8:
+ * 43 us instead of 59 us for 2^27 elements; float16: 19.2 instead of 20.4). */
+static int contig_unroll(const GpuElemwise *ge, int ept) {
+  int u;
+  unsigned cap;
+  ew_tuning(&u, &cap);
+  (void)ge;
+  if (u > 0) return u;
+  return ept >= 8 ? 2 : 4;
 }
 
 /* ---------------------------------------------------------------- codegen */
@@ -97,10 +111,11 @@ static void gen_prologue(const GpuElemwise *ge, ga_strb *sb, const ew_variant *v
   }
   ga_strb_printf(sb,
                  "\n#define GA_EW_EPT %d\n#define GA_EW_UNROLL %d\n#define GA_EW_THREADS %d\n"
-                 "#define GA_EW_IDX %s\n#define GA_EW_IDX32 %d\n#define GA_EW_ND %u\n"
-                 "#define GA_EW_NARR %u\n",
+                 "#define GA_EW_IDX %s\n#define GA_EW_IDX32 %d\n#define GA_EW_OFF32 %d\n"
+                 "#define GA_EW_ND %u\n#define GA_EW_NARR %u\n",
                  v->ept, v->unroll, GA_EW_THREADS, v->idx32 ? "unsigned int" : "size_t",
-                 v->idx32, v->nd ? v->nd : 1, ge->narray ? ge->narray : 1);
+                 v->idx32 & 1, (v->idx32 >> 1) & 1, v->nd ? v->nd : 1,
+                 ge->narray ? ge->narray : 1);
   if (v->kind == 2)
     ga_strb_printf(sb, "#define GA_EW_TP %d\n#define GA_EW_TQ %d\n#define GA_EW_PWI %d\n", v->tp,
                    v->tq, v->pwi > 0 ? v->pwi : 1);
@@ -305,6 +320,7 @@ GpuElemwise *GpuElemwise_new(gpucontext *ctx, const char *preamble, const char *
     want.kind = 0;
     want.ept = ge->ept;
     ew_tuning(&want.unroll, &cap);
+    want.unroll = contig_unroll(ge, want.ept);
     want.idx32 = 1;
     if (get_variant(ge, &want, &err) == NULL) goto fail;
   }
@@ -390,6 +406,7 @@ static int call_contig(GpuElemwise *ge, void **args, size_t n) {
     k++;
   }
   want.ept = aligned ? ge->ept : 1;
+  want.unroll = contig_unroll(ge, want.ept);
   want.idx32 = n < ((size_t)1 << 31);
   v = get_variant(ge, &want, &err);
   if (v == NULL) return err;
@@ -539,6 +556,19 @@ static int call_strided(GpuElemwise *ge, void **args, size_t n, unsigned int nd)
     want.modes |= mode << (2 * k);
     k++;
   }
+  if (want.idx32) {
+    /* 32-bit byte offsets when no argument spans 2 GiB */
+    int small = 1;
+    for (k = 0; k < ge->narray && small; k++) {
+      unsigned long long span = 64;
+      for (j = 0; j < nd; j++) {
+        ssize_t st = ge->strides[k][j];
+        span += (unsigned long long)(ge->dims[j] - 1) * (unsigned long long)(st < 0 ? -st : st);
+      }
+      if (span >= 0x7fffffffULL) small = 0;
+    }
+    if (small) want.idx32 |= 2;
+  }
   v = get_variant(ge, &want, &err);
   if (v == NULL) return err;
 
@@ -569,7 +599,11 @@ static int call_strided(GpuElemwise *ge, void **args, size_t n, unsigned int nd)
 
   blocks = (nchunks + GA_EW_THREADS - 1) / GA_EW_THREADS;
   if (blocks == 0) blocks = 1;
-  if (capsm != 0 && blocks > (size_t)capsm * ctx->num_sms) blocks = (size_t)capsm * ctx->num_sms;
+  /* measured on B200: CTAs that handle a single chunk per thread are bound by
+   * the CTA launch rate when the kernel mostly writes (broadcast of two small
+   * inputs into 134 MB: 35 us uncapped, 21-22 us at 16-32 CTAs per SM) */
+  if (capsm == 0) capsm = 32;
+  if (blocks > (size_t)capsm * ctx->num_sms) blocks = (size_t)capsm * ctx->num_sms;
   if (blocks > 0x7fffffffu) blocks = 0x7fffffffu;
   grid[0] = (unsigned)blocks;
   return ga_launch(ctx, &v->fn, grid, block, 0, ge->params);
@@ -653,8 +687,20 @@ static int call_transpose(GpuElemwise *ge, void **args, size_t n, unsigned int n
    * the staged reads are long contiguous bursts; 64 along Q; shrink until the
    * staged tiles fit the 48 KiB of static shared memory. */
   {
-    int tp = 32, tq = 64;
-    while (tp < 256 && (size_t)tp < ge->dims[pdim_ax]) tp *= 2;
+    int tp = 32, tq = 64, tpmax = 256;
+    /* measured on B200: 256 x 64 for 2-byte staged elements (cfg4: 35.8 us,
+     * 128 x 64: 38.3); 128 x 32 for 4 bytes and more (fp32 8192 x 4096
+     * transpose: 49.0 us, 128 x 64: 53.2) */
+    for (i = 0, k = 0; i < ge->n; i++) {
+      if (!is_array(&ge->args[i])) continue;
+      if (((want.modes >> (2 * k)) & 3) == 3 && gpuarray_get_elsize(ge->args[i].typecode) >= 4) {
+        tpmax = 128;
+        tq = 32;
+      }
+      k++;
+    }
+    if (tq < want.ept) tq = want.ept;
+    while (tp < tpmax && (size_t)tp < ge->dims[pdim_ax]) tp *= 2;
     for (;;) {
       smem = 0;
       for (i = 0, k = 0; i < ge->n; i++) {

@@ -9,6 +9,7 @@
 #define GA_EW_THREADS 256
 #define GA_EW_IDX unsigned int
 #define GA_EW_IDX32 1
+#define GA_EW_OFF32 1
 #define GA_EW_ND 3
 #define GA_EW_NARR 3
 #include "cluda.h"

@@ -13,10 +13,13 @@
  * Byte offsets are always 64-bit.
  *
  * Needs the definitions listed in ga_ew_contig.cuh plus GA_EW_ND,
- * GA_EW_NARR, GA_EW_IDX32 (0/1).
+ * GA_EW_NARR, GA_EW_IDX32 (0/1), GA_EW_OFF32 (0/1).
  */
 #include "ga_ew_common.cuh"
 
+#ifndef GA_EW_OFF32
+#define GA_EW_OFF32 0
+#endif
 #define GA_EW_NOUT ((GA_EW_ND > 1) ? (GA_EW_ND - 1) : 1)
 
 /* Mirrors the block the host marshals in ga_elemwise.c (all 8-byte units). */
@@ -32,9 +35,16 @@ struct ga__ew_layout {
 
 #define GA__P_ARR(k, n, S, C, R, W, M) , char *n##_p
 #define GA__P_SC(n, T) , T n##_s
-#define GA__DECL(k, n, S, C, R, W, M) C n##_c[GA_EW_EPT]; long long n##_off = 0;
-#define GA__STEP(k, n, S, C, R, W, M) n##_off += (long long)pos * L.str[k][d];
-#define GA__STEP0(k, n, S, C, R, W, M) n##_off += (long long)r * L.str[k][0];
+/* byte offset of a row: 32-bit arithmetic when the host found that no argument
+ * spans 2 GiB (one multiply-add per dimension instead of a 64-bit product) */
+#if GA_EW_OFF32
+typedef int ga__ew_off;
+#else
+typedef long long ga__ew_off;
+#endif
+#define GA__DECL(k, n, S, C, R, W, M) C n##_c[GA_EW_EPT]; ga__ew_off n##_off = 0;
+#define GA__STEP(k, n, S, C, R, W, M) n##_off += (ga__ew_off)pos * (ga__ew_off)L.str[k][d];
+#define GA__STEP0(k, n, S, C, R, W, M) n##_off += (ga__ew_off)r * (ga__ew_off)L.str[k][0];
 #define GA__ARG_ARR(k, n, S, C, R, W, M) n##_c[e],
 #define GA__ARG_SC(n, T) n##_s,
 
