@@ -25,7 +25,7 @@
 enum { SHAPE_ROWS = 0, SHAPE_COLS = 1, SHAPE_GENERAL = 2 };
 
 typedef struct rd_variant {
-  int shape, vec, idx64, tpo, dst_tc, write_val, write_idx, group, flat, mu, onerun;
+  int shape, vec, idx64, tpo, dst_tc, write_val, write_idx, group, flat, mu, onerun, fast8;
   ga_function fn;
   struct rd_variant *next;
 } rd_variant;
@@ -139,11 +139,11 @@ static char *gen_source(const GpuReduction *gr, const rd_variant *v) {
                       "#define GA_RD_WRITE_IDX %d\n#define GA_RD_IDX_T %s\n#define GA_RD_VEC %d\n"
                       "#define GA_RD_THREADS %d\n#define GA_RD_TPO %d\n"
                       "#define GA_RD_BY %d\n#define GA_RD_GROUP %d\n#define GA_RD_FLAT %d\n"
-                      "#define GA_RD_MU %d\n#define GA_RD_ONERUN %d\n#define %s\n"
+                      "#define GA_RD_MU %d\n#define GA_RD_ONERUN %d\n#define GA_RD_FAST8 %d\n#define %s\n"
                       "#include \"ga_reduce.cuh\"\n",
                  gr->kind, tc_is_float(gr->src_tc), v->write_val, v->write_idx,
                  v->idx64 ? "unsigned long long" : "unsigned int", v->vec, RD_THREADS, v->tpo,
-                 RD_BY, v->group ? v->group : RD_THREADS, v->flat, v->mu ? v->mu : 1, v->onerun,
+                 RD_BY, v->group ? v->group : RD_THREADS, v->flat, v->mu ? v->mu : 1, v->onerun, v->fast8,
                  v->shape == SHAPE_ROWS   ? "GA_RD_BUILD_ROWS"
                  : v->shape == SHAPE_COLS ? "GA_RD_BUILD_COLS"
                                           : "GA_RD_BUILD_GENERAL");
@@ -164,7 +164,7 @@ static rd_variant *get_variant(GpuReduction *gr, const rd_variant *want, int *er
         v->tpo == want->tpo && v->dst_tc == want->dst_tc &&
         v->write_val == want->write_val && v->write_idx == want->write_idx &&
         v->group == want->group && v->flat == want->flat && v->mu == want->mu &&
-        v->onerun == want->onerun)
+        v->onerun == want->onerun && v->fast8 == want->fast8)
       return v;
   v = malloc(sizeof(*v));
   if (v == NULL) {
@@ -682,6 +682,14 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
     grid[0] = (unsigned)(blocks ? blocks : 1);
   }
 
+  /* whole-word arithmetic on vectors of 1-byte elements (see ga__fold_lanes) */
+  if (elsize == 1 && want.vec % 4 == 0 && want.shape == SHAPE_ROWS) {
+    if (gr->op == GA_REDUCE_SUM && !tc_is_float(want.dst_tc) &&
+        gpuarray_get_elsize(want.dst_tc) >= 4)
+      want.fast8 = gr->src_tc == GA_BYTE ? 1 : 2;
+    else if (gr->op == GA_REDUCE_ANY) want.fast8 = 3;
+    else if (gr->op == GA_REDUCE_ALL) want.fast8 = 4;
+  }
   v1 = get_variant(gr, &want, &err);
   if (v1 == NULL) return err;
   if (L.splits > 1) {

@@ -46,6 +46,10 @@
 #ifndef GA_RD_MU
 #define GA_RD_MU 1 /* rows: runs (or, with GA_RD_ONERUN, outputs) a group loads from at once */
 #endif
+#ifndef GA_RD_FAST8
+#define GA_RD_FAST8 0 /* 1-byte elements folded a 32-bit word at a time: 1 signed sum,
+                         2 unsigned sum, 3 any, 4 all */
+#endif
 #ifndef GA_RD_ONERUN
 #define GA_RD_ONERUN 0 /* rows: every output is one short contiguous run and nothing is split */
 #endif
@@ -312,6 +316,68 @@ struct alignas((sizeof(GA_RD_SRC_T) * N >= 16) ? 16 : sizeof(GA_RD_SRC_T) * N) g
   GA_RD_SRC_T v[N];
 };
 
+#if GA_RD_FAST8
+/* A vector of 1-byte elements folded into ONE state with word arithmetic
+ * instead of element by element: sums with a 4-way byte dot product against
+ * ones (exact: a vector's sum fits 32 bits by far), ANY with an OR of the
+ * words, ALL with the classic has-a-zero-byte test. Same results as the
+ * per-element form; about a tenth of the instructions. */
+static __device__ __forceinline__ void ga__fold_words(ga__state &s,
+                                                      const ga__rd_pack<GA_RD_VEC> &t) {
+  unsigned int w[GA_RD_VEC / 4];
+  memcpy(w, &t, sizeof(w));
+#if GA_RD_FAST8 == 1
+  int acc = 0;
+#pragma unroll
+  for (int i = 0; i < GA_RD_VEC / 4; i++) acc = __dp4a((int)w[i], 0x01010101, acc);
+  s.v = GA_RD_COMBINE(s.v, (GA_RD_ACC_T)acc);
+#elif GA_RD_FAST8 == 2
+  unsigned int acc = 0;
+#pragma unroll
+  for (int i = 0; i < GA_RD_VEC / 4; i++) acc = __dp4a(w[i], 0x01010101u, acc);
+  s.v = GA_RD_COMBINE(s.v, (GA_RD_ACC_T)acc);
+#elif GA_RD_FAST8 == 3
+  unsigned int acc = 0;
+#pragma unroll
+  for (int i = 0; i < GA_RD_VEC / 4; i++) acc |= w[i];
+  s.v = GA_RD_COMBINE(s.v, (GA_RD_ACC_T)(acc != 0));
+#else
+  unsigned int zero = 0;
+#pragma unroll
+  for (int i = 0; i < GA_RD_VEC / 4; i++) zero |= (w[i] - 0x01010101u) & ~w[i] & 0x80808080u;
+  s.v = GA_RD_COMBINE(s.v, (GA_RD_ACC_T)(zero == 0));
+#endif
+}
+#endif
+
+/* element j of a vector into state j (the states are merged at the end) */
+static __device__ __forceinline__ void ga__fold_lanes(ga__state *st,
+                                                      const ga__rd_pack<GA_RD_VEC> &t,
+                                                      const GA_RD_IDX_T f0,
+                                                      const GA_RD_IDX_T imul) {
+#if GA_RD_FAST8
+  ga__fold_words(st[0], t);
+#else
+#pragma unroll
+  for (int j = 0; j < GA_RD_VEC; j++)
+    ga__take(st[j], GA_RD_LOAD(t.v[j]), f0 + (GA_RD_IDX_T)j * imul);
+#endif
+}
+
+/* every element of a vector into one state */
+static __device__ __forceinline__ void ga__fold_one(ga__state &s,
+                                                    const ga__rd_pack<GA_RD_VEC> &t,
+                                                    const GA_RD_IDX_T f0,
+                                                    const GA_RD_IDX_T imul) {
+#if GA_RD_FAST8
+  ga__fold_words(s, t);
+#else
+#pragma unroll
+  for (int j = 0; j < GA_RD_VEC; j++)
+    ga__take(s, GA_RD_LOAD(t.v[j]), f0 + (GA_RD_IDX_T)j * imul);
+#endif
+}
+
 /* ------------------------------------------------------------------ rows */
 #if defined(GA_RD_BUILD_ROWS)
 /* byte offset and flat-index base of reduced "row" r (all reduced dims but the
@@ -398,10 +464,7 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
           t[k] = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(base[k])[i];
 #pragma unroll
         for (int k = 0; k < GA_RD_MU; k++)
-#pragma unroll
-          for (int j = 0; j < GA_RD_VEC; j++)
-            ga__take(st[k], GA_RD_LOAD(t[k].v[j]),
-                     (GA_RD_IDX_T)(i * GA_RD_VEC + (unsigned)j) * imul);
+          ga__fold_one(st[k], t[k], (GA_RD_IDX_T)(i * GA_RD_VEC) * imul, imul);
       }
       for (unsigned int i = nv * GA_RD_VEC + lane; i < len; i += GA_RD_GROUP) {
 #pragma unroll
@@ -457,10 +520,7 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
               t[k] = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(rp[k])[i];
 #pragma unroll
             for (int k = 0; k < GA_RD_MU; k++)
-#pragma unroll
-              for (int j = 0; j < GA_RD_VEC; j++)
-                ga__take(st[j], GA_RD_LOAD(t[k].v[j]),
-                         fb[k] + (GA_RD_IDX_T)(i * GA_RD_VEC + (unsigned)j) * imul);
+              ga__fold_lanes(st, t[k], fb[k] + (GA_RD_IDX_T)(i * GA_RD_VEC) * imul, imul);
           }
           for (unsigned int i = nv * GA_RD_VEC + lane; i < len; i += GA_RD_GROUP) {
 #pragma unroll
@@ -491,19 +551,13 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
 #pragma unroll 4
         for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
           const ga__rd_pack<GA_RD_VEC> t = pv[i];
-          const GA_RD_IDX_T f0 = fbase + (GA_RD_IDX_T)(i * GA_RD_VEC) * imul;
-#pragma unroll
-          for (int j = 0; j < GA_RD_VEC; j++)
-            ga__take(st[j], GA_RD_LOAD(t.v[j]), f0 + (GA_RD_IDX_T)j * imul);
+          ga__fold_lanes(st, t, fbase + (GA_RD_IDX_T)(i * GA_RD_VEC) * imul, imul);
         }
 #else
 #pragma unroll 8
         for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
           const ga__rd_pack<GA_RD_VEC> t = pv[i];
-          const GA_RD_IDX_T f0 = fbase + (GA_RD_IDX_T)(i * GA_RD_VEC) * imul;
-#pragma unroll
-          for (int j = 0; j < GA_RD_VEC; j++)
-            ga__take(st[j], GA_RD_LOAD(t.v[j]), f0 + (GA_RD_IDX_T)j * imul);
+          ga__fold_lanes(st, t, fbase + (GA_RD_IDX_T)(i * GA_RD_VEC) * imul, imul);
         }
 #endif
         for (unsigned int i = nv * GA_RD_VEC + lane; i < len; i += GA_RD_GROUP)
@@ -524,10 +578,7 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
           ga__row_decode(L, nro, ub + ru, roff, fbase);
           const ga__rd_pack<GA_RD_VEC> t = *reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(
               obase + roff + (ga__i64)pv * (ga__i64)(GA_RD_VEC * sizeof(GA_RD_SRC_T)));
-#pragma unroll
-          for (int j = 0; j < GA_RD_VEC; j++)
-            ga__take(st[j], GA_RD_LOAD(t.v[j]),
-                     fbase + (GA_RD_IDX_T)(pv * GA_RD_VEC + (unsigned)j) * imul);
+          ga__fold_lanes(st, t, fbase + (GA_RD_IDX_T)(pv * GA_RD_VEC) * imul, imul);
         }
         if (tail != 0) {
           for (unsigned int idx = lane; idx < nrows * tail; idx += GA_RD_GROUP) {

@@ -211,6 +211,37 @@ def test_all_any(api, ctx, oracle, rng, dt, name):
         check_reduce(api, ctx, oracle, name, x, axes, out_dtype=np.bool_)
 
 
+@pytest.mark.parametrize("shape,axes", [((5, 70000), [1]), ((300017,), [0]), ((1000, 64), [1]),
+                                        ((40, 3, 4096), [0, 2]), ((64, 48), [1]), ((2, 1 << 20), [1])])
+def test_one_byte_elements_fold_by_words(api, ctx, oracle, rng, shape, axes):
+    """Contiguous runs of 1-byte elements are summed / tested a 32-bit word at a
+    time; every byte position and the byte values that stress the word tricks
+    (0x00, 0x01, 0x7f, 0x80, 0xff) must give the per-element answers."""
+    special = np.array([0, 1, 0x7f, 0x80, 0xff], np.uint8)
+    u = special[rng.integers(0, 5, shape)]
+    check_reduce(api, ctx, oracle, "sum", u, axes, out_dtype=np.uint64)
+    check_reduce(api, ctx, oracle, "sum", u, axes, out_dtype=np.int32)
+    check_reduce(api, ctx, oracle, "sum", u.view(np.int8), axes, out_dtype=np.int64)
+    b = rng.random(shape) < 0.5
+    check_reduce(api, ctx, oracle, "sum", b, axes, out_dtype=np.int64)
+    # all / any: mostly-nonzero and mostly-zero data with single exceptions at
+    # every byte position of a word
+    for base, exc in ((0x80, 0), (0xff, 0), (1, 0), (0, 1), (0, 0x80)):
+        x = np.full(shape, base, np.uint8)
+        flat = x.reshape(-1)
+        for pos in range(0, min(flat.size, 4096), 4):
+            if (pos // 4) % 9 == 0:
+                flat[pos + (pos // 36) % 4] = exc
+        flat[-1 - (flat.size // 3) % 4] = exc
+        for name in ("all", "any"):
+            check_reduce(api, ctx, oracle, name, x, axes, out_dtype=np.bool_)
+            check_reduce(api, ctx, oracle, name, x.view(np.int8), axes, out_dtype=np.bool_)
+    for name in ("all", "any"):
+        check_reduce(api, ctx, oracle, name, b, axes, out_dtype=np.bool_)
+        check_reduce(api, ctx, oracle, name, np.ones(shape, np.bool_), axes, out_dtype=np.bool_)
+        check_reduce(api, ctx, oracle, name, np.zeros(shape, np.bool_), axes, out_dtype=np.bool_)
+
+
 def test_bitwise_on_floats_is_refused(api, ctx):
     with pytest.raises(api.GpuArrayException) as ei:
         api.GpuReduction(ctx, api.GA_REDUCE_XOR, np.float32)
