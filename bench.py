@@ -279,6 +279,113 @@ def side_configs(api, ctx, torch, stream, once=False):
     return out
 
 
+def other_shapes(api, ctx, torch, stream):
+    """`--other-shapes`: shapes outside the five named configurations that the
+    same kernels meet in practice (short runs, kept axis in the middle,
+    broadcasts, narrow element types), each 130-270 MB so that one launch
+    exceeds L2, timed like the side configurations: 10 launches back to back
+    behind a memset, CUDA events on the library's stream."""
+    peak, _ = measured_peak()
+    out = {}
+    g = torch.Generator(device="cuda").manual_seed(7)
+    stall_buf = api.GpuArray.empty(ctx, (2 << 30,), np.uint8)
+    npdt = {torch.float32: np.float32, torch.float16: np.float16, torch.float64: np.float64,
+            torch.int8: np.int8, torch.uint8: np.uint8}
+
+    def dev_array(t):
+        return api.GpuArray.from_pointer(ctx, t.data_ptr(), tuple(t.shape), npdt[t.dtype])
+
+    def timed(name, fn, nbytes, reps=10):
+        for _ in range(3):
+            fn()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            stall_buf.memset(0)
+        a.record(stream)
+        for _ in range(reps):
+            fn()
+        b.record(stream)
+        ctx.sync()
+        us = a.elapsed_time(b) * 1e3 / reps
+        out[name] = {"us": round(us, 2), "GB/s": round(nbytes / us / 1e3, 1),
+                     "frac_measured_peak": round(nbytes / us / 1e3 / peak, 3), "bytes": nbytes}
+
+    S, MX, AM, ANY = (api.GA_REDUCE_SUM, api.GA_REDUCE_MAX, api.GA_REDUCE_ARGMAX, api.GA_REDUCE_ANY)
+    reductions = [
+        ("sum f32 (64,256,56,56) over (0,2,3)", (64, 256, 56, 56), [0, 2, 3], torch.float32, S),
+        ("sum f32 (64,56,56,256) over (0,1,2)", (64, 56, 56, 256), [0, 1, 2], torch.float32, S),
+        ("sum f16 (64,256,56,56) over (0,2,3)", (64, 256, 56, 56), [0, 2, 3], torch.float16, S),
+        ("sum f32 (512,512,256) over (0)", (512, 512, 256), [0], torch.float32, S),
+        ("sum f32 (512,512,256) over (1)", (512, 512, 256), [1], torch.float32, S),
+        ("sum f32 (512,512,256) over (2)", (512, 512, 256), [2], torch.float32, S),
+        ("sum f32 (512,512,256) over (0,2)", (512, 512, 256), [0, 2], torch.float32, S),
+        ("max f32 (8192,8192) over (1)", (8192, 8192), [1], torch.float32, MX),
+        ("argmax f32 (8192,8192) over (0)", (8192, 8192), [0], torch.float32, AM),
+        ("sum f32 (2^21,32) over (1)", (1 << 21, 32), [1], torch.float32, S),
+        ("max f32 (2^22,16) over (1)", (1 << 22, 16), [1], torch.float32, MX),
+        ("argmax f32 (2^17,512) over (1)", (1 << 17, 512), [1], torch.float32, AM),
+        ("sum f32 (2^26) all", (1 << 26,), [0], torch.float32, S),
+        ("sum f64 (4096,8192) over (0)", (4096, 8192), [0], torch.float64, S),
+        ("sum i8->i64 (2^28) all", (1 << 28,), [0], torch.int8, S),
+        ("any i8 (2^28) all", (1 << 28,), [0], torch.int8, ANY),
+    ]
+    for name, shape, axes, tdt, op in reductions:
+        if tdt == torch.int8:
+            t = torch.randint(-3, 4, shape, device="cuda", dtype=torch.int8, generator=g)
+        else:
+            t = torch.randn(*shape, device="cuda", generator=g).to(tdt)
+        torch.cuda.synchronize()
+        gx = dev_array(t)
+        free = [s for i, s in enumerate(shape) if i not in axes]
+        r = api.GpuReduction(ctx, op, npdt[tdt])
+        if op == AM:
+            di = api.GpuArray.empty(ctx, free, np.int64)
+            fn = lambda: r(None, di, gx, axes)
+        else:
+            odt = np.bool_ if op == ANY else (np.int64 if tdt == torch.int8 else npdt[tdt])
+            dv = api.GpuArray.empty(ctx, free, odt)
+            fn = lambda: r(dv, None, gx, axes)
+        timed(name, fn, t.numel() * t.element_size())
+        del t, gx
+
+    R, W = api.GE_READ, api.GE_WRITE
+    M, N = 8192, 4096
+    ta = torch.randn(M, N, device="cuda", generator=g)
+    tb = torch.randn(1, N, device="cuda", generator=g)
+    tc = torch.randn(M, 1, device="cuda", generator=g)
+    to = torch.empty(M, N, device="cuda")
+    torch.cuda.synchronize()
+    ga, gb, gc, go = dev_array(ta), dev_array(tb), dev_array(tc), dev_array(to)
+    add = api.GpuElemwise(ctx, "o = a + b", [("a", np.float32, R), ("b", np.float32, R),
+                                             ("o", np.float32, W)], nd=2)
+    scale = api.GpuElemwise(ctx, "o = a * 2.0f", [("a", np.float32, R), ("o", np.float32, W)], nd=2)
+    timed("o = a + b, b a row (1,N) broadcast, f32 (8192,4096)", lambda: add(ga, gb, go, flags=api.GE_BROADCAST), 8 * M * N)
+    timed("o = a + b, b a column (M,1) broadcast", lambda: add(ga, gc, go, flags=api.GE_BROADCAST), 8 * M * N)
+    gt = ga.transpose((1, 0))
+    got = dev_array(torch.empty(N, M, device="cuda"))
+    timed("o = 2a, a the transposed view, f32", lambda: scale(gt, got), 8 * M * N)
+    t3a = torch.randn(64, 1, 1024, device="cuda", generator=g)
+    t3b = torch.randn(1, 512, 1, device="cuda", generator=g)
+    t3o = torch.empty(64, 512, 1024, device="cuda")
+    torch.cuda.synchronize()
+    g3a, g3b, g3o = dev_array(t3a), dev_array(t3b), dev_array(t3o)
+    timed("o = a + b, (64,1,1024) + (1,512,1) -> (64,512,1024) f32 (write only)",
+          lambda: add(g3a, g3b, g3o, flags=api.GE_BROADCAST), 4 * 64 * 512 * 1024)
+    tu = torch.randint(0, 255, (1 << 27,), device="cuda", dtype=torch.uint8, generator=g)
+    tuo = torch.empty(1 << 27, device="cuda", dtype=torch.uint8)
+    th = torch.randn(1 << 25, device="cuda", generator=g).half()
+    tho = torch.empty(1 << 25, device="cuda", dtype=torch.float16)
+    torch.cuda.synchronize()
+    gu, guo, gh, gho = dev_array(tu), dev_array(tuo), dev_array(th), dev_array(tho)
+    inc8 = api.GpuElemwise(ctx, "o = a + 1", [("a", np.uint8, R), ("o", np.uint8, W)], nd=1)
+    sc16 = api.GpuElemwise(ctx, "o = a * 2.0f", [("a", np.float16, R), ("o", np.float16, W)], nd=1,
+                           convert_f16=True)
+    timed("o = a + 1, uint8 2^27 contiguous", lambda: inc8(gu, guo), 2 * (1 << 27))
+    timed("o = 2a, float16 2^25 contiguous", lambda: sc16(gh, gho), 4 * (1 << 25))
+    return out
+
+
 def cfg5_sharded(api, ctx, torch, dist, stream, rank, world):
     """fp64 (2048, 1024, 1024): each rank owns 2048/world leading planes, reduces
     them to a partial of the final shape and one gpucomm all-reduce (NCCL on the
@@ -490,6 +597,8 @@ def run_ours(args, rank, world, local_rank):
             line["configs"] = side_configs(api, ctx, torch, stream, once=args.side_once)
         except Exception as e:
             line["configs"] = {"error": str(e)[:300]}
+    if world == 1 and args.other_shapes:
+        line["other_shapes"] = other_shapes(api, ctx, torch, stream)
     emit(line)
     if world > 1:
         dist.destroy_process_group()
@@ -498,7 +607,7 @@ def run_ours(args, rank, world, local_rank):
 # dram__bytes_read.sum + dram__bytes_write.sum of one 16384-row ga_rd_rows
 # launch: 4 x the 4096-row ncu capture summarised in
 # profiles/ga_rd_rows_cfg3_maxandargmax.md (traffic is proportional to rows).
-TRAFFIC_BYTES_PER_LAUNCH = 2126280704
+TRAFFIC_BYTES_PER_LAUNCH = 2132034560
 
 
 _REAL_STDOUT = None
@@ -535,6 +644,9 @@ def main():
                     help="profiler captures: run every side config exactly once, cfg5 on 128 planes")
     ap.add_argument("--no-clocks", action="store_true",
                     help="skip the nvidia-smi sampling window (profiler captures)")
+    ap.add_argument("--other-shapes", action="store_true",
+                    help="also time reductions and elementwise calls on shapes outside the five "
+                         "named configurations (adds an `other_shapes` object to the line)")
     ap.add_argument("--cfg5-sharded", action="store_true",
                     help="with N > 1: also time fp64 (2048,1024,1024) SUM / MIN / MAX with the "
                          "reduced leading axis sharded and one gpucomm all-reduce per result")
