@@ -139,6 +139,45 @@ def test_reduction_templates_compile_for_sm100a(api, op, shape):
     assert err == 0 and size > 0, log
 
 
+ROWS_VARIANTS = [
+    # (op, src typecode name, dst typecode name, vec, group | runs-at-once << 16 | one-run << 20 | flat << 21)
+    ("SUM", "GA_FLOAT", "GA_FLOAT", 4, 8 | 4 << 16 | 1 << 20),        # 8 lanes per output, 4 outputs at once
+    ("MAXANDARGMAX", "GA_FLOAT", "GA_FLOAT", 4, 1 | 4 << 16 | 1 << 20),  # one lane per output
+    ("ARGMIN", "GA_HALF", "GA_HALF", 8, 32 | 2 << 16 | 1 << 20),
+    ("SUM", "GA_DOUBLE", "GA_DOUBLE", 2, 32 | 4 << 16),                # a warp on 4 runs of its output at once
+    ("MINANDARGMIN", "GA_INT", "GA_INT", 4, 32 | 2 << 16),
+    ("SUM", "GA_FLOAT", "GA_FLOAT", 4, 32 | 1 << 21),                  # flattened (run, vector) space
+    ("PROD", "GA_FLOAT", "GA_FLOAT", 4, 256),                          # a CTA per (output, split)
+]
+
+
+@pytest.mark.parametrize("op,src,dst,vec,group", ROWS_VARIANTS)
+def test_row_reduction_variants_compile_for_sm100a(api, op, src, dst, vec, group):
+    L = api.lib()
+    L.gpuarray_b200_reduction_source.restype = ctypes.c_void_p
+    p = L.gpuarray_b200_reduction_source(getattr(api, "GA_REDUCE_" + op), getattr(api, src),
+                                         getattr(api, dst), 0, vec, 0, 1, group)
+    text = ctypes.string_at(p)
+    assert b"ga_reduce.cuh" in text
+    err, size, log = _compile(api, text)
+    assert err == 0 and size > 0, log
+
+
+@pytest.mark.parametrize("fast8,op,src,dst", [(1, "SUM", "GA_BYTE", "GA_LONG"), (2, "SUM", "GA_UBYTE", "GA_UINT"),
+                                              (3, "ANY", "GA_BOOL", "GA_BOOL"), (4, "ALL", "GA_UBYTE", "GA_BOOL")])
+def test_byte_folding_variants_compile_for_sm100a(api, fast8, op, src, dst):
+    """1-byte sums / all / any that fold whole 32-bit words: the host adds
+    GA_RD_FAST8 to the variant; here it is put in front of the generated source."""
+    L = api.lib()
+    L.gpuarray_b200_reduction_source.restype = ctypes.c_void_p
+    p = L.gpuarray_b200_reduction_source(getattr(api, "GA_REDUCE_" + op), getattr(api, src),
+                                         getattr(api, dst), 0, 16, 0, 1, 32)
+    text = ctypes.string_at(p).replace(b"#define GA_RD_FAST8 0", b"#define GA_RD_FAST8 %d" % fast8)
+    assert (b"#define GA_RD_FAST8 %d" % fast8) in text
+    err, size, log = _compile(api, text)
+    assert err == 0 and size > 0, log
+
+
 def test_bad_expression_reports_compiler_log(api):
     src = b'#include "cluda.h"\nKERNEL void k(GLOBAL_MEM ga_float *a) { a[0] = undefined_name; }\n'
     err, size, log = _compile(api, src)

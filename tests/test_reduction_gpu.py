@@ -368,15 +368,20 @@ def test_nan_and_signed_zero_rules(api, ctx, oracle):
     assert np.isnan(got_v[5]) and got_i[5] == 0
 
 
-def test_destination_strides_and_offsets_are_honoured(api, ctx, oracle, rng):
-    x = make_data(rng, np.float32, (50, 2000))
+@pytest.mark.parametrize("shape,axes", [((50, 2000), [1]),        # a warp per long run
+                                        ((50, 24), [1]),          # part of a warp per short run
+                                        ((50, 300), [1]),
+                                        ((6, 50, 40), [0, 2]),    # several short runs per output
+                                        ((900, 50), [0])])        # column kernel
+def test_destination_strides_and_offsets_are_honoured(api, ctx, oracle, rng, shape, axes):
+    x = make_data(rng, np.float32, shape)
     g = api.GpuArray.from_numpy(ctx, x)
     vbuf = api.GpuArray.from_numpy(ctx, np.full(200, -7, np.float32))
     ibuf = api.GpuArray.from_numpy(ctx, np.full(200, -7, np.int64))
     v, i = vbuf[150:0:-3], ibuf[3:103:2]        # 50 elements each, odd strides
     assert v.shape == (50,) and i.shape == (50,)
-    api.maxandargmax(v, i, g, [1])
-    want_v, want_i = oracle.minmaxarg(x, [1])
+    api.maxandargmax(v, i, g, axes)
+    want_v, want_i = oracle.minmaxarg(x, axes)
     hv, hi = vbuf.to_numpy(), ibuf.to_numpy()
     assert (hv[150:0:-3] == want_v).all() and (hi[3:103:2] == want_i).all()
     mask = np.ones(200, bool)
