@@ -13,6 +13,7 @@ reductions) and removes the mako dependency:
     from libgpuarray_b200 import pygpu_compat
     pygpu_compat.install()
     x.sum(axis=1)        # ndgpuarray method -> GpuReduction_call
+    x.argmax(axis=1)     # added: max / min / argmax / argmin (pygpu has them commented out)
 
 pygpu arrays are handed over without copies: `GpuContext.ptr` is the
 gpucontext*, `GpuArray.gpudata` the device address of element [0,...,0].
@@ -66,6 +67,72 @@ def _run(opcode, ary, redux, out_type, out):
     return out
 
 
+def _axis_mask(nd, axis):
+    if axis is None:
+        return [True] * nd
+    redux = [False] * nd
+    if not isinstance(axis, (list, tuple)):
+        axis = (axis,)
+    for ax in axis:
+        if ax < 0:
+            ax += nd
+        if ax < 0 or ax >= nd:
+            raise ValueError("axis out of bounds")
+        redux[ax] = True
+    return redux
+
+
+def _minmax(ary, opcode, axis, want_value, want_index):
+    """max / min / argmax / argmin, which pygpu leaves commented out
+    (pygpu/_array.py:264-280). A tuple of axes is reduced as in
+    GpuArray_maxandargmax: the index is the flattened position over the listed
+    axes, in the order listed."""
+    import pygpu
+    if ary.size == 0:
+        raise ValueError("min/max of an empty array")
+    if ary.ndim == 0:
+        ary = ary.reshape((1,))
+    axes = list(range(ary.ndim)) if axis is None else \
+        [a + ary.ndim if a < 0 else a for a in (axis if isinstance(axis, (list, tuple)) else (axis,))]
+    kept = tuple(d for i, d in enumerate(ary.shape) if i not in axes)
+    ctx = _ctx(ary.context)
+    key = (int(ary.context.ptr), opcode, ary.dtype.str)
+    if key not in _operators:
+        _operators[key] = api.GpuReduction(ctx, opcode, ary.dtype)
+    val = idx = None
+    if want_value:
+        val = pygpu.gpuarray.empty(kept, dtype=ary.dtype, context=ary.context, cls=type(ary))
+    if want_index:
+        idx = pygpu.gpuarray.empty(kept, dtype="int64", context=ary.context, cls=type(ary))
+    _operators[key](_wrap(ctx, val) if want_value else None, _wrap(ctx, idx) if want_index else None,
+                    _wrap(ctx, ary), axes)
+    return val, idx
+
+
+def amax(ary, axis=None):
+    return _minmax(ary, api.GA_REDUCE_MAX, axis, True, False)[0]
+
+
+def amin(ary, axis=None):
+    return _minmax(ary, api.GA_REDUCE_MIN, axis, True, False)[0]
+
+
+def argmax(ary, axis=None):
+    return _minmax(ary, api.GA_REDUCE_ARGMAX, axis, False, True)[1]
+
+
+def argmin(ary, axis=None):
+    return _minmax(ary, api.GA_REDUCE_ARGMIN, axis, False, True)[1]
+
+
+def maxandargmax(ary, axis=None):
+    return _minmax(ary, api.GA_REDUCE_MAXANDARGMAX, axis, True, True)
+
+
+def minandargmin(ary, axis=None):
+    return _minmax(ary, api.GA_REDUCE_MINANDARGMIN, axis, True, True)
+
+
 def reduce1(ary, op, neutral, out_type, axis=None, out=None, oper=None):
     """Same signature and axis handling as pygpu.reduction.reduce1."""
     nd = ary.ndim
@@ -115,3 +182,5 @@ def install():
     pygpu.reduction.reduce1 = reduce1
     pygpu.reduction.ReductionKernel = ReductionKernel
     pygpu._array.reduce1 = reduce1
+    for name, fn in (("max", amax), ("min", amin), ("argmax", argmax), ("argmin", argmin)):
+        setattr(pygpu._array.ndgpuarray, name, fn)

@@ -140,6 +140,17 @@ def part3():
     assert (np.asarray(gb.all(axis=1)) == b.all(axis=1)).all()
     assert (np.asarray(gb.any(axis=0)) == b.any(axis=0)).all()
     assert bool(np.asarray(gb.any())) == bool(b.any())
+    # max / min / argmax / argmin, added to ndgpuarray by install()
+    y = np.round(x * 4) / 4                                           # ties
+    gy = pygpu.array(y, context=ctx, cls=ndgpuarray)
+    for axis in (None, 0, 1, 2, -1):
+        assert (np.asarray(gy.max(axis=axis)) == y.max(axis=axis)).all(), axis
+        assert (np.asarray(gy.min(axis=axis)) == y.min(axis=axis)).all(), axis
+        assert (np.asarray(gy.argmax(axis=axis)) == y.argmax(axis=axis)).all(), axis
+        assert (np.asarray(gy.argmin(axis=axis)) == y.argmin(axis=axis)).all(), axis
+    v, i = pygpu_compat.maxandargmax(gy, axis=(0, 2))
+    flat = y.transpose(1, 0, 2).reshape(500, -1)
+    assert (np.asarray(v) == flat.max(1)).all() and (np.asarray(i) == flat.argmax(1)).all()
     print("part3 ok")
 
 
