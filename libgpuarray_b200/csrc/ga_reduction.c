@@ -25,7 +25,7 @@
 enum { SHAPE_ROWS = 0, SHAPE_COLS = 1, SHAPE_GENERAL = 2 };
 
 typedef struct rd_variant {
-  int shape, vec, idx64, tpo, dst_tc, write_val, write_idx, group, flat, mu, onerun, fast8;
+  int shape, vec, idx64, tpo, dst_tc, write_val, write_idx, group, flat, mu, onerun, fast8, lazy;
   ga_function fn;
   struct rd_variant *next;
 } rd_variant;
@@ -135,15 +135,25 @@ static char *gen_source(const GpuReduction *gr, const rd_variant *v) {
   ga_strb_printf(&sb, "#define GA_RD_MAP(x) %s\n#define GA_RD_COMBINE(a, b) %s\n"
                       "#define GA_RD_IDENT %s\n#define GA_RD_BETTER(b, a) %s\n",
                  map, combine, ident, op_is_min(gr->op) ? "((b) < (a))" : "((b) > (a))");
+  if (gr->kind == 1) {
+    const int mn = op_is_min(gr->op);
+    if (gr->src_tc == GA_DOUBLE)
+      ga_strb_printf(&sb, "#define GA_RD_PICK(a, b) %s((a), (b))\n", mn ? "fmin" : "fmax");
+    else if (tc_is_float(gr->src_tc))
+      ga_strb_printf(&sb, "#define GA_RD_PICK(a, b) %s((a), (b))\n", mn ? "fminf" : "fmaxf");
+    else
+      ga_strb_printf(&sb, "#define GA_RD_PICK(a, b) ((a) %s (b) ? (a) : (b))\n", mn ? "<" : ">");
+  }
   ga_strb_printf(&sb, "#define GA_RD_KIND %d\n#define GA_RD_ISFLOAT %d\n#define GA_RD_WRITE_VAL %d\n"
                       "#define GA_RD_WRITE_IDX %d\n#define GA_RD_IDX_T %s\n#define GA_RD_VEC %d\n"
                       "#define GA_RD_THREADS %d\n#define GA_RD_TPO %d\n"
                       "#define GA_RD_BY %d\n#define GA_RD_GROUP %d\n#define GA_RD_FLAT %d\n"
-                      "#define GA_RD_MU %d\n#define GA_RD_ONERUN %d\n#define GA_RD_FAST8 %d\n#define %s\n"
+                      "#define GA_RD_MU %d\n#define GA_RD_ONERUN %d\n#define GA_RD_FAST8 %d\n#define GA_RD_LAZY %d\n"
+                      "#define %s\n"
                       "#include \"ga_reduce.cuh\"\n",
                  gr->kind, tc_is_float(gr->src_tc), v->write_val, v->write_idx,
                  v->idx64 ? "unsigned long long" : "unsigned int", v->vec, RD_THREADS, v->tpo,
-                 RD_BY, v->group ? v->group : RD_THREADS, v->flat, v->mu ? v->mu : 1, v->onerun, v->fast8,
+                 RD_BY, v->group ? v->group : RD_THREADS, v->flat, v->mu ? v->mu : 1, v->onerun, v->fast8, v->lazy,
                  v->shape == SHAPE_ROWS   ? "GA_RD_BUILD_ROWS"
                  : v->shape == SHAPE_COLS ? "GA_RD_BUILD_COLS"
                                           : "GA_RD_BUILD_GENERAL");
@@ -164,7 +174,7 @@ static rd_variant *get_variant(GpuReduction *gr, const rd_variant *want, int *er
         v->tpo == want->tpo && v->dst_tc == want->dst_tc &&
         v->write_val == want->write_val && v->write_idx == want->write_idx &&
         v->group == want->group && v->flat == want->flat && v->mu == want->mu &&
-        v->onerun == want->onerun && v->fast8 == want->fast8)
+        v->onerun == want->onerun && v->fast8 == want->fast8 && v->lazy == want->lazy)
       return v;
   v = malloc(sizeof(*v));
   if (v == NULL) {
@@ -430,10 +440,11 @@ static int all_multiple(const long long *v, unsigned n, long long m) {
 }
 
 /* Tuning for experiments: GPUARRAY_B200_RD="ctas_per_sm,seg_vectors,cta_min_vectors,
- * cols_ctas_per_sm,onerun_ctas_per_sm,onerun_loads_per_lane,onerun_outputs_at_once". The
+ * cols_ctas_per_sm,onerun_ctas_per_sm,onerun_loads_per_lane,onerun_outputs_at_once,
+ * lazy_index (0/1),lazy_min_vectors_per_lane". The
  * defaults are the best of sweeps on a B200. */
 static unsigned rd_cols_ctas_per_sm = 3;
-static unsigned rd_onerun_ctas_per_sm = 3, rd_onerun_lpl = 4, rd_onerun_mu = 0;
+static unsigned rd_onerun_ctas_per_sm = 3, rd_onerun_lpl = 4, rd_onerun_mu = 0, rd_lazy = 1, rd_lazy_min = 32;
 
 static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_bytes) {
   static int parsed = 0;
@@ -442,8 +453,8 @@ static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_
   if (!parsed) {
     const char *env = getenv("GPUARRAY_B200_RD");
     if (env != NULL)
-      sscanf(env, "%u,%u,%u,%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm,
-             &rd_onerun_ctas_per_sm, &rd_onerun_lpl, &rd_onerun_mu);
+      sscanf(env, "%u,%u,%u,%u,%u,%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm,
+             &rd_onerun_ctas_per_sm, &rd_onerun_lpl, &rd_onerun_mu, &rd_lazy, &rd_lazy_min);
     if (rd_cols_ctas_per_sm == 0) rd_cols_ctas_per_sm = 3;
     *warp_bytes = t_warp;
     if (t_ctas == 0) t_ctas = 32;
@@ -682,6 +693,13 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
     grid[0] = (unsigned)(blocks ? blocks : 1);
   }
 
+  /* (value, index) operators over long runs scan values only (GA_RD_LAZY). Measured on
+   * B200: 32 KiB fp32 rows (64 vectors per lane) 49.7 -> 46.2 us for 268 MB, the headline's
+   * 128 KB rows 321.7 -> 316.5 us; 8 KiB fp64 runs (16 per lane) lose 6 % to the extra
+   * look at the winning vector, hence the threshold. */
+  if (gr->kind == 1 && want.shape == SHAPE_ROWS && !want.onerun && !want.flat && want.mu <= 1 &&
+      rd_lazy && L.seg / (unsigned)want.vec / (unsigned)(want.group ? want.group : RD_THREADS) >= rd_lazy_min)
+    want.lazy = 1;
   /* whole-word arithmetic on vectors of 1-byte elements (see ga__fold_lanes) */
   if (elsize == 1 && want.vec % 4 == 0 && want.shape == SHAPE_ROWS) {
     if (gr->op == GA_REDUCE_SUM && !tc_is_float(want.dst_tc) &&

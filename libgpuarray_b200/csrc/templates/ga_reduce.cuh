@@ -50,6 +50,10 @@
 #define GA_RD_FAST8 0 /* 1-byte elements folded a 32-bit word at a time: 1 signed sum,
                          2 unsigned sum, 3 any, 4 all */
 #endif
+#ifndef GA_RD_LAZY
+#define GA_RD_LAZY 0 /* rows, (value, index) operators: scan values only, recover the index
+                        afterwards; needs GA_RD_PICK(a, b) = the better of two values */
+#endif
 #ifndef GA_RD_ONERUN
 #define GA_RD_ONERUN 0 /* rows: every output is one short contiguous run and nothing is split */
 #endif
@@ -552,6 +556,48 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
         for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
           const ga__rd_pack<GA_RD_VEC> t = pv[i];
           ga__fold_lanes(st, t, fbase + (GA_RD_IDX_T)(i * GA_RD_VEC) * imul, imul);
+        }
+#elif GA_RD_LAZY
+        /* (value, index) operators over a long run: the scan keeps only the
+         * best value and the vector it came from (strictly better only, so the
+         * earliest vector wins ties); the element and its index are recovered
+         * from that one vector afterwards. A third of the instructions of
+         * comparing and selecting (value, index) pairs per element. */
+        {
+          GA_RD_X_T bv = (GA_RD_X_T)(GA_RD_IDENT);
+          unsigned int bi = lane; /* where to look if nothing beats the identity */
+#pragma unroll 8
+          for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
+            const ga__rd_pack<GA_RD_VEC> t = pv[i];
+            GA_RD_X_T m = GA_RD_LOAD(t.v[0]);
+#pragma unroll
+            for (int j = 1; j < GA_RD_VEC; j++) m = GA_RD_PICK(m, GA_RD_LOAD(t.v[j]));
+            if (GA_RD_BETTER(m, bv)) {
+              bv = m;
+              bi = i;
+            }
+          }
+          if (bi < nv) {
+            const ga__rd_pack<GA_RD_VEC> t = pv[bi];
+            ga__state loc = ga__init();
+#pragma unroll
+            for (int j = GA_RD_VEC - 1; j >= 0; j--) {
+              const GA_RD_X_T x = GA_RD_LOAD(t.v[j]);
+              if (x == bv) { /* first match last: it keeps its own bit pattern (+-0) */
+                loc.v = x;
+                loc.i = fbase + (GA_RD_IDX_T)(bi * GA_RD_VEC + (unsigned)j) * imul;
+              }
+            }
+            if (loc.i == GA__IDX_NONE) {
+              /* nothing beat the identity and the first vector does not hold it
+               * (NaNs): find the first element equal to it, if any, the long way */
+              for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
+                const ga__rd_pack<GA_RD_VEC> u = pv[i];
+                ga__fold_one(loc, u, fbase + (GA_RD_IDX_T)(i * GA_RD_VEC) * imul, imul);
+              }
+            }
+            ga__merge(st[0], loc);
+          }
         }
 #else
 #pragma unroll 8

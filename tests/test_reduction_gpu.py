@@ -368,6 +368,58 @@ def test_nan_and_signed_zero_rules(api, ctx, oracle):
     assert np.isnan(got_v[5]) and got_i[5] == 0
 
 
+def test_long_runs_scan_values_then_recover_the_index(api, ctx, oracle, rng):
+    """Over long contiguous runs the arg-reductions scan values only and find the
+    element afterwards; the corner cases of that recovery, per row of 6000:"""
+    n = 6000
+    nan, inf = np.float32("nan"), np.float32("inf")
+    rows = []
+    r = np.full(n, -inf, np.float32); rows.append(r)                       # identity everywhere
+    r = np.full(n, -inf, np.float32); r[:8] = nan; rows.append(r)          # NaNs first, identity after
+    r = np.full(n, nan, np.float32); r[4097] = -inf; rows.append(r)        # one identity among NaNs
+    r = np.full(n, nan, np.float32); r[0] = -inf; r[5] = 2; rows.append(r)
+    r = np.full(n, nan, np.float32); rows.append(r)                        # NaN first: kept
+    r = np.full(n, -1, np.float32); r[130] = -0.0; r[131] = 0.0; r[4000] = 0.0; rows.append(r)
+    r = np.full(n, -1, np.float32); r[131] = 0.0; r[132] = -0.0; r[77] = -0.0; rows.append(r)
+    r = np.full(n, 3, np.float32); rows.append(r)                          # all equal
+    r = np.full(n, 3, np.float32); r[-1] = 4; rows.append(r)               # winner in the ragged end
+    r = np.full(n, 3, np.float32); r[127] = 9; r[128] = 9; r[5000] = 9; rows.append(r)  # ties across lanes
+    r = rng.standard_normal(n).astype(np.float32); r[3001] = inf; r[3000] = nan; rows.append(r)
+    x = np.stack(rows)
+    for name, data in (("maxandargmax", x), ("minandargmin", -x), ("argmax", x), ("max", x), ("min", -x)):
+        check_reduce(api, ctx, oracle, name, data, [1])
+        check_reduce(api, ctx, oracle, name, data, [1], layout="window")   # scalar loads
+    check_reduce(api, ctx, oracle, "maxandargmax", x.astype(np.float64), [1])
+    # float16 goes through float32 and back, which does not keep a NaN's payload bits:
+    # rows without NaN only
+    check_reduce(api, ctx, oracle, "minandargmin", (-x[[0, 5, 6, 7, 8, 9]]).astype(np.float16), [1])
+    # whole-array reductions: runs cut into segments, CTA groups, tickets
+    big = np.full(3_000_000, -inf, np.float32)
+    check_reduce(api, ctx, oracle, "maxandargmax", big, [0])
+    big[2_000_001] = nan
+    big[1_999_999] = 5
+    big[2_500_000] = 5
+    check_reduce(api, ctx, oracle, "maxandargmax", big, [0])
+    check_reduce(api, ctx, oracle, "minandargmin", -big, [0])
+    for dt in (np.int32, np.int8, np.uint16, np.int64):
+        info = np.iinfo(dt)
+        xi = np.full((7, n), info.min, dt)
+        xi[1, 4321] = info.min + 1
+        xi[2, :] = info.max
+        xi[3, 17] = info.max
+        xi[3, 5017] = info.max
+        xi[4] = rng.integers(info.min, info.max, n, dtype=dt)
+        xi[5, -3:] = info.max
+        xi[6, 0] = info.max
+        check_reduce(api, ctx, oracle, "maxandargmax", xi, [1])
+        check_reduce(api, ctx, oracle, "minandargmin", xi, [1])
+    # several long runs per output, listed in an order that differs from memory order
+    y = np.round(rng.standard_normal((12, 3, 2048)) * 2).astype(np.float32)
+    check_reduce(api, ctx, oracle, "maxandargmax", y, [0, 2])
+    check_reduce(api, ctx, oracle, "maxandargmax", y, [2, 0])
+    check_reduce(api, ctx, oracle, "minandargmin", y, [2, 0])
+
+
 @pytest.mark.parametrize("shape,axes", [((50, 2000), [1]),        # a warp per long run
                                         ((50, 24), [1]),          # part of a warp per short run
                                         ((50, 300), [1]),
