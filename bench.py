@@ -607,7 +607,7 @@ def run_ours(args, rank, world, local_rank):
 # dram__bytes_read.sum + dram__bytes_write.sum of one 16384-row ga_rd_rows
 # launch: 4 x the 4096-row ncu capture summarised in
 # profiles/ga_rd_rows_cfg3_maxandargmax.md (traffic is proportional to rows).
-TRAFFIC_BYTES_PER_LAUNCH = 2132034560
+TRAFFIC_BYTES_PER_LAUNCH = 2167131136
 
 
 _REAL_STDOUT = None
