@@ -279,7 +279,7 @@ def side_configs(api, ctx, torch, stream, once=False):
     return out
 
 
-def other_shapes(api, ctx, torch, stream):
+def other_shapes(api, ctx, torch, stream, once=False):
     """`--other-shapes`: shapes outside the five named configurations that the
     same kernels meet in practice (short runs, kept axis in the middle,
     broadcasts, narrow element types), each 130-270 MB so that one launch
@@ -288,7 +288,7 @@ def other_shapes(api, ctx, torch, stream):
     peak, _ = measured_peak()
     out = {}
     g = torch.Generator(device="cuda").manual_seed(7)
-    stall_buf = api.GpuArray.empty(ctx, (2 << 30,), np.uint8)
+    stall_buf = api.GpuArray.empty(ctx, (4096 if once else 2 << 30,), np.uint8)
     npdt = {torch.float32: np.float32, torch.float16: np.float16, torch.float64: np.float64,
             torch.int8: np.int8, torch.uint8: np.uint8}
 
@@ -296,11 +296,13 @@ def other_shapes(api, ctx, torch, stream):
         return api.GpuArray.from_pointer(ctx, t.data_ptr(), tuple(t.shape), npdt[t.dtype])
 
     def timed(name, fn, nbytes, reps=10):
-        for _ in range(3):
+        if once:                      # profiler captures: one launch per case
+            reps = 1
+        for _ in range(0 if once else 3):
             fn()
         a = torch.cuda.Event(enable_timing=True)
         b = torch.cuda.Event(enable_timing=True)
-        for _ in range(3):
+        for _ in range(0 if once else 3):
             stall_buf.memset(0)
         a.record(stream)
         for _ in range(reps):
@@ -598,7 +600,7 @@ def run_ours(args, rank, world, local_rank):
         except Exception as e:
             line["configs"] = {"error": str(e)[:300]}
     if world == 1 and args.other_shapes:
-        line["other_shapes"] = other_shapes(api, ctx, torch, stream)
+        line["other_shapes"] = other_shapes(api, ctx, torch, stream, once=args.side_once)
     emit(line)
     if world > 1:
         dist.destroy_process_group()
@@ -641,7 +643,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--side-once", action="store_true",
-                    help="profiler captures: run every side config exactly once, cfg5 on 128 planes")
+                    help="profiler captures: run every side config (and every --other-shapes case) "
+                         "exactly once, cfg5 on 128 planes")
     ap.add_argument("--no-clocks", action="store_true",
                     help="skip the nvidia-smi sampling window (profiler captures)")
     ap.add_argument("--other-shapes", action="store_true",
