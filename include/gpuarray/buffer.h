@@ -21,7 +21,9 @@ typedef struct _gpukernel gpukernel;
 typedef struct _gpucontext_props gpucontext_props;
 
 /* ---- enumeration (reference buffer.h:56-72) ---- */
+/* replaces src/gpuarray/buffer.h:56 */
 GPUARRAY_PUBLIC int gpu_get_platform_count(const char *name, unsigned int *platcount);
+/* replaces src/gpuarray/buffer.h:70 */
 GPUARRAY_PUBLIC int gpu_get_device_count(const char *name, unsigned int platform,
                                          unsigned int *devcount);
 
@@ -30,24 +32,36 @@ GPUARRAY_PUBLIC int gpu_get_device_count(const char *name, unsigned int platform
 #define GA_CTX_SCHED_SINGLE 1
 #define GA_CTX_SCHED_MULTI  2
 
+/* replaces src/gpuarray/buffer.h:89 */
 GPUARRAY_PUBLIC int gpucontext_props_new(gpucontext_props **res);
+/* replaces src/gpuarray/buffer.h:99 */
 GPUARRAY_PUBLIC int gpucontext_props_cuda_dev(gpucontext_props *p, int devno);
 /* Always fails: there is no OpenCL backend in this engine. */
+/* replaces src/gpuarray/buffer.h:111 */
 GPUARRAY_PUBLIC int gpucontext_props_opencl_dev(gpucontext_props *p, int platno, int devno);
+/* replaces src/gpuarray/buffer.h:122 */
 GPUARRAY_PUBLIC int gpucontext_props_sched(gpucontext_props *p, int sched);
 /* Accepted and ignored: this engine always runs one in-order stream per context. */
+/* replaces src/gpuarray/buffer.h:164 */
 GPUARRAY_PUBLIC int gpucontext_props_set_single_stream(gpucontext_props *p);
+/* replaces src/gpuarray/buffer.h:177 */
 GPUARRAY_PUBLIC int gpucontext_props_kernel_cache(gpucontext_props *p, const char *path);
+/* replaces src/gpuarray/buffer.h:192 */
 GPUARRAY_PUBLIC int gpucontext_props_alloc_cache(gpucontext_props *p, size_t initial, size_t max);
+/* replaces src/gpuarray/buffer.h:205 */
 GPUARRAY_PUBLIC void gpucontext_props_del(gpucontext_props *p);
 
 /* ---- context lifetime (reference buffer.h:223-265) ----
  * `name` is "cuda" (device taken from props, default 0) or "cudaN".
  * Takes ownership of `props` (may be NULL). Not thread safe. */
+/* replaces src/gpuarray/buffer.h:223 */
 GPUARRAY_PUBLIC int gpucontext_init(gpucontext **res, const char *name, gpucontext_props *props);
+/* replaces src/gpuarray/buffer.h:236 */
 GPUARRAY_PUBLIC void gpucontext_deref(gpucontext *ctx);
+/* replaces src/gpuarray/buffer.h:250 */
 GPUARRAY_PUBLIC int gpucontext_property(gpucontext *ctx, int prop_id, void *res);
 /* Message of the last error on `ctx` (or the process-global one if NULL). */
+/* replaces src/gpuarray/buffer.h:265 */
 GPUARRAY_PUBLIC const char *gpucontext_error(gpucontext *ctx, int err);
 
 /* ---- buffers (reference buffer.h:283-494) ---- */
@@ -59,38 +73,57 @@ GPUARRAY_PUBLIC const char *gpucontext_error(gpucontext *ctx, int err);
 #define GA_BUFFER_HOST       0x08 /* pinned host memory visible to the device */
 #define GA_BUFFER_MASK       0xffff
 
+/* replaces src/gpuarray/buffer.h:283 */
 GPUARRAY_PUBLIC gpudata *gpudata_alloc(gpucontext *ctx, size_t sz, void *data, int flags, int *ret);
+/* replaces src/gpuarray/buffer.h:351 */
 GPUARRAY_PUBLIC void gpudata_retain(gpudata *b);
+/* replaces src/gpuarray/buffer.h:363 */
 GPUARRAY_PUBLIC void gpudata_release(gpudata *b);
 /* 1 if the two buffers may overlap in device memory. */
+/* replaces src/gpuarray/buffer.h:379 */
 GPUARRAY_PUBLIC int gpudata_share(gpudata *a, gpudata *b, int *ret);
+/* replaces src/gpuarray/buffer.h:396 */
 GPUARRAY_PUBLIC int gpudata_move(gpudata *dst, size_t dstoff, gpudata *src, size_t srcoff, size_t sz);
+/* replaces src/gpuarray/buffer.h:416 */
 GPUARRAY_PUBLIC int gpudata_transfer(gpudata *dst, size_t dstoff, gpudata *src, size_t srcoff, size_t sz);
 /* Blocking device->host copy; the observable synchronisation point. */
+/* replaces src/gpuarray/buffer.h:432 */
 GPUARRAY_PUBLIC int gpudata_read(void *dst, gpudata *src, size_t srcoff, size_t sz);
+/* replaces src/gpuarray/buffer.h:448 */
 GPUARRAY_PUBLIC int gpudata_write(gpudata *dst, size_t dstoff, const void *src, size_t sz);
 /* Fill from dstoff to the end of the buffer with the byte `data`. */
+/* replaces src/gpuarray/buffer.h:462 */
 GPUARRAY_PUBLIC int gpudata_memset(gpudata *dst, size_t dstoff, int data);
+/* replaces src/gpuarray/buffer.h:476 */
 GPUARRAY_PUBLIC int gpudata_sync(gpudata *b);
+/* replaces src/gpuarray/buffer.h:492 */
 GPUARRAY_PUBLIC int gpudata_property(gpudata *buf, int prop_id, void *res);
+/* replaces src/gpuarray/buffer.h:494 */
 GPUARRAY_PUBLIC gpucontext *gpudata_context(gpudata *b);
 
 /* ---- raw kernels (reference buffer.h:523-599) ----
  * The source strings are concatenated and compiled with NVRTC for sm_100a.
  * `typecodes` lists the kernel parameters; GA_BUFFER marks a gpudata*. */
+/* replaces src/gpuarray/buffer.h:523 */
 GPUARRAY_PUBLIC gpukernel *gpukernel_init(gpucontext *ctx, unsigned int count,
                                           const char **strings, const size_t *lengths,
                                           const char *fname, unsigned int numargs,
                                           const int *typecodes, int flags, int *ret,
                                           char **err_str);
+/* replaces src/gpuarray/buffer.h:536 */
 GPUARRAY_PUBLIC void gpukernel_retain(gpukernel *k);
+/* replaces src/gpuarray/buffer.h:547 */
 GPUARRAY_PUBLIC void gpukernel_release(gpukernel *k);
+/* replaces src/gpuarray/buffer.h:562 */
 GPUARRAY_PUBLIC int gpukernel_setarg(gpukernel *k, unsigned int i, void *a);
 /* gs = blocks per grid dimension, ls = threads per block dimension (n <= 3).
  * args == NULL uses the values stored by gpukernel_setarg. */
+/* replaces src/gpuarray/buffer.h:579 */
 GPUARRAY_PUBLIC int gpukernel_call(gpukernel *k, unsigned int n, const size_t *gs,
                                    const size_t *ls, size_t shared, void **args);
+/* replaces src/gpuarray/buffer.h:597 */
 GPUARRAY_PUBLIC int gpukernel_property(gpukernel *k, int prop_id, void *res);
+/* replaces src/gpuarray/buffer.h:599 */
 GPUARRAY_PUBLIC gpucontext *gpukernel_context(gpukernel *k);
 
 /* ---- property ids (numeric values are ABI) ---- */

@@ -11,14 +11,20 @@
 extern "C" {
 #endif
 
+/* replaces src/gpuarray/collectives.h:33 */
 GPUARRAY_PUBLIC int GpuArray_reduce_from(const GpuArray *src, int opcode, int root, gpucomm *comm);
+/* replaces src/gpuarray/collectives.h:53 */
 GPUARRAY_PUBLIC int GpuArray_reduce(const GpuArray *src, GpuArray *dest, int opcode, int root,
                                     gpucomm *comm);
+/* replaces src/gpuarray/collectives.h:71 */
 GPUARRAY_PUBLIC int GpuArray_all_reduce(const GpuArray *src, GpuArray *dest, int opcode,
                                         gpucomm *comm);
+/* replaces src/gpuarray/collectives.h:90 */
 GPUARRAY_PUBLIC int GpuArray_reduce_scatter(const GpuArray *src, GpuArray *dest, int opcode,
                                             gpucomm *comm);
+/* replaces src/gpuarray/collectives.h:106 */
 GPUARRAY_PUBLIC int GpuArray_broadcast(GpuArray *array, int root, gpucomm *comm);
+/* replaces src/gpuarray/collectives.h:124 */
 GPUARRAY_PUBLIC int GpuArray_all_gather(const GpuArray *src, GpuArray *dest, gpucomm *comm);
 
 #ifdef __cplusplus

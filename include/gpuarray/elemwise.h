@@ -43,10 +43,12 @@ typedef struct _gpuelemwise_arg {
  *  n, args   argument descriptors, deep-copied
  *  nd        rank hint for ahead-of-time compilation; any rank works at call time
  * Returns NULL on failure with the reason in the context's error. */
+/* replaces src/gpuarray/elemwise.h:98 */
 GPUARRAY_PUBLIC GpuElemwise *GpuElemwise_new(gpucontext *ctx, const char *preamble,
                                              const char *expr, unsigned int n,
                                              gpuelemwise_arg *args, unsigned int nd, int flags);
 /* NULL is allowed (the reference requires non-NULL). */
+/* replaces src/gpuarray/elemwise.h:130 */
 GPUARRAY_PUBLIC void GpuElemwise_free(GpuElemwise *ge);
 
 /* Runs the operation (reference elemwise.h:140, src/gpuarray_elemwise.c:767-787).
@@ -54,6 +56,7 @@ GPUARRAY_PUBLIC void GpuElemwise_free(GpuElemwise *ge);
  * the declared type for GE_SCALAR ones. The first GE_WRITE array defines the
  * shape; outputs never broadcast. Zero-size shapes succeed without a launch.
  * Returns after enqueueing on the context's stream. */
+/* replaces src/gpuarray/elemwise.h:140 */
 GPUARRAY_PUBLIC int GpuElemwise_call(GpuElemwise *ge, void **args, int flags);
 
 #ifdef __cplusplus

@@ -35,6 +35,7 @@ enum ga_error {
 };
 
 /* Static description of a code; replaces src/gpuarray_error.c:7-30. */
+/* replaces src/gpuarray/error.h:49 */
 GPUARRAY_PUBLIC const char *gpuarray_error_str(int err);
 
 #ifdef __cplusplus

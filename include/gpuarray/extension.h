@@ -18,6 +18,7 @@ typedef struct _GpuArrayIpcMemHandle { char priv[64]; } GpuArrayIpcMemHandle;
 /* Known names: "cuda_enter", "cuda_exit", "cuda_make_ctx", "cuda_get_stream",
  * "cuda_make_buf", "cuda_get_sz", "cuda_wait", "cuda_record",
  * "cuda_get_ipc_handle", "cuda_open_ipc_handle". Unknown names give NULL. */
+/* replaces src/gpuarray/extension.h:31 */
 GPUARRAY_PUBLIC void *gpuarray_get_extension(const char *name);
 
 #ifdef __cplusplus

@@ -13,18 +13,24 @@ extern "C" {
 #endif
 
 /* Registers a user type; returns its new typecode (>= 512) or -1. */
+/* replaces src/gpuarray/util.h:35 */
 GPUARRAY_PUBLIC int gpuarray_register_type(gpuarray_type *t, int *ret);
 /* Never NULL: unknown codes give a descriptor with typecode -1 and size 0. */
+/* replaces src/gpuarray/util.h:46 */
 GPUARRAY_PUBLIC const gpuarray_type *gpuarray_get_type(int typecode);
+/* replaces src/gpuarray/util.h:57 */
 GPUARRAY_PUBLIC size_t gpuarray_get_elsize(int typecode);
 /* OR of the GA_USE_* flags needed by a -1 terminated list of typecodes. */
+/* replaces src/gpuarray/util.h:74 */
 GPUARRAY_PUBLIC int gpuarray_type_flags(int init, ...);
+/* replaces src/gpuarray/util.h:76 */
 GPUARRAY_PUBLIC int gpuarray_type_flagsa(unsigned int n, gpuelemwise_arg *arg);
 
 /* Removes size-1 dimensions (keeping at least one) and merges neighbouring
  * dimensions that are jointly contiguous for every one of the `n` stride
  * vectors (NULL entries are skipped). Works in place. Same contract as
  * src/gpuarray_util.c:153-188. */
+/* replaces src/gpuarray/util.h:97 */
 GPUARRAY_PUBLIC void gpuarray_elemwise_collapse(unsigned int n, unsigned int *nd,
                                                 size_t *dim, ssize_t **strs);
 
