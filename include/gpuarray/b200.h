@@ -44,6 +44,22 @@ GPUARRAY_PUBLIC char *gpuarray_b200_elemwise_source(const char *preamble, const 
 GPUARRAY_PUBLIC char *gpuarray_b200_reduction_source(int op, int src_tc, int dst_tc, int shape,
                                                      int vec, int idx64, int tpo, int group);
 
+/* The plan GpuReduction_call would make (kernel variant, split of the reduced
+ * extent, launch geometry) for a source of the given shape and byte strides on a
+ * device with num_sms multiprocessors, computed on the host alone. `base` stands
+ * for the address of the source's first element (its alignment decides the
+ * vector width); destinations are taken as C-contiguous. out[0..19] = kernel
+ * shape (0 rows, 1 cols, 2 general), vector width, group size, flattened runs,
+ * runs at once, one-run mode, lazy index, byte folding, threads per output
+ * (general kernel), 64-bit index, splits, seg, nseg, units, grid x, grid y,
+ * block x, block y, outputs, reduced elements per output. No reference
+ * counterpart (its scheduler is src/gpuarray_reduction.c:673-776). */
+GPUARRAY_PUBLIC int gpuarray_b200_reduction_plan(int op, int src_tc, int dst_tc, unsigned int nd,
+                                                 const size_t *dims, const ssize_t *strides,
+                                                 unsigned int reduxLen, const int *reduxList,
+                                                 unsigned long long base, unsigned int num_sms,
+                                                 unsigned long long *out);
+
 /* Sum of n contiguous float32 values on the current device WITHOUT allocating
  * anything: no cudaMalloc / cudaFree, no library workspace. (No counterpart in
  * the reference, whose reductions allocate per call.) It is for callers that

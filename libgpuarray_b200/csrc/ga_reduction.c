@@ -299,10 +299,9 @@ static int check_dst(gpucontext *ctx, const GpuArray *d, const GpuArray *s, cons
 static long long ll_abs(long long v) { return v < 0 ? -v : v; }
 
 /* Fills nf/nr, dims, strides, weights and totals of `L`. */
-static int normalise(const GpuReduction *gr, rd_layout *L, const GpuArray *d0, const GpuArray *d1,
-                     const GpuArray *s, const unsigned char *red, unsigned reduxLen,
-                     const int *reduxList) {
-  gpucontext *ctx = gr->ctx;
+static int normalise(int kind, ga_error_rec *e, rd_layout *L, const GpuArray *d0,
+                     const GpuArray *d1, const GpuArray *s, const unsigned char *red,
+                     unsigned reduxLen, const int *reduxList) {
   unsigned i, k, n;
   unsigned long long mul;
 
@@ -330,7 +329,7 @@ static int normalise(const GpuReduction *gr, rd_layout *L, const GpuArray *d0, c
       continue;
     }
     if (n == RD_MAXD)
-      return ga_err_fmt(ctx->err, GA_UNSUPPORTED_ERROR,
+      return ga_err_fmt(e, GA_UNSUPPORTED_ERROR,
                         "More than %d kept dimensions remain after collapsing", RD_MAXD);
     L->fdim[n] = s->dimensions[i];
     L->fsrc[n] = s0;
@@ -352,10 +351,10 @@ static int normalise(const GpuReduction *gr, rd_layout *L, const GpuArray *d0, c
       L->nr_total *= dsz;
       if (dsz != 1) {
         if (m == 64)
-          return ga_err_set(ctx->err, GA_UNSUPPORTED_ERROR, "More than 64 reduced axes");
+          return ga_err_set(e, GA_UNSUPPORTED_ERROR, "More than 64 reduced axes");
         dim[m] = dsz;
         str[m] = s->strides[ax];
-        w[m] = gr->kind == 1 ? mul : 0;
+        w[m] = kind == 1 ? mul : 0;
         m++;
       }
       mul *= dsz;
@@ -384,7 +383,7 @@ static int normalise(const GpuReduction *gr, rd_layout *L, const GpuArray *d0, c
         continue;
       }
       if (n == RD_MAXD)
-        return ga_err_fmt(ctx->err, GA_UNSUPPORTED_ERROR,
+        return ga_err_fmt(e, GA_UNSUPPORTED_ERROR,
                           "More than %d reduced dimensions remain after collapsing", RD_MAXD);
       L->rdim[n] = dim[i];
       L->rsrc[n] = str[i];
@@ -465,6 +464,285 @@ static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_
   *seg_vecs = t_seg;
 }
 
+/* What the planner needs to know besides the normalised layout. */
+typedef struct rd_plan_in {
+  ga_error_rec *e;
+  int kind;
+  ga_reduce_op op;
+  int src_tc, dst_tc, need_val, need_idx;
+  unsigned num_sms;
+  unsigned long long p_src; /* address of the source's first element (alignment only) */
+} rd_plan_in;
+
+/* Chooses the kernel variant, the split of the reduced extent and the launch
+ * geometry for a normalised problem. Pure host arithmetic: no device, no
+ * allocation (gpuarray_b200_reduction_plan exposes it to tests). */
+static int rd_plan(const rd_plan_in *in, rd_layout *L, rd_variant *want, unsigned grid[3],
+                   unsigned block[3]) {
+  unsigned ctas_per_sm, seg_vecs, cta_min_vecs;
+  size_t elsize = gpuarray_get_elsize(in->src_tc), target;
+  grid[0] = grid[1] = grid[2] = 1;
+  block[0] = RD_THREADS;
+  block[1] = block[2] = 1;
+  rd_tuning(&ctas_per_sm, &seg_vecs, &cta_min_vecs);
+  target = (size_t)in->num_sms * ctas_per_sm;
+
+  memset(want, 0, sizeof(*want));
+  want->dst_tc = in->dst_tc;
+  want->write_val = in->need_val;
+  want->write_idx = in->need_idx;
+  want->idx64 = L->nr_total >= 0xffffffffULL;
+  want->vec = 1;
+  want->tpo = 1;
+  L->splits = 1;
+
+  if (L->nr_total > 0 && L->nr >= 1 && L->rsrc[L->nr - 1] == (long long)elsize &&
+      L->rdim[L->nr - 1] >= 2) {
+    /* --- contiguous reduced run --- */
+    unsigned vec = (unsigned)(16 / elsize);
+    unsigned long long rows_outer = L->nr_total / L->rdim[L->nr - 1];
+    want->shape = SHAPE_ROWS;
+    if (vec > 1 && in->p_src % 16 == 0 && all_multiple(L->fsrc, (unsigned)L->nf, 16) &&
+        all_multiple(L->rsrc, (unsigned)L->nr - 1, 16))
+      want->vec = (int)vec;
+    L->inner = L->rdim[L->nr - 1];
+    {
+      unsigned long long nvrow = L->inner / (unsigned)want->vec, groups_target, nwork, blocks, share;
+      unsigned gpb;
+      /* Who shares a work item, and whether the reduced extent is split:
+       *  - plenty of outputs: a warp per output, no split;
+       *  - a moderate number of outputs with long runs: a CTA per output;
+       *  - few outputs: split the reduced extent (CTAs when the runs are long
+       *    and the outputs very few, which also keeps the partial count low). */
+      int need_split = 0;
+      /* loads one lane of a warp issues per run: short runs need help to keep
+       * enough bytes in flight (see the kernel's comment) */
+      unsigned long long nload = nvrow + (L->inner % (unsigned)want->vec != 0);
+      if (rows_outer == 1 && nload <= 256) {
+        unsigned g = 1, lpl;
+        while (g < 32 && g * rd_onerun_lpl < nload) g *= 2;
+        lpl = (unsigned)((nload + g - 1) / g);
+        want->onerun = 1;
+        want->group = (int)g;
+        want->mu = rd_onerun_mu ? (int)rd_onerun_mu : lpl <= 2 ? 4 : 2;
+        L->seg = L->inner;
+        L->nseg = 1;
+        L->units = 1;
+        gpb = RD_THREADS / g;
+        blocks = (L->nf_total + (unsigned long long)gpb * (unsigned)want->mu - 1) /
+                 ((unsigned long long)gpb * (unsigned)want->mu);
+        if (rd_onerun_ctas_per_sm && blocks > (unsigned long long)in->num_sms * rd_onerun_ctas_per_sm)
+          blocks = (unsigned long long)in->num_sms * rd_onerun_ctas_per_sm;
+        grid[0] = (unsigned)blocks;
+        goto rows_done;
+      }
+      want->flat = nvrow < 16;
+      want->mu = want->flat ? 1 : nload <= 64 ? 4 : nload <= 256 ? 2 : 1;
+      if (nvrow >= cta_min_vecs) want->group = RD_THREADS;
+      else if (L->nf_total >= (unsigned long long)in->num_sms * 16) want->group = 32;
+      else if (L->nf_total >= (unsigned long long)in->num_sms * 4 && nvrow >= 1024)
+        want->group = RD_THREADS;
+      else {
+        /* warps, unless long runs would leave them either too few or with
+         * shares too short to be worth a ticket (see the cap below) */
+        unsigned long long s_w = ((unsigned long long)target * (RD_THREADS / 32) + L->nf_total - 1) /
+                                 L->nf_total;
+        unsigned long long cap_w = L->nr_total * elsize / (24u << 10);
+        if (cap_w < 1) cap_w = 1;
+        if (s_w > cap_w) s_w = cap_w;
+        need_split = 1;
+        want->group = (nvrow >= 2048 && (L->nf_total < (unsigned long long)in->num_sms ||
+                                        L->nf_total * s_w < (unsigned long long)in->num_sms * 16))
+                         ? RD_THREADS : 32;
+      }
+      if (want->group == RD_THREADS) want->flat = 0, want->mu = 1;
+      gpb = RD_THREADS / (unsigned)want->group;
+      /* measured on B200: whole-CTA groups run best as a few long-lived CTAs
+       * per SM, warp groups as many (a full complement of resident warps) */
+      groups_target = want->group == RD_THREADS ? (unsigned long long)in->num_sms * 4
+                                               : (unsigned long long)target * gpb;
+      L->seg = L->inner;
+      L->nseg = 1;
+      L->units = rows_outer;
+      if (need_split) {
+        unsigned long long s;
+        if (!want->flat) {
+          unsigned long long seg = (unsigned long long)want->group * vec * seg_vecs;
+          if (seg < L->inner) {
+            L->seg = seg;
+            L->nseg = (L->inner + seg - 1) / seg;
+            L->units = rows_outer * L->nseg;
+          }
+        }
+        s = (groups_target + L->nf_total - 1) / L->nf_total;
+        if (want->group == 32) {
+          /* measured on B200: a warp's share should stay above ~24 KiB, or the
+           * ramp of each share and the ticketed finish outweigh the parallelism */
+          unsigned long long cap = L->nr_total * elsize / (24u << 10);
+          if (cap < 1) cap = 1;
+          if (s > cap) s = cap;
+        }
+        if (s > L->units) s = L->units;
+        if (s > 1u << 20) s = 1u << 20;
+        L->splits = s ? s : 1;
+      }
+      if (L->seg >= 0x7fffffffULL) {
+        /* a single run longer than 32-bit indexing: cut it even without splitting */
+        L->seg = (unsigned long long)want->group * vec * seg_vecs * 1024;
+        L->nseg = (L->inner + L->seg - 1) / L->seg;
+        L->units = rows_outer * L->nseg;
+      }
+      make_div32((unsigned int)(nvrow ? nvrow : 1), L->dv);
+      share = (L->units / L->splits + 1) * (nvrow + 1);
+      if (want->flat && share >= 0xffffffffULL)
+        return ga_err_set(in->e, GA_XLARGE_ERROR, "Reduction share exceeds 32-bit indexing");
+      nwork = L->nf_total * L->splits;
+      blocks = (nwork + gpb - 1) / gpb;
+      grid[0] = blocks > 0x7fffffffULL ? 0x7fffffffu : (unsigned)blocks;
+    rows_done:;
+    }
+  } else if (L->nr_total > 0 && L->nf >= 1 && L->fsrc[L->nf - 1] == (long long)elsize &&
+             L->fdim[L->nf - 1] >= 16) {
+    /* --- contiguous kept run --- */
+    unsigned vec = (unsigned)(16 / elsize);
+    unsigned long long ko, nwork, s;
+    if (vec > 4) vec = 4;
+    want->shape = SHAPE_COLS;
+    L->inner = L->fdim[L->nf - 1];
+    while (vec > 1 && !(L->inner % vec == 0 && in->p_src % (vec * elsize) == 0 &&
+                        all_multiple(L->fsrc, (unsigned)L->nf - 1, (long long)(vec * elsize)) &&
+                        all_multiple(L->rsrc, (unsigned)L->nr, (long long)(vec * elsize))))
+      vec /= 2;
+    want->vec = (int)vec;
+    L->tiles = (L->inner + 32ULL * vec - 1) / (32ULL * vec);
+    ko = L->nf_total / L->inner;
+    nwork = ko * L->tiles;
+    s = ((unsigned long long)in->num_sms * rd_cols_ctas_per_sm + nwork - 1) / nwork;
+    if (s > (L->nr_total + RD_BY * 8 - 1) / (RD_BY * 8)) s = (L->nr_total + RD_BY * 8 - 1) / (RD_BY * 8);
+    if (s > 1024) s = 1024;
+    L->splits = s ? s : 1;
+    L->units = nwork; /* tickets: one per column tile */
+    grid[0] = nwork > 0x7fffffffULL ? 0x7fffffffu : (unsigned)nwork;
+    grid[1] = (unsigned)L->splits;
+    block[0] = 32;
+    block[1] = RD_BY;
+  } else {
+    /* --- arbitrary strides --- */
+    unsigned long long groups_per_block, blocks;
+    want->shape = SHAPE_GENERAL;
+    if (L->nr_total >= 2048 && L->nf_total < 4096) want->tpo = RD_THREADS;
+    else if (L->nr_total >= 64) want->tpo = 32;
+    groups_per_block = RD_THREADS / (unsigned)want->tpo;
+    blocks = (L->nf_total + groups_per_block - 1) / groups_per_block;
+    if (blocks > (unsigned long long)target * 8) blocks = (unsigned long long)target * 8;
+    grid[0] = (unsigned)(blocks ? blocks : 1);
+  }
+
+  /* (value, index) operators over long runs scan values only (GA_RD_LAZY). Measured on
+   * B200: 32 KiB fp32 rows (64 vectors per lane) 49.7 -> 46.2 us for 268 MB, the headline's
+   * 128 KB rows 321.7 -> 316.5 us; 8 KiB fp64 runs (16 per lane) lose 6 % to the extra
+   * look at the winning vector, hence the threshold. */
+  if (in->kind == 1 && want->shape == SHAPE_ROWS && !want->onerun && !want->flat && want->mu <= 1 &&
+      rd_lazy && L->seg / (unsigned)want->vec / (unsigned)(want->group ? want->group : RD_THREADS) >= rd_lazy_min)
+    want->lazy = 1;
+  /* whole-word arithmetic on vectors of 1-byte elements (see ga__fold_lanes) */
+  if (elsize == 1 && want->vec % 4 == 0 && want->shape == SHAPE_ROWS) {
+    if (in->op == GA_REDUCE_SUM && !tc_is_float(want->dst_tc) &&
+        gpuarray_get_elsize(want->dst_tc) >= 4)
+      want->fast8 = in->src_tc == GA_BYTE ? 1 : 2;
+    else if (in->op == GA_REDUCE_ANY) want->fast8 = 3;
+    else if (in->op == GA_REDUCE_ALL) want->fast8 = 4;
+  }
+  return GA_NO_ERROR;
+}
+
+/* Test and tooling hook: the plan GpuReduction_call would make for a source of
+ * the given shape and byte strides on a device with `num_sms` SMs, without any
+ * device. Destinations are taken as C-contiguous. `base` stands for the
+ * address of the source's first element (its alignment decides vector width).
+ * out[0..19] = shape (0 rows, 1 cols, 2 general), vec, group, flat, runs at
+ * once, one-run mode, lazy index, byte folding, threads per output (general),
+ * 64-bit index, splits, seg, nseg, units, grid x, grid y, block x, block y,
+ * outputs, reduced elements per output. Returns a GA_* code. */
+GPUARRAY_PUBLIC int gpuarray_b200_reduction_plan(int op, int src_tc, int dst_tc, unsigned int nd,
+                                                 const size_t *dims, const ssize_t *strides,
+                                                 unsigned int reduxLen, const int *reduxList,
+                                                 unsigned long long base, unsigned int num_sms,
+                                                 unsigned long long *out) {
+  GpuArray s, d;
+  size_t ddims[64];
+  ssize_t dstr[64];
+  unsigned char red[64];
+  rd_layout L;
+  rd_variant want;
+  rd_plan_in in;
+  unsigned grid[3], block[3], i, k;
+  size_t step;
+  int err;
+  if (nd == 0 || nd > 64 || reduxLen == 0 || reduxLen > nd || (int)op < 0 ||
+      op >= GA_REDUCE_ENDSUPPORTED)
+    return ga_err_set(ga_global_err, GA_INVALID_ERROR, "Invalid rank, axis count or operator");
+  memset(red, 0, sizeof(red));
+  for (i = 0; i < reduxLen; i++) {
+    if (reduxList[i] < 0 || (unsigned)reduxList[i] >= nd || red[reduxList[i]])
+      return ga_err_set(ga_global_err, GA_INVALID_ERROR, "Bad reduction axis");
+    red[reduxList[i]] = 1;
+  }
+  memset(&s, 0, sizeof(s));
+  memset(&d, 0, sizeof(d));
+  s.nd = nd;
+  s.dimensions = (size_t *)dims;
+  s.strides = (ssize_t *)strides;
+  for (i = 0, k = 0; i < nd; i++)
+    if (!red[i]) ddims[k++] = dims[i];
+  step = gpuarray_get_elsize(dst_tc);
+  for (i = k; i > 0; i--) {
+    dstr[i - 1] = (ssize_t)step;
+    step *= ddims[i - 1];
+  }
+  d.nd = k;
+  d.dimensions = ddims;
+  d.strides = dstr;
+  memset(&in, 0, sizeof(in));
+  in.e = ga_global_err;
+  in.op = (ga_reduce_op)op;
+  in.kind = op_is_pair(in.op);
+  in.src_tc = src_tc;
+  in.dst_tc = dst_tc;
+  in.need_val = op_writes_val(in.op);
+  in.need_idx = op_writes_idx(in.op);
+  in.num_sms = num_sms;
+  in.p_src = base;
+  err = normalise(in.kind, in.e, &L, in.need_val ? &d : NULL, in.need_idx ? &d : NULL, &s, red,
+                  reduxLen, reduxList);
+  if (err != GA_NO_ERROR) return err;
+  memset(out, 0, 20 * sizeof(*out));
+  out[18] = L.nf_total;
+  out[19] = L.nr_total;
+  if (L.nf_total == 0 || L.nr_total == 0) return GA_NO_ERROR;
+  err = rd_plan(&in, &L, &want, grid, block);
+  if (err != GA_NO_ERROR) return err;
+  out[0] = (unsigned long long)want.shape;
+  out[1] = (unsigned long long)want.vec;
+  out[2] = (unsigned long long)(want.group ? want.group : RD_THREADS);
+  out[3] = (unsigned long long)want.flat;
+  out[4] = (unsigned long long)(want.mu ? want.mu : 1);
+  out[5] = (unsigned long long)want.onerun;
+  out[6] = (unsigned long long)want.lazy;
+  out[7] = (unsigned long long)want.fast8;
+  out[8] = (unsigned long long)want.tpo;
+  out[9] = (unsigned long long)want.idx64;
+  out[10] = L.splits;
+  out[11] = L.seg;
+  out[12] = L.nseg;
+  out[13] = L.units;
+  out[14] = grid[0];
+  out[15] = grid[1];
+  out[16] = block[0];
+  out[17] = block[1];
+  return GA_NO_ERROR;
+}
+
 int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const GpuArray *s0,
                       unsigned reduxLen, const int *reduxList, int flags) {
   GpuReduction *gr = (GpuReduction *)cgr;
@@ -472,9 +750,8 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
   unsigned char red[64];
   rd_layout L;
   rd_variant want, *v1;
-  unsigned i, ndd, ctas_per_sm, seg_vecs, cta_min_vecs;
+  unsigned i, ndd;
   unsigned grid[3] = {1, 1, 1}, block[3] = {RD_THREADS, 1, 1};
-  size_t elsize, target;
   int err = GA_NO_ERROR, need_val, need_idx;
   CUdeviceptr p_src, p_d0 = 0, p_d1 = 0, p_val = 0, p_idx = 0, p_tic = 0;
   void *params[7];
@@ -529,184 +806,28 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
       return ga_err_set(ctx->err, GA_VALUE_ERROR, "Index destination must hold 8-byte integers");
   }
 
-  err = normalise(gr, &L, d0, d1, s0, red, reduxLen, reduxList);
+  err = normalise(gr->kind, ctx->err, &L, d0, d1, s0, red, reduxLen, reduxList);
   if (err != GA_NO_ERROR) return err;
   if (L.nf_total == 0) return GA_NO_ERROR;
   if (L.nr_total == 0 && gr->kind == 1)
     return ga_err_set(ctx->err, GA_VALUE_ERROR, "min/max over zero elements");
 
-  elsize = gpuarray_get_elsize(gr->src_tc);
   p_src = s0->data->ptr + s0->offset;
   if (d0 != NULL) p_d0 = d0->data->ptr + d0->offset;
   if (d1 != NULL) p_d1 = d1->data->ptr + d1->offset;
-  rd_tuning(&ctas_per_sm, &seg_vecs, &cta_min_vecs);
-  target = (size_t)ctx->num_sms * ctas_per_sm;
-
-  memset(&want, 0, sizeof(want));
-  want.dst_tc = d0 != NULL ? d0->typecode : gr->src_tc;
-  want.write_val = need_val;
-  want.write_idx = need_idx;
-  want.idx64 = L.nr_total >= 0xffffffffULL;
-  want.vec = 1;
-  want.tpo = 1;
-  L.splits = 1;
-
-  if (L.nr_total > 0 && L.nr >= 1 && L.rsrc[L.nr - 1] == (long long)elsize &&
-      L.rdim[L.nr - 1] >= 2) {
-    /* --- contiguous reduced run --- */
-    unsigned vec = (unsigned)(16 / elsize);
-    unsigned long long rows_outer = L.nr_total / L.rdim[L.nr - 1];
-    want.shape = SHAPE_ROWS;
-    if (vec > 1 && p_src % 16 == 0 && all_multiple(L.fsrc, (unsigned)L.nf, 16) &&
-        all_multiple(L.rsrc, (unsigned)L.nr - 1, 16))
-      want.vec = (int)vec;
-    L.inner = L.rdim[L.nr - 1];
-    {
-      unsigned long long nvrow = L.inner / (unsigned)want.vec, groups_target, nwork, blocks, share;
-      unsigned gpb;
-      /* Who shares a work item, and whether the reduced extent is split:
-       *  - plenty of outputs: a warp per output, no split;
-       *  - a moderate number of outputs with long runs: a CTA per output;
-       *  - few outputs: split the reduced extent (CTAs when the runs are long
-       *    and the outputs very few, which also keeps the partial count low). */
-      int need_split = 0;
-      /* loads one lane of a warp issues per run: short runs need help to keep
-       * enough bytes in flight (see the kernel's comment) */
-      unsigned long long nload = nvrow + (L.inner % (unsigned)want.vec != 0);
-      if (rows_outer == 1 && nload <= 256) {
-        unsigned g = 1, lpl;
-        while (g < 32 && g * rd_onerun_lpl < nload) g *= 2;
-        lpl = (unsigned)((nload + g - 1) / g);
-        want.onerun = 1;
-        want.group = (int)g;
-        want.mu = rd_onerun_mu ? (int)rd_onerun_mu : lpl <= 2 ? 4 : 2;
-        L.seg = L.inner;
-        L.nseg = 1;
-        L.units = 1;
-        gpb = RD_THREADS / g;
-        blocks = (L.nf_total + (unsigned long long)gpb * (unsigned)want.mu - 1) /
-                 ((unsigned long long)gpb * (unsigned)want.mu);
-        if (rd_onerun_ctas_per_sm && blocks > (unsigned long long)ctx->num_sms * rd_onerun_ctas_per_sm)
-          blocks = (unsigned long long)ctx->num_sms * rd_onerun_ctas_per_sm;
-        grid[0] = (unsigned)blocks;
-        goto rows_done;
-      }
-      want.flat = nvrow < 16;
-      want.mu = want.flat ? 1 : nload <= 64 ? 4 : nload <= 256 ? 2 : 1;
-      if (nvrow >= cta_min_vecs) want.group = RD_THREADS;
-      else if (L.nf_total >= (unsigned long long)ctx->num_sms * 16) want.group = 32;
-      else if (L.nf_total >= (unsigned long long)ctx->num_sms * 4 && nvrow >= 1024)
-        want.group = RD_THREADS;
-      else {
-        /* warps, unless long runs would leave them either too few or with
-         * shares too short to be worth a ticket (see the cap below) */
-        unsigned long long s_w = ((unsigned long long)target * (RD_THREADS / 32) + L.nf_total - 1) /
-                                 L.nf_total;
-        unsigned long long cap_w = L.nr_total * elsize / (24u << 10);
-        if (cap_w < 1) cap_w = 1;
-        if (s_w > cap_w) s_w = cap_w;
-        need_split = 1;
-        want.group = (nvrow >= 2048 && (L.nf_total < (unsigned long long)ctx->num_sms ||
-                                        L.nf_total * s_w < (unsigned long long)ctx->num_sms * 16))
-                         ? RD_THREADS : 32;
-      }
-      if (want.group == RD_THREADS) want.flat = 0, want.mu = 1;
-      gpb = RD_THREADS / (unsigned)want.group;
-      /* measured on B200: whole-CTA groups run best as a few long-lived CTAs
-       * per SM, warp groups as many (a full complement of resident warps) */
-      groups_target = want.group == RD_THREADS ? (unsigned long long)ctx->num_sms * 4
-                                               : (unsigned long long)target * gpb;
-      L.seg = L.inner;
-      L.nseg = 1;
-      L.units = rows_outer;
-      if (need_split) {
-        unsigned long long s;
-        if (!want.flat) {
-          unsigned long long seg = (unsigned long long)want.group * vec * seg_vecs;
-          if (seg < L.inner) {
-            L.seg = seg;
-            L.nseg = (L.inner + seg - 1) / seg;
-            L.units = rows_outer * L.nseg;
-          }
-        }
-        s = (groups_target + L.nf_total - 1) / L.nf_total;
-        if (want.group == 32) {
-          /* measured on B200: a warp's share should stay above ~24 KiB, or the
-           * ramp of each share and the ticketed finish outweigh the parallelism */
-          unsigned long long cap = L.nr_total * elsize / (24u << 10);
-          if (cap < 1) cap = 1;
-          if (s > cap) s = cap;
-        }
-        if (s > L.units) s = L.units;
-        if (s > 1u << 20) s = 1u << 20;
-        L.splits = s ? s : 1;
-      }
-      if (L.seg >= 0x7fffffffULL) {
-        /* a single run longer than 32-bit indexing: cut it even without splitting */
-        L.seg = (unsigned long long)want.group * vec * seg_vecs * 1024;
-        L.nseg = (L.inner + L.seg - 1) / L.seg;
-        L.units = rows_outer * L.nseg;
-      }
-      make_div32((unsigned int)(nvrow ? nvrow : 1), L.dv);
-      share = (L.units / L.splits + 1) * (nvrow + 1);
-      if (want.flat && share >= 0xffffffffULL)
-        return ga_err_set(ctx->err, GA_XLARGE_ERROR, "Reduction share exceeds 32-bit indexing");
-      nwork = L.nf_total * L.splits;
-      blocks = (nwork + gpb - 1) / gpb;
-      grid[0] = blocks > 0x7fffffffULL ? 0x7fffffffu : (unsigned)blocks;
-    rows_done:;
-    }
-  } else if (L.nr_total > 0 && L.nf >= 1 && L.fsrc[L.nf - 1] == (long long)elsize &&
-             L.fdim[L.nf - 1] >= 16) {
-    /* --- contiguous kept run --- */
-    unsigned vec = (unsigned)(16 / elsize);
-    unsigned long long ko, nwork, s;
-    if (vec > 4) vec = 4;
-    want.shape = SHAPE_COLS;
-    L.inner = L.fdim[L.nf - 1];
-    while (vec > 1 && !(L.inner % vec == 0 && p_src % (vec * elsize) == 0 &&
-                        all_multiple(L.fsrc, (unsigned)L.nf - 1, (long long)(vec * elsize)) &&
-                        all_multiple(L.rsrc, (unsigned)L.nr, (long long)(vec * elsize))))
-      vec /= 2;
-    want.vec = (int)vec;
-    L.tiles = (L.inner + 32ULL * vec - 1) / (32ULL * vec);
-    ko = L.nf_total / L.inner;
-    nwork = ko * L.tiles;
-    s = ((unsigned long long)ctx->num_sms * rd_cols_ctas_per_sm + nwork - 1) / nwork;
-    if (s > (L.nr_total + RD_BY * 8 - 1) / (RD_BY * 8)) s = (L.nr_total + RD_BY * 8 - 1) / (RD_BY * 8);
-    if (s > 1024) s = 1024;
-    L.splits = s ? s : 1;
-    L.units = nwork; /* tickets: one per column tile */
-    grid[0] = nwork > 0x7fffffffULL ? 0x7fffffffu : (unsigned)nwork;
-    grid[1] = (unsigned)L.splits;
-    block[0] = 32;
-    block[1] = RD_BY;
-  } else {
-    /* --- arbitrary strides --- */
-    unsigned long long groups_per_block, blocks;
-    want.shape = SHAPE_GENERAL;
-    if (L.nr_total >= 2048 && L.nf_total < 4096) want.tpo = RD_THREADS;
-    else if (L.nr_total >= 64) want.tpo = 32;
-    groups_per_block = RD_THREADS / (unsigned)want.tpo;
-    blocks = (L.nf_total + groups_per_block - 1) / groups_per_block;
-    if (blocks > (unsigned long long)target * 8) blocks = (unsigned long long)target * 8;
-    grid[0] = (unsigned)(blocks ? blocks : 1);
-  }
-
-  /* (value, index) operators over long runs scan values only (GA_RD_LAZY). Measured on
-   * B200: 32 KiB fp32 rows (64 vectors per lane) 49.7 -> 46.2 us for 268 MB, the headline's
-   * 128 KB rows 321.7 -> 316.5 us; 8 KiB fp64 runs (16 per lane) lose 6 % to the extra
-   * look at the winning vector, hence the threshold. */
-  if (gr->kind == 1 && want.shape == SHAPE_ROWS && !want.onerun && !want.flat && want.mu <= 1 &&
-      rd_lazy && L.seg / (unsigned)want.vec / (unsigned)(want.group ? want.group : RD_THREADS) >= rd_lazy_min)
-    want.lazy = 1;
-  /* whole-word arithmetic on vectors of 1-byte elements (see ga__fold_lanes) */
-  if (elsize == 1 && want.vec % 4 == 0 && want.shape == SHAPE_ROWS) {
-    if (gr->op == GA_REDUCE_SUM && !tc_is_float(want.dst_tc) &&
-        gpuarray_get_elsize(want.dst_tc) >= 4)
-      want.fast8 = gr->src_tc == GA_BYTE ? 1 : 2;
-    else if (gr->op == GA_REDUCE_ANY) want.fast8 = 3;
-    else if (gr->op == GA_REDUCE_ALL) want.fast8 = 4;
+  {
+    rd_plan_in in;
+    in.e = ctx->err;
+    in.kind = gr->kind;
+    in.op = gr->op;
+    in.src_tc = gr->src_tc;
+    in.dst_tc = d0 != NULL ? d0->typecode : gr->src_tc;
+    in.need_val = need_val;
+    in.need_idx = need_idx;
+    in.num_sms = ctx->num_sms;
+    in.p_src = p_src;
+    err = rd_plan(&in, &L, &want, grid, block);
+    if (err != GA_NO_ERROR) return err;
   }
   v1 = get_variant(gr, &want, &err);
   if (v1 == NULL) return err;
