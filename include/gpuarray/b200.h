@@ -44,6 +44,22 @@ GPUARRAY_PUBLIC char *gpuarray_b200_elemwise_source(const char *preamble, const 
 GPUARRAY_PUBLIC char *gpuarray_b200_reduction_source(int op, int src_tc, int dst_tc, int shape,
                                                      int vec, int idx64, int tpo, int group);
 
+/* The shape work of GpuElemwise_call on plain shape / byte-stride lists, with no
+ * device: contiguous-fast-path test (reference check_contig,
+ * src/gpuarray_elemwise.c:547-576), rank padding, broadcast, output-defines-
+ * shape and dimension collapsing (check_basic, :272-383). args[i] gives the
+ * typecode and GE_* flags of argument i; nds/dims/strides describe the array
+ * arguments (entries of GE_SCALAR arguments are ignored). Returns the GA_* code
+ * the call would return up to that point; out[0] = 0 contiguous kernel / 1
+ * strided kernels, out[1] = element count, out[2] = rank after collapsing,
+ * then the collapsed extents, then per array argument its collapsed byte
+ * strides (strided path only). out must hold 3 + 8 + 8 * n words. */
+GPUARRAY_PUBLIC int gpuarray_b200_elemwise_shapes(unsigned int n, const gpuelemwise_arg *args,
+                                                  const unsigned int *nds,
+                                                  const size_t *const *dims,
+                                                  const ssize_t *const *strides, int call_flags,
+                                                  long long *out);
+
 /* The plan GpuReduction_call would make (kernel variant, split of the reduced
  * extent, launch geometry) for a source of the given shape and byte strides on a
  * device with num_sms multiprocessors, computed on the host alone. `base` stands

@@ -774,6 +774,81 @@ static int call_transpose(GpuElemwise *ge, void **args, size_t n, unsigned int n
   return ga_launch(ctx, &v->fn, grid, block, 0, ge->params);
 }
 
+/* Test and tooling hook: the shape work of GpuElemwise_call (contiguous fast
+ * path test, rank padding, broadcast, output-defines-shape, dimension
+ * collapsing) on plain shape / byte-stride lists, without any device.
+ *   n            number of arguments; args[i] gives typecode and GE_* flags
+ *   nds[i], dims[i], strides[i]   rank, extents, byte strides of array i
+ *                (ignored for GE_SCALAR arguments)
+ * Returns the GA_* code the call would return up to this point. out[0] = path
+ * (0 contiguous kernel, 1 strided/transposing kernels), out[1] = element count,
+ * out[2] = rank after collapsing (1 for the contiguous path), then that many
+ * collapsed extents, then per array argument that many collapsed byte strides
+ * (strided path only). `out` must hold 3 + 8 + 8 * n words. */
+GPUARRAY_PUBLIC int gpuarray_b200_elemwise_shapes(unsigned int n, const gpuelemwise_arg *args,
+                                                  const unsigned int *nds,
+                                                  const size_t *const *dims,
+                                                  const ssize_t *const *strides, int call_flags,
+                                                  long long *out) {
+  struct _gpucontext fake;
+  GpuElemwise ge;
+  GpuArray arrs[32];
+  void *ptrs[32];
+  unsigned int i, j, k, nd = 0;
+  size_t cnt = 0;
+  int err;
+  if (n > 32) return ga_err_set(ga_global_err, GA_UNSUPPORTED_ERROR, "More than 32 arguments");
+  memset(&fake, 0, sizeof(fake));
+  fake.err = ga_global_err;
+  memset(&ge, 0, sizeof(ge));
+  ge.ctx = &fake;
+  ge.args = (gpuelemwise_arg *)args;
+  ge.n = n;
+  for (i = 0; i < n; i++) {
+    ptrs[i] = &arrs[i];
+    if (!is_array(&args[i])) continue;
+    ge.narray++;
+    memset(&arrs[i], 0, sizeof(arrs[i]));
+    arrs[i].nd = nds[i];
+    arrs[i].dimensions = (size_t *)dims[i];
+    arrs[i].strides = (ssize_t *)strides[i];
+    arrs[i].typecode = args[i].typecode;
+    arrs[i].flags = GA_ALIGNED | GA_WRITEABLE;
+    GpuArray_fix_flags(&arrs[i]);
+  }
+  ge.strides = calloc(ge.narray ? ge.narray : 1, sizeof(ssize_t *));
+  if (ge.strides == NULL || grow_scratch(&ge, 8) != 0) {
+    err = ga_err_sys(ga_global_err, "calloc");
+    goto done;
+  }
+  if (check_contig(&ge, ptrs, &cnt)) {
+    out[0] = 0;
+    out[1] = (long long)cnt;
+    out[2] = 1;
+    out[3] = (long long)cnt;
+    err = GA_NO_ERROR;
+    goto done;
+  }
+  err = check_basic(&ge, ptrs, call_flags, &cnt, &nd);
+  if (err != GA_NO_ERROR) goto done;
+  if (nd > 8) {
+    err = ga_err_set(ga_global_err, GA_UNSUPPORTED_ERROR, "More than 8 dimensions remain");
+    goto done;
+  }
+  out[0] = 1;
+  out[1] = (long long)cnt;
+  out[2] = (long long)nd;
+  for (j = 0; j < nd; j++) out[3 + j] = (long long)ge.dims[j];
+  for (k = 0; k < ge.narray; k++)
+    for (j = 0; j < nd; j++) out[3 + nd + k * nd + j] = (long long)ge.strides[k][j];
+done:
+  if (ge.strides != NULL)
+    for (k = 0; k < ge.narray; k++) free(ge.strides[k]);
+  free(ge.strides);
+  free(ge.dims);
+  return err;
+}
+
 int GpuElemwise_call(GpuElemwise *ge, void **args, int flags) {
   gpucontext *ctx = ge->ctx;
   size_t n = 0;

@@ -1,0 +1,155 @@
+"""Host-side shape logic of GpuElemwise_call (reference check_contig /
+check_basic, src/gpuarray_elemwise.c:272-383,547-576), exercised without a
+device through gpuarray_b200_elemwise_shapes: contiguous fast path, rank
+padding on the left, broadcast of inputs only, output-defines-shape, and
+dimension collapsing (checked against the oracle's collapse and NumPy)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+
+class Arg(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char_p), ("typecode", ctypes.c_int), ("flags", ctypes.c_int)]
+
+
+def shapes(api, specs, flags):
+    """specs: list of (dtype, GE flags, shape or None, byte strides or None)."""
+    L = api.lib()
+    fn = L.gpuarray_b200_elemwise_shapes
+    fn.restype = ctypes.c_int
+    n = len(specs)
+    args = (Arg * n)()
+    nds = (ctypes.c_uint * n)()
+    dimp = (ctypes.POINTER(ctypes.c_size_t) * n)()
+    strp = (ctypes.POINTER(ctypes.c_ssize_t) * n)()
+    keep = []
+    for i, (dt, fl, shape, strides) in enumerate(specs):
+        args[i].name = b"a%d" % i
+        args[i].typecode = api.typecode(np.dtype(dt))
+        args[i].flags = fl
+        if shape is not None:
+            nds[i] = len(shape)
+            d = (ctypes.c_size_t * max(len(shape), 1))(*shape)
+            s = (ctypes.c_ssize_t * max(len(shape), 1))(*strides)
+            keep += [d, s]
+            dimp[i] = ctypes.cast(d, ctypes.POINTER(ctypes.c_size_t))
+            strp[i] = ctypes.cast(s, ctypes.POINTER(ctypes.c_ssize_t))
+    out = (ctypes.c_longlong * (3 + 8 + 8 * n))()
+    err = fn(n, args, nds, dimp, strp, flags, out)
+    if err != 0:
+        return err, None
+    nd = out[2]
+    res = {"path": out[0], "n": out[1], "dims": list(out[3:3 + nd])}
+    narr = sum(1 for sp in specs if sp[2] is not None)
+    if out[0] == 1:
+        res["strides"] = [list(out[3 + nd + k * nd:3 + nd + (k + 1) * nd]) for k in range(narr)]
+    return 0, res
+
+
+def cs(shape, isz):
+    s, step = [], isz
+    for d in reversed(shape):
+        s.insert(0, step)
+        step *= d
+    return s
+
+
+def fs(shape, isz):
+    s, step = [], isz
+    for d in shape:
+        s.append(step)
+        step *= d
+    return s
+
+
+def test_contiguous_fast_path(api):
+    R, W = api.GE_READ, api.GE_WRITE
+    sh = (7, 5, 3)
+    err, r = shapes(api, [(np.float32, R, sh, cs(sh, 4)), (np.float64, R, sh, cs(sh, 8)),
+                          (np.float32, W, sh, cs(sh, 4))], 0)
+    assert err == 0 and r["path"] == 0 and r["n"] == 105          # dtype mix does not matter
+    err, r = shapes(api, [(np.float32, R, sh, fs(sh, 4)), (np.float32, W, sh, fs(sh, 4))], 0)
+    assert err == 0 and r["path"] == 0                            # all F-contiguous
+    err, r = shapes(api, [(np.float32, R, sh, fs(sh, 4)), (np.float32, W, sh, cs(sh, 4))], 0)
+    assert err == 0 and r["path"] == 1 and r["n"] == 105          # C and F mixed: strided kernels
+    err, r = shapes(api, [(np.float32, R, (), []), (np.float32, W, (), [])], 0)
+    assert err == 0 and r["path"] == 0 and r["n"] == 1            # 0-d arrays
+    err, r = shapes(api, [(np.float32, R, (4, 0), cs((4, 0), 4)), (np.float32, W, (4, 0), cs((4, 0), 4))], 0)
+    assert err == 0 and r["n"] == 0                               # zero-size: success, nothing to do
+    # a scalar argument takes no part in the shape
+    err, r = shapes(api, [(np.float32, R, sh, cs(sh, 4)), (np.float32, api.GE_SCALAR, None, None),
+                          (np.float32, W, sh, cs(sh, 4))], 0)
+    assert err == 0 and r["path"] == 0
+
+
+def test_broadcast_padshape_and_output_rules(api):
+    R, W = api.GE_READ, api.GE_WRITE
+    B, P = api.GE_BROADCAST, api.GE_PADSHAPE
+    a = (np.float32, R, (2, 1), cs((2, 1), 4))
+    b = (np.float32, R, (1, 3), cs((1, 3), 4))
+    out = (np.float32, W, (2, 3), cs((2, 3), 4))
+    assert shapes(api, [a, b, out], 0)[0] == api.GA_VALUE_ERROR    # broadcast needs the flag
+    err, r = shapes(api, [a, b, out], B)
+    assert err == 0 and r["path"] == 1 and r["dims"] == [2, 3]
+    assert r["strides"] == [[4, 0], [0, 4], [12, 4]]               # size-1 dims get stride 0
+    # the first output defines the shape and never broadcasts, flag or not
+    small_out = (np.float32, W, (1, 3), cs((1, 3), 4))
+    big_in = (np.float32, R, (2, 3), cs((2, 3), 4))
+    assert shapes(api, [big_in, small_out], B)[0] == api.GA_VALUE_ERROR
+    # ranks must agree unless GE_PADSHAPE, which pads on the left
+    v = (np.float32, R, (3,), [4])
+    assert shapes(api, [v, out], B)[0] == api.GA_VALUE_ERROR
+    err, r = shapes(api, [v, out], B | P)
+    assert err == 0 and r["dims"] == [2, 3] and r["strides"][0] == [0, 4]
+    # ... but an output of lower rank is refused
+    low_out = (np.float32, W, (3,), [4])
+    assert shapes(api, [big_in, low_out], B | P)[0] == api.GA_VALUE_ERROR
+    # no output at all
+    assert shapes(api, [a, b], B)[0] == api.GA_VALUE_ERROR
+
+
+def test_config4_collapses_to_three_dimensions(api):
+    """fp16 NHWC buffer viewed as NCHW + per-channel bias -> NCHW output."""
+    R, W = api.GE_READ, api.GE_WRITE
+    x = (np.float16, R, (64, 256, 56, 56), [1605632, 2, 28672, 512])
+    bias = (np.float16, R, (1, 256, 1, 1), [512, 2, 2, 2])
+    y = (np.float16, W, (64, 256, 56, 56), cs((64, 256, 56, 56), 2))
+    err, r = shapes(api, [x, bias, y], api.GE_BROADCAST)
+    assert err == 0 and r["path"] == 1 and r["n"] == 51380224
+    assert r["dims"] == [64, 256, 3136]
+    assert r["strides"] == [[1605632, 2, 512], [0, 2, 0], [1605632, 6272, 2]]
+
+
+def test_random_broadcasts_match_numpy_and_the_oracle_collapse(api, oracle, rng):
+    R, W, B = api.GE_READ, api.GE_WRITE, api.GE_BROADCAST
+    done = 0
+    for _ in range(600):
+        nd = int(rng.integers(1, 6))
+        shape = tuple(int(d) for d in rng.choice([1, 2, 3, 4, 5], size=nd))
+        specs, views = [], []
+        for k in range(int(rng.integers(1, 4))):
+            ish = tuple(1 if rng.random() < 0.3 else d for d in shape)
+            base = np.zeros(tuple(2 * d for d in ish), np.float32)
+            v = base[tuple(slice(0, d) for d in ish)]                  # a window: non-trivial strides
+            if rng.random() < 0.4 and nd > 1:
+                perm = rng.permutation(nd)
+                v = np.zeros(tuple(ish[i] for i in perm), np.float32).transpose(np.argsort(perm))
+            assert v.shape == ish
+            specs.append((np.float32, R, ish, list(v.strides)))
+            views.append(v)
+        o = np.zeros(shape, np.float32)
+        specs.append((np.float32, W, shape, list(o.strides)))
+        views.append(o)
+        err, r = shapes(api, specs, B)
+        assert err == 0
+        if r["path"] == 0:
+            assert all(s[2] == shape for s in specs)
+            continue
+        # expectation: NumPy's broadcast strides (0 on size-1 dims), then the oracle's collapse
+        bstr = [[0 if v.shape[j] == 1 else v.strides[j] for j in range(nd)] for v in views]
+        edims, estr = oracle.collapse(list(shape), bstr)
+        assert r["dims"] == edims and r["strides"] == estr
+        assert r["n"] == int(np.prod(shape))
+        done += 1
+    assert done > 300
