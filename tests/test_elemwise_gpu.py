@@ -336,6 +336,19 @@ def test_strided_layouts(api, ctx, oracle, rng, shape, dt):
                  [a, b, c], convert_f16=f16)
 
 
+def test_high_rank_layouts_that_do_not_collapse(api, ctx, oracle, rng):
+    """The rank given to GpuElemwise_new is only a hint (the reference's
+    tests/check_elemwise.c:552 passes 0 and calls with 4-D arrays): 6 and 9
+    dimensions, step-2 windows on every axis so that nothing collapses."""
+    for shape in ((2, 3, 2, 3, 2, 5), (2, 2, 2, 3, 2, 2, 2, 2, 3)):
+        va = strided_views(rng, np.float32, shape)
+        vb = strided_views(rng, np.float32, shape)
+        for i in (2, 3):                                             # window, reversed
+            run_both(api, ctx, oracle, "c = a * b", [("a", np.float32, R), ("b", np.float32, R),
+                                                      ("c", np.float32, W)],
+                     [va[i], vb[2], strided_views(rng, np.float32, shape)[2]])
+
+
 @pytest.mark.parametrize("shape", [(2, 5, 7, 24), (3, 8, 8, 64), (1, 3, 5, 130), (2, 17, 9, 16)])
 def test_nhwc_view_to_nchw_bias_relu(api, ctx, oracle, rng, shape):
     """The broadcast + transposing case: NHWC buffer viewed as NCHW, bias (1,C,1,1)."""

@@ -242,6 +242,17 @@ def test_one_byte_elements_fold_by_words(api, ctx, oracle, rng, shape, axes):
         check_reduce(api, ctx, oracle, name, np.zeros(shape, np.bool_), axes, out_dtype=np.bool_)
 
 
+def test_high_rank_windows_that_do_not_collapse(api, ctx, oracle, rng):
+    """Seven dimensions, step-2 windows on every axis: up to 5 kept and 4
+    reduced dimensions survive collapsing."""
+    shape = (3, 2, 4, 2, 3, 2, 5)
+    x = make_data(rng, np.float32, shape)
+    for axes in ([1, 3, 5], [0, 2, 4, 6], [6], [0], [5, 1], [2, 3, 4, 5, 6]):
+        for name in ("sum", "maxandargmax"):
+            check_reduce(api, ctx, oracle, name, x, axes, layout="window")
+            check_reduce(api, ctx, oracle, name, x, axes, layout="F")
+
+
 def test_bitwise_on_floats_is_refused(api, ctx):
     with pytest.raises(api.GpuArrayException) as ei:
         api.GpuReduction(ctx, api.GA_REDUCE_XOR, np.float32)
