@@ -170,6 +170,11 @@ def lib():
         sig("gpucomm_get_rank", ci, vp, ctypes.POINTER(ci))
         sig("gpucomm_all_reduce", ci, vp, sz, vp, sz, sz, ci, ci, vp)
         sig("GpuArray_all_reduce", ci, A, A, ci, vp)
+        sig("GpuArray_reduce", ci, A, A, ci, ci, vp)
+        sig("GpuArray_reduce_from", ci, A, ci, ci, vp)
+        sig("GpuArray_reduce_scatter", ci, A, A, ci, vp)
+        sig("GpuArray_broadcast", ci, A, ci, vp)
+        sig("GpuArray_all_gather", ci, A, A, vp)
     sig("gpuarray_b200_error_code", ci, vp)
     sig("gpuarray_b200_sum_f32_noalloc", ci, vp, sz, vp, vp)
     sig("gpuarray_b200_launch_count", ctypes.c_ulonglong)
@@ -567,6 +572,25 @@ class GpuComm:
     def all_reduce(self, src, dst, opcode):
         _check(self.ctx.ptr, lib().GpuArray_all_reduce(ctypes.byref(src.ga), ctypes.byref(dst.ga),
                                                        opcode, self.ptr))
+
+    def reduce(self, src, dst, opcode, root):
+        """dst is the root's result array; the other ranks pass None."""
+        if dst is None:
+            _check(self.ctx.ptr, lib().GpuArray_reduce_from(ctypes.byref(src.ga), opcode, root, self.ptr))
+        else:
+            _check(self.ctx.ptr, lib().GpuArray_reduce(ctypes.byref(src.ga), ctypes.byref(dst.ga),
+                                                       opcode, root, self.ptr))
+
+    def reduce_scatter(self, src, dst, opcode):
+        _check(self.ctx.ptr, lib().GpuArray_reduce_scatter(ctypes.byref(src.ga), ctypes.byref(dst.ga),
+                                                           opcode, self.ptr))
+
+    def broadcast(self, arr, root):
+        _check(self.ctx.ptr, lib().GpuArray_broadcast(ctypes.byref(arr.ga), root, self.ptr))
+
+    def all_gather(self, src, dst):
+        _check(self.ctx.ptr, lib().GpuArray_all_gather(ctypes.byref(src.ga), ctypes.byref(dst.ga),
+                                                       self.ptr))
 
     def free(self):
         if self.ptr is not None:

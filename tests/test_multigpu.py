@@ -73,6 +73,29 @@ def _worker(rank, world, q_id, q_err):
         bv, bi = sharding.finish_minmaxarg(allreduce, v.to_numpy(), gi)
         wv, wi = O.minmaxarg(xt, [0, 2])
         assert (bv == wv).all() and (bi == wi).all()
+        # the other collectives of the reference's interface
+        # (src/gpuarray/collectives.h): reduce to a root, reduce-scatter,
+        # broadcast, all-gather
+        a = np.arange(6 * world, dtype=np.float32).reshape(world, 6) + 100 * rank
+        ga = api.GpuArray.from_numpy(ctx, a)
+        if rank == 1:
+            res = api.GpuArray.empty(ctx, a.shape, np.float32)
+            comm.reduce(ga, res, api.GA_SUM, 1)
+            want = sum(np.arange(6 * world, dtype=np.float32).reshape(world, 6) + 100 * r
+                       for r in range(world))
+            assert (res.to_numpy() == want).all()
+        else:
+            comm.reduce(ga, None, api.GA_SUM, 1)
+        part = api.GpuArray.empty(ctx, (6,), np.float32)
+        comm.reduce_scatter(ga, part, api.GA_MAX)
+        assert (part.to_numpy() == a[rank] - 100 * rank + 100 * (world - 1)).all()
+        b = api.GpuArray.from_numpy(ctx, np.full(5, rank + 7, np.int32))
+        comm.broadcast(b, 0)
+        assert (b.to_numpy() == 7).all()
+        mine = api.GpuArray.from_numpy(ctx, np.full(3, rank, np.int64))
+        everyone = api.GpuArray.empty(ctx, (world, 3), np.int64)
+        comm.all_gather(mine, everyone)
+        assert (everyone.to_numpy() == np.arange(world)[:, None]).all()
         ctx.sync()
         comm.free()
         ctx.close()
