@@ -295,7 +295,10 @@ class GpuArray:
 
     @classmethod
     def from_pointer(cls, ctx, devptr, shape, dtype, strides=None, nbytes=None, writeable=True):
-        """View over external device memory (borrowed; caller keeps it alive)."""
+        """View over external device memory (borrowed; caller keeps it alive).
+        `devptr` is the address of element [0, ..., 0]; with `strides` (bytes,
+        may be negative) the wrapped buffer is the span the view reaches, or
+        `nbytes` starting at `devptr` when that is given."""
         dtype = np.dtype(dtype)
         shape = tuple(int(s) for s in shape)
         if strides is None:
@@ -303,15 +306,26 @@ class GpuArray:
             for s in reversed(shape):
                 strides.insert(0, step)
                 step *= s
+        lo = hi = 0
+        if 0 not in shape:
+            for d, st in zip(shape, strides):
+                span = (d - 1) * int(st)
+                if span < 0:
+                    lo += span
+                else:
+                    hi += span
+        hi += dtype.itemsize
         if nbytes is None:
-            nbytes = int(np.prod(shape, dtype=np.int64)) * dtype.itemsize
-        buf = ctx.wrap_device_pointer(devptr, nbytes)
+            base, offset, nbytes = devptr + lo, -lo, hi - lo
+        else:
+            base, offset = devptr, 0
+        buf = ctx.wrap_device_pointer(base, nbytes)
         if not buf:
             raise GpuArrayException("cuda_make_buf failed", GA_MEMORY_ERROR)
         self = cls(ctx)
         dims = (ctypes.c_size_t * max(len(shape), 1))(*shape)
         strs = (ctypes.c_ssize_t * max(len(shape), 1))(*strides)
-        err = lib().GpuArray_fromdata(ctypes.byref(self.ga), buf, 0, typecode(dtype), len(shape),
+        err = lib().GpuArray_fromdata(ctypes.byref(self.ga), buf, offset, typecode(dtype), len(shape),
                                       dims, strs, 1 if writeable else 0)
         lib().gpudata_release(buf)
         _check(ctx.ptr, err)

@@ -44,6 +44,26 @@ static int array_is_aligned(const GpuArray *a) {
   return 1;
 }
 
+/* Host-side stand-in for a memory checker: the lowest and highest byte an
+ * array can reach, from its offset, extents and byte strides, must lie inside
+ * its buffer. Kernels are only launched on arrays that pass, so a wrong
+ * GpuArray (hand-built with GpuArray_fromdata, say) is a host error instead of
+ * a device fault. */
+int ga_array_in_bounds(const GpuArray *a) {
+  long long lo = (long long)a->offset, hi = (long long)a->offset;
+  unsigned int i;
+  if (a->data == NULL) return 0;
+  for (i = 0; i < a->nd; i++) {
+    long long span;
+    if (a->dimensions[i] == 0) return 1; /* no element at all */
+    span = (long long)(a->dimensions[i] - 1) * (long long)a->strides[i];
+    if (span < 0) lo += span;
+    else hi += span;
+  }
+  hi += (long long)gpuarray_get_elsize(a->typecode);
+  return lo >= 0 && (unsigned long long)hi <= (unsigned long long)a->data->sz;
+}
+
 void GpuArray_fix_flags(GpuArray *a) {
   a->flags &= GA_WRITEABLE;
   if (ga_array_is_c_contiguous(a)) a->flags |= GA_C_CONTIGUOUS;

@@ -869,6 +869,9 @@ int GpuElemwise_call(GpuElemwise *ge, void **args, int flags) {
         return ga_err_fmt(ctx->err, GA_UNALIGNED_ERROR, "Argument %u is not aligned", i);
       if (is_output(&ge->args[i]) && !GpuArray_ISWRITEABLE(a))
         return ga_err_fmt(ctx->err, GA_VALUE_ERROR, "Output argument %u is not writeable", i);
+      if (!ga_array_in_bounds(a))
+        return ga_err_fmt(ctx->err, GA_VALUE_ERROR,
+                          "Argument %u (%s) reaches outside its buffer", i, ge->args[i].name);
     }
   }
   if (check_contig(ge, args, &n)) {

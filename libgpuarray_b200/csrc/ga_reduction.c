@@ -293,6 +293,8 @@ static int check_dst(gpucontext *ctx, const GpuArray *d, const GpuArray *s, cons
     return ga_err_fmt(ctx->err, GA_VALUE_ERROR, "%s is not writeable", what);
   if (!GpuArray_ISALIGNED(d))
     return ga_err_fmt(ctx->err, GA_UNALIGNED_ERROR, "%s is not aligned", what);
+  if (!ga_array_in_bounds(d))
+    return ga_err_fmt(ctx->err, GA_VALUE_ERROR, "%s reaches outside its buffer", what);
   return GA_NO_ERROR;
 }
 
@@ -769,6 +771,8 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
   if (GpuArray_context(s0) != ctx)
     return ga_err_set(ctx->err, GA_VALUE_ERROR, "Source belongs to another context");
   if (!GpuArray_ISALIGNED(s0)) return ga_err_set(ctx->err, GA_UNALIGNED_ERROR, "Source is not aligned");
+  if (!ga_array_in_bounds(s0))
+    return ga_err_set(ctx->err, GA_VALUE_ERROR, "Source reaches outside its buffer");
   memset(red, 0, sizeof(red));
   for (i = 0; i < reduxLen; i++) {
     if (reduxList[i] < 0 || (unsigned)reduxList[i] >= s0->nd)

@@ -246,6 +246,8 @@ struct _gpukernel {
 
 GA_HIDDEN int ga_array_is_c_contiguous(const GpuArray *a);
 GA_HIDDEN int ga_array_is_f_contiguous(const GpuArray *a);
+/* 1 when every element of `a` lies inside its buffer (bytes [0, size) of a->data). */
+GA_HIDDEN int ga_array_in_bounds(const GpuArray *a);
 GA_HIDDEN void ga_extcopy_cache_free(gpucontext *ctx);
 GA_HIDDEN void ga_maxandargmax_cache_free(gpucontext *ctx);
 

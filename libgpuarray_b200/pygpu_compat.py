@@ -40,8 +40,7 @@ def _ctx(pygpu_context):
 
 
 def _wrap(ctx, a):
-    return api.GpuArray.from_pointer(ctx, int(a.gpudata), a.shape, a.dtype, strides=a.strides,
-                                     nbytes=max(int(a.size) * a.dtype.itemsize, 1))
+    return api.GpuArray.from_pointer(ctx, int(a.gpudata), a.shape, a.dtype, strides=a.strides)
 
 
 def _run(opcode, ary, redux, out_type, out):

@@ -121,3 +121,35 @@ def test_user_kernel_through_gpukernel(api, ctx, rng):
     want = (y.astype(np.float64) + 2.5 * x.astype(np.float64)).astype(np.float32)
     assert (gy.to_numpy() == want).all()
     L.GpuKernel_clear(ctypes.byref(k))
+
+
+def test_arrays_that_reach_outside_their_buffer_are_refused_on_the_host(api, ctx):
+    """A GpuArray whose extents and strides lead past its buffer (hand-built
+    with GpuArray_fromdata, here through from_pointer with too small a size)
+    is a host error, not a device access."""
+    real = api.GpuArray.from_numpy(ctx, np.arange(4096, dtype=np.float32))
+    out = api.GpuArray.empty(ctx, (4096,), np.float32)
+    short = api.GpuArray.from_pointer(ctx, real.devptr, (4096,), np.float32, nbytes=4096 * 4 - 4)
+    ge = api.GpuElemwise(ctx, "o = a + 1.0f", [("a", np.float32, api.GE_READ), ("o", np.float32, api.GE_WRITE)],
+                         nd=1)
+    with pytest.raises(api.GpuArrayException) as ei:
+        ge(short, out)
+    assert ei.value.code == api.GA_VALUE_ERROR and "outside its buffer" in str(ei.value)
+    with pytest.raises(api.GpuArrayException) as ei:
+        ge(real, short)                              # as the output
+    assert ei.value.code == api.GA_VALUE_ERROR
+    tot = api.GpuArray.empty(ctx, (), np.float32)
+    rs = api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.float32)
+    with pytest.raises(api.GpuArrayException) as ei:
+        rs(tot, None, short, [0])
+    assert ei.value.code == api.GA_VALUE_ERROR and "outside its buffer" in str(ei.value)
+    # a negative stride that starts at the buffer's first element walks below it
+    back = api.GpuArray.from_pointer(ctx, real.devptr, (16,), np.float32, strides=[-4], nbytes=64)
+    with pytest.raises(api.GpuArrayException):
+        rs(tot, None, back, [0])
+    # the same views with honest sizes work
+    ok = api.GpuArray.from_pointer(ctx, real.devptr + 15 * 4, (16,), np.float32, strides=[-4])
+    rs(tot, None, ok, [0])
+    assert float(tot.to_numpy()) == float(np.arange(16, dtype=np.float32).sum())
+    ge(real, out)
+    assert (out.to_numpy() == np.arange(4096, dtype=np.float32) + 1).all()
