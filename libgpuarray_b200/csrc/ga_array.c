@@ -660,6 +660,8 @@ int GpuArray_take1(GpuArray *a, const GpuArray *v, const GpuArray *i, int check_
     return ga_err_set(ctx->err, GA_VALUE_ERROR, "Destination array not writeable");
   if (!GpuArray_ISALIGNED(a) || !GpuArray_ISALIGNED(v) || !GpuArray_ISALIGNED(i))
     return ga_err_set(ctx->err, GA_UNALIGNED_ERROR, "Not all arrays are aligned");
+  if (!ga_array_in_bounds(a) || !ga_array_in_bounds(v) || !ga_array_in_bounds(i))
+    return ga_err_set(ctx->err, GA_VALUE_ERROR, "An array reaches outside its buffer");
   if (!GpuArray_IS_C_CONTIGUOUS(a))
     return ga_err_set(ctx->err, GA_INVALID_ERROR, "Destination array (a) not C-contiguous");
   if (!GpuArray_IS_C_CONTIGUOUS(i))
