@@ -752,7 +752,7 @@ int GpuArray_fdump(FILE *fd, const GpuArray *a) {
   size_t elsize = GpuArray_ITEMSIZE(a), n = array_nelems(a), k;
   char *buf, *p;
   int err;
-  buf = malloc((n * elsize) != 0 ? n * elsize : 1);
+  buf = calloc((n * elsize) != 0 ? n * elsize : 1, 1);
   if (buf == NULL) return ga_err_set(ctx->err, GA_MEMORY_ERROR, "Out of memory");
   err = GpuArray_read(buf, n * elsize, a);
   for (k = 0, p = buf; err == GA_NO_ERROR && k < n; k++, p += elsize) {

@@ -107,9 +107,11 @@ static void disk_put(const char *dir, const uint64_t key[2], const char *bin, si
   snprintf(tmp, sizeof(tmp), "%s.%ld.tmp", path, (long)getpid());
   f = fopen(tmp, "wb");
   if (f == NULL) return;
-  if (fwrite(bin, 1, sz, f) == sz && fclose(f) == 0) rename(tmp, path);
-  else {
-    unlink(tmp);
+  {
+    const int written = fwrite(bin, 1, sz, f) == sz;
+    const int closed = fclose(f) == 0; /* always close, even after a short write */
+    if (written && closed) rename(tmp, path);
+    else unlink(tmp);
   }
 }
 
