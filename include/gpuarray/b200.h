@@ -60,6 +60,24 @@ GPUARRAY_PUBLIC int gpuarray_b200_elemwise_shapes(unsigned int n, const gpuelemw
                                                   const ssize_t *const *strides, int call_flags,
                                                   long long *out);
 
+/* Everything GpuElemwise_call decides for a call (kernel, widths, access modes,
+ * tile, launch geometry), computed on the host alone for arrays given by rank,
+ * extents, byte strides and the address of their first element (alignment only).
+ * obj_flags as for GpuElemwise_new, call_flags as for GpuElemwise_call.
+ * out[0..15] = kernel (0 contiguous, 1 strided, 2 tiled transpose), elements per
+ * thread chunk, chunks in flight, rank after collapsing, index width bits, access
+ * modes (2 bits per array argument: 0 gather, 1 vector, 2 broadcast, 3 staged
+ * through shared memory), tile P, tile Q, P positions per thread, grid x/y/z,
+ * block x/y/z, element count. Reference counterpart of the decisions:
+ * src/gpuarray_elemwise.c:385-442,578-602 and src/gpuarray_kernel.c:38-89. */
+GPUARRAY_PUBLIC int gpuarray_b200_elemwise_plan(unsigned int n, const gpuelemwise_arg *args,
+                                                const unsigned int *nds,
+                                                const size_t *const *dims,
+                                                const ssize_t *const *strides,
+                                                const unsigned long long *bases, int obj_flags,
+                                                int call_flags, unsigned int num_sms,
+                                                unsigned long long *out);
+
 /* The plan GpuReduction_call would make (kernel variant, split of the reduced
  * extent, launch geometry) for a source of the given shape and byte strides on a
  * device with num_sms multiprocessors, computed on the host alone. `base` stands

@@ -49,6 +49,10 @@ struct _GpuElemwise {
   unsigned long long *blob;
   size_t blob_words;
   void **params;
+  /* dry run (gpuarray_b200_elemwise_plan): choose, record, launch nothing */
+  int dry;
+  ew_variant dry_variant;
+  unsigned dry_grid[3], dry_block[3];
 };
 
 static int is_array(const gpuelemwise_arg *a) { return ISCLR(a->flags, GE_SCALAR); }
@@ -154,6 +158,11 @@ static char *gen_source(const GpuElemwise *ge, const ew_variant *v) {
 static ew_variant *get_variant(GpuElemwise *ge, const ew_variant *want, int *err) {
   ew_variant *v;
   char *src, *listing = NULL;
+  if (ge->dry) {
+    ge->dry_variant = *want;
+    ge->dry_variant.next = NULL;
+    return &ge->dry_variant;
+  }
   for (v = ge->variants; v != NULL; v = v->next)
     if (v->kind == want->kind && v->ept == want->ept && v->unroll == want->unroll &&
         v->nd == want->nd && v->idx32 == want->idx32 && v->modes == want->modes &&
@@ -360,6 +369,16 @@ void GpuElemwise_free(GpuElemwise *ge) {
 
 static CUdeviceptr array_base(const GpuArray *a) { return a->data->ptr + a->offset; }
 
+static int ew_launch(GpuElemwise *ge, const ew_variant *v, const unsigned grid[3],
+                     const unsigned block[3]) {
+  if (ge->dry) {
+    memcpy(ge->dry_grid, grid, sizeof(ge->dry_grid));
+    memcpy(ge->dry_block, block, sizeof(ge->dry_block));
+    return GA_NO_ERROR;
+  }
+  return ga_launch(ge->ctx, &v->fn, grid, block, 0, ge->params);
+}
+
 /* The contiguous fast path applies when every array has the same shape and
  * they are all C- or all F-contiguous (reference check_contig). Returns 1 and
  * the element count if so. */
@@ -424,7 +443,7 @@ static int call_contig(GpuElemwise *ge, void **args, size_t n) {
   if (capsm != 0 && blocks > (size_t)capsm * ctx->num_sms) blocks = (size_t)capsm * ctx->num_sms;
   if (blocks > 0x7fffffffu) blocks = 0x7fffffffu;
   grid[0] = (unsigned)blocks;
-  return ga_launch(ctx, &v->fn, grid, block, 0, ge->params);
+  return ew_launch(ge, v, grid, block);
 }
 
 static void make_div32(unsigned int d, unsigned int out[4]) {
@@ -606,7 +625,7 @@ static int call_strided(GpuElemwise *ge, void **args, size_t n, unsigned int nd)
   if (blocks > (size_t)capsm * ctx->num_sms) blocks = (size_t)capsm * ctx->num_sms;
   if (blocks > 0x7fffffffu) blocks = 0x7fffffffu;
   grid[0] = (unsigned)blocks;
-  return ga_launch(ctx, &v->fn, grid, block, 0, ge->params);
+  return ew_launch(ge, v, grid, block);
 }
 
 /* Tiled transpose: taken when some pure input is contiguous along a dimension
@@ -771,7 +790,7 @@ static int call_transpose(GpuElemwise *ge, void **args, size_t n, unsigned int n
     if (!is_array(&ge->args[i])) ge->params[p++] = args[i];
   ntiles = tiles_p * tiles_q * nouter;
   grid[0] = ntiles > 0x7fffffffULL ? 0x7fffffffu : (unsigned)ntiles;
-  return ga_launch(ctx, &v->fn, grid, block, 0, ge->params);
+  return ew_launch(ge, v, grid, block);
 }
 
 /* Test and tooling hook: the shape work of GpuElemwise_call (contiguous fast
@@ -846,6 +865,109 @@ done:
     for (k = 0; k < ge.narray; k++) free(ge.strides[k]);
   free(ge.strides);
   free(ge.dims);
+  return err;
+}
+
+/* Test and tooling hook: everything GpuElemwise_call decides for a call -
+ * kernel, widths, per-argument access modes, tile, launch geometry - computed
+ * on the host alone for arrays described by rank, extents, byte strides and the
+ * address of their first element (alignment only; nothing is dereferenced).
+ * obj_flags are the GpuElemwise_new flags (GE_CONVERT_F16 ...), call_flags the
+ * GpuElemwise_call flags. out[0..15] = kernel (0 contiguous, 1 strided, 2
+ * tiled transpose), elements per thread chunk, chunks in flight, rank after
+ * collapsing, index width bits (1: 32-bit indices, 2: 32-bit row offsets),
+ * access modes (2 bits per array: 0 gather, 1 vector, 2 broadcast, 3 staged
+ * through shared memory), tile P, tile Q, P positions per thread, grid x/y/z,
+ * block x/y/z, element count. */
+GPUARRAY_PUBLIC int gpuarray_b200_elemwise_plan(unsigned int n, const gpuelemwise_arg *args,
+                                                const unsigned int *nds,
+                                                const size_t *const *dims,
+                                                const ssize_t *const *strides,
+                                                const unsigned long long *bases, int obj_flags,
+                                                int call_flags, unsigned int num_sms,
+                                                unsigned long long *out) {
+  struct _gpucontext fake;
+  struct _gpudata bufs[32];
+  GpuElemwise ge;
+  GpuArray arrs[32];
+  void *ptrs[32];
+  unsigned int i, k, nd = 0;
+  size_t cnt = 0;
+  int err;
+  if (n > 32) return ga_err_set(ga_global_err, GA_UNSUPPORTED_ERROR, "More than 32 arguments");
+  memset(&fake, 0, sizeof(fake));
+  fake.err = ga_global_err;
+  fake.num_sms = num_sms;
+  memset(&ge, 0, sizeof(ge));
+  ge.ctx = &fake;
+  ge.args = (gpuelemwise_arg *)args;
+  ge.n = n;
+  ge.flags = obj_flags;
+  ge.dry = 1;
+  ge.min_elsize = 16;
+  ge.max_elsize = 1;
+  for (i = 0; i < n; i++) {
+    size_t es = gpuarray_get_elsize(args[i].typecode);
+    ptrs[i] = &arrs[i];
+    if (!is_array(&args[i])) continue;
+    ge.narray++;
+    if (es < ge.min_elsize) ge.min_elsize = (unsigned)es;
+    if (es > ge.max_elsize) ge.max_elsize = (unsigned)es;
+    memset(&bufs[i], 0, sizeof(bufs[i]));
+    bufs[i].ptr = (CUdeviceptr)bases[i];
+    bufs[i].ctx = &fake;
+    bufs[i].sz = bufs[i].asz = (size_t)-1;
+    bufs[i].refcnt = 1;
+    memset(&arrs[i], 0, sizeof(arrs[i]));
+    arrs[i].data = &bufs[i];
+    arrs[i].nd = nds[i];
+    arrs[i].dimensions = (size_t *)dims[i];
+    arrs[i].strides = (ssize_t *)strides[i];
+    arrs[i].typecode = args[i].typecode;
+    arrs[i].flags = GA_ALIGNED | GA_WRITEABLE;
+    GpuArray_fix_flags(&arrs[i]);
+  }
+  if (ge.narray == 0) ge.min_elsize = ge.max_elsize = 4;
+  ge.ept = (int)(16 / ge.min_elsize);
+  while (ge.ept > 1 && (unsigned)ge.ept * ge.max_elsize > 64) ge.ept /= 2;
+  ge.strides = calloc(ge.narray ? ge.narray : 1, sizeof(ssize_t *));
+  ge.params = calloc(n + 2, sizeof(void *));
+  if (ge.strides == NULL || ge.params == NULL || grow_scratch(&ge, 8) != 0) {
+    err = ga_err_sys(ga_global_err, "calloc");
+    goto done;
+  }
+  if (check_contig(&ge, ptrs, &cnt)) {
+    err = cnt == 0 ? GA_NO_ERROR : call_contig(&ge, ptrs, cnt);
+  } else {
+    err = check_basic(&ge, ptrs, call_flags, &cnt, &nd);
+    if (err == GA_NO_ERROR && cnt != 0) err = call_strided(&ge, ptrs, cnt, nd);
+  }
+  if (err != GA_NO_ERROR) goto done;
+  memset(out, 0, 16 * sizeof(*out));
+  out[15] = cnt;
+  if (cnt != 0) {
+    const ew_variant *v = &ge.dry_variant;
+    out[0] = (unsigned long long)v->kind;
+    out[1] = (unsigned long long)v->ept;
+    out[2] = (unsigned long long)v->unroll;
+    out[3] = v->nd;
+    out[4] = (unsigned long long)v->idx32;
+    out[5] = v->modes;
+    out[6] = (unsigned long long)v->tp;
+    out[7] = (unsigned long long)v->tq;
+    out[8] = (unsigned long long)v->pwi;
+    for (k = 0; k < 3; k++) {
+      out[9 + k] = ge.dry_grid[k];
+      out[12 + k] = ge.dry_block[k];
+    }
+  }
+done:
+  if (ge.strides != NULL)
+    for (k = 0; k < ge.narray; k++) free(ge.strides[k]);
+  free(ge.strides);
+  free(ge.dims);
+  free(ge.params);
+  free(ge.blob);
   return err;
 }
 

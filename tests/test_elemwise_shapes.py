@@ -153,3 +153,136 @@ def test_random_broadcasts_match_numpy_and_the_oracle_collapse(api, oracle, rng)
         assert r["n"] == int(np.prod(shape))
         done += 1
     assert done > 300
+
+
+# ---------------------------------------------------------------- call plans
+
+def plan(api, specs, obj_flags=0, call_flags=0, sms=148, bases=None):
+    """specs as for shapes(); returns the decisions GpuElemwise_call would take."""
+    L = api.lib()
+    fn = L.gpuarray_b200_elemwise_plan
+    fn.restype = ctypes.c_int
+    n = len(specs)
+    args = (Arg * n)()
+    nds = (ctypes.c_uint * n)()
+    dimp = (ctypes.POINTER(ctypes.c_size_t) * n)()
+    strp = (ctypes.POINTER(ctypes.c_ssize_t) * n)()
+    addr = (ctypes.c_ulonglong * n)()
+    keep = []
+    for i, (dt, fl, shape, strides) in enumerate(specs):
+        args[i].name = b"a%d" % i
+        args[i].typecode = api.typecode(np.dtype(dt))
+        args[i].flags = fl
+        addr[i] = (bases[i] if bases else 0x7f0000000000 + (i << 32))
+        if shape is not None:
+            nds[i] = len(shape)
+            d = (ctypes.c_size_t * max(len(shape), 1))(*shape)
+            s = (ctypes.c_ssize_t * max(len(shape), 1))(*strides)
+            keep += [d, s]
+            dimp[i] = ctypes.cast(d, ctypes.POINTER(ctypes.c_size_t))
+            strp[i] = ctypes.cast(s, ctypes.POINTER(ctypes.c_ssize_t))
+    out = (ctypes.c_ulonglong * 16)()
+    err = fn(n, args, nds, dimp, strp, addr, obj_flags, call_flags, sms, out)
+    keys = ["kind", "ept", "unroll", "nd", "idx", "modes", "tp", "tq", "pwi", "gx", "gy", "gz",
+            "bx", "by", "bz", "n"]
+    return err, dict(zip(keys, [int(v) for v in out]))
+
+
+def modes(p, narr):
+    return [(p["modes"] >> (2 * k)) & 3 for k in range(narr)]
+
+
+def test_plans_of_the_named_elementwise_configurations(api):
+    R, W = api.GE_READ, api.GE_WRITE
+    n = 1 << 24
+    # config 1: contiguous fp32, 4 elements per chunk, 4 chunks in flight, 4096 CTAs of 256
+    err, p = plan(api, [(np.float32, R, (n,), [4]), (np.float32, R, (n,), [4]), (np.float32, W, (n,), [4])])
+    assert err == 0 and (p["kind"], p["ept"], p["unroll"], p["idx"] & 1) == (0, 4, 4, 1)
+    assert p["gx"] == n // (4 * 4 * 256) and p["bx"] == 256
+    # an unaligned base: one element at a time
+    err, p = plan(api, [(np.float32, R, (n,), [4]), (np.float32, W, (n,), [4])],
+                  bases=[0x7f0000000004, 0x7f1000000000])
+    assert err == 0 and p["kind"] == 0 and p["ept"] == 1
+    # narrow types: 16 / 8 elements per chunk, 2 chunks in flight
+    err, p = plan(api, [(np.uint8, R, (n,), [1]), (np.uint8, W, (n,), [1])])
+    assert err == 0 and (p["ept"], p["unroll"]) == (16, 2)
+    err, p = plan(api, [(np.float16, R, (n,), [2]), (np.float16, W, (n,), [2])], obj_flags=api.GE_CONVERT_F16)
+    assert err == 0 and (p["ept"], p["unroll"]) == (8, 2)
+    # more than 2^31 elements: 64-bit indices
+    big = (1 << 31) + 64
+    err, p = plan(api, [(np.uint8, R, (big,), [1]), (np.uint8, W, (big,), [1])])
+    assert err == 0 and p["idx"] & 1 == 0
+    # config 4: fp16 NHWC view -> NCHW: tiled transpose, 256 x 64 tile, 2 P positions per thread
+    x = (np.float16, R, (64, 256, 56, 56), [1605632, 2, 28672, 512])
+    bias = (np.float16, R, (1, 256, 1, 1), [512, 2, 2, 2])
+    y = (np.float16, W, (64, 256, 56, 56), cs((64, 256, 56, 56), 2))
+    err, p = plan(api, [x, bias, y], obj_flags=api.GE_CONVERT_F16, call_flags=api.GE_BROADCAST)
+    assert err == 0 and p["kind"] == 2 and (p["tp"], p["tq"], p["pwi"], p["nd"]) == (256, 64, 2, 3)
+    assert modes(p, 3)[0] == 3 and p["gx"] == 64 * 1 * 49                  # 64 images x (256/256) x (3136/64)
+    # an fp32 transposed view: 128 x 32 tiles
+    M, N = 8192, 4096
+    a_t = (np.float32, R, (N, M), [4, 4 * N])
+    o = (np.float32, W, (N, M), cs((N, M), 4))
+    err, p = plan(api, [a_t, o])
+    assert err == 0 and p["kind"] == 2 and (p["tp"], p["tq"], p["pwi"]) == (128, 32, 1)
+    # row / column broadcasts: strided kernel, vector + broadcast modes, 32-bit offsets, capped grid
+    a = (np.float32, R, (M, N), cs((M, N), 4))
+    row = (np.float32, R, (1, N), cs((1, N), 4))
+    col = (np.float32, R, (M, 1), cs((M, 1), 4))
+    out = (np.float32, W, (M, N), cs((M, N), 4))
+    err, p = plan(api, [a, row, out], call_flags=api.GE_BROADCAST)
+    assert err == 0 and p["kind"] == 1 and modes(p, 3) == [1, 1, 1] and p["idx"] == 3
+    assert p["gx"] == 148 * 32
+    err, p = plan(api, [a, col, out], call_flags=api.GE_BROADCAST)
+    assert err == 0 and p["kind"] == 1 and modes(p, 3) == [1, 2, 1]
+    # a step-2 slice is gathered element by element
+    half = (np.float32, R, (M, N // 2), [4 * N, 8])
+    oh = (np.float32, W, (M, N // 2), cs((M, N // 2), 4))
+    err, p = plan(api, [half, oh])
+    assert err == 0 and p["kind"] == 1 and modes(p, 2) == [0, 1]
+    # arrays spanning more than 2 GiB keep 64-bit row offsets
+    wide = (np.float32, R, (1 << 15, 1 << 13), [1 << 17, 8])                # 4 GiB span, step 2
+    ow = (np.float32, W, (1 << 15, 1 << 13), cs((1 << 15, 1 << 13), 4))
+    err, p = plan(api, [wide, ow])
+    assert err == 0 and p["kind"] == 1 and p["idx"] == 1
+
+
+def test_plan_invariants_over_random_layouts(api, rng):
+    R, W, B = api.GE_READ, api.GE_WRITE, api.GE_BROADCAST
+    done = 0
+    for _ in range(1500):
+        nd = int(rng.integers(1, 5))
+        shape = tuple(int(d) for d in rng.choice([1, 2, 3, 8, 17, 64, 300, 4096], size=nd))
+        dt = [np.float32, np.float16, np.float64, np.uint8][int(rng.integers(0, 4))]
+        isz = np.dtype(dt).itemsize
+        specs = []
+        for k in range(int(rng.integers(1, 4))):
+            ish = tuple(1 if rng.random() < 0.25 else d for d in shape)
+            st = cs(ish, isz)
+            r = rng.random()
+            if r < 0.3 and nd > 1:
+                perm = [int(q) for q in rng.permutation(nd)]
+                st2 = cs(tuple(ish[i] for i in perm), isz)
+                st = [st2[perm.index(j)] for j in range(nd)]
+            elif r < 0.45:
+                st = [2 * v for v in st]
+            elif r < 0.55:
+                st[-1] = -st[-1]
+            specs.append((dt, R, ish, st))
+        specs.append((dt, W, shape, cs(shape, isz)))
+        sms = int(rng.choice([1, 16, 148]))
+        err, p = plan(api, specs, obj_flags=api.GE_CONVERT_F16 if dt == np.float16 else 0, call_flags=B,
+                      sms=sms)
+        assert err == 0
+        total = int(np.prod(shape))
+        assert p["n"] == total
+        assert p["kind"] in (0, 1, 2) and p["bx"] * p["by"] * p["bz"] == 256
+        assert 1 <= p["gx"] <= 0x7fffffff and p["gy"] == 1 and p["gz"] == 1
+        assert p["ept"] in (1, 2, 4, 8, 16) and p["ept"] * isz <= 16
+        if p["kind"] == 1:
+            assert p["gx"] <= sms * 32 and p["unroll"] == 1 and 1 <= p["nd"] <= nd
+        if p["kind"] == 2:
+            assert p["tp"] in (32, 64, 128, 256) and p["tq"] in (32, 64) and p["tq"] % p["ept"] == 0
+            assert 3 in modes(p, len(specs))
+        done += 1
+    assert done == 1500
