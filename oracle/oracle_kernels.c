@@ -18,7 +18,9 @@
  *                      the reference passes no -fmad option,
  *                      src/gpuarray_buffer_cuda.c:1113-1121).
  * Pinned by tests/test_oracle.py against the known answers of the reference's
- * tests/check_util.c:41-148 and tests/check_reduction.c.
+ * tests/check_util.c:41-148 and tests/check_reduction.c, and by
+ * tests/test_golden.py against outputs of the reference's own compiled util
+ * code (tests/golden/).
  */
 #include <math.h>
 #include <stddef.h>
