@@ -94,6 +94,17 @@ GPUARRAY_PUBLIC int gpuarray_b200_reduction_plan(int op, int src_tc, int dst_tc,
                                                  unsigned long long base, unsigned int num_sms,
                                                  unsigned long long *out);
 
+/* gpuarray_b200_reduction_plan plus the parameter block the kernel would
+ * receive (struct ga__rd_layout of the reduction template), copied into
+ * `layout` (cap bytes available, *used = its size): for tools that run the
+ * kernel templates outside the library. */
+GPUARRAY_PUBLIC int gpuarray_b200_reduction_layout(int op, int src_tc, int dst_tc, unsigned int nd,
+                                                   const size_t *dims, const ssize_t *strides,
+                                                   unsigned int reduxLen, const int *reduxList,
+                                                   unsigned long long base, unsigned int num_sms,
+                                                   unsigned long long *out, void *layout,
+                                                   size_t cap, size_t *used);
+
 /* Sum of n contiguous float32 values on the current device WITHOUT allocating
  * anything: no cudaMalloc / cudaFree, no library workspace. (No counterpart in
  * the reference, whose reductions allocate per call.) It is for callers that

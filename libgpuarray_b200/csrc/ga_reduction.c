@@ -666,14 +666,13 @@ static int rd_plan(const rd_plan_in *in, rd_layout *L, rd_variant *want, unsigne
  * once, one-run mode, lazy index, byte folding, threads per output (general),
  * 64-bit index, splits, seg, nseg, units, grid x, grid y, block x, block y,
  * outputs, reduced elements per output. Returns a GA_* code. */
-GPUARRAY_PUBLIC int gpuarray_b200_reduction_plan(int op, int src_tc, int dst_tc, unsigned int nd,
-                                                 const size_t *dims, const ssize_t *strides,
-                                                 unsigned int reduxLen, const int *reduxList,
-                                                 unsigned long long base, unsigned int num_sms,
-                                                 unsigned long long *out) {
-  GpuArray s, d;
+static int plan_worker(int op, int src_tc, int dst_tc, unsigned int nd, const size_t *dims,
+                       const ssize_t *strides, unsigned int reduxLen, const int *reduxList,
+                       unsigned long long base, unsigned int num_sms, unsigned long long *out,
+                       rd_layout *layout_out) {
+  GpuArray s, d, di;
   size_t ddims[64];
-  ssize_t dstr[64];
+  ssize_t dstr[64], distr[64];
   unsigned char red[64];
   rd_layout L;
   rd_variant want;
@@ -705,6 +704,15 @@ GPUARRAY_PUBLIC int gpuarray_b200_reduction_plan(int op, int src_tc, int dst_tc,
   d.nd = k;
   d.dimensions = ddims;
   d.strides = dstr;
+  step = 8; /* the index destination holds 8-byte integers */
+  for (i = k; i > 0; i--) {
+    distr[i - 1] = (ssize_t)step;
+    step *= ddims[i - 1];
+  }
+  memset(&di, 0, sizeof(di));
+  di.nd = k;
+  di.dimensions = ddims;
+  di.strides = distr;
   memset(&in, 0, sizeof(in));
   in.e = ga_global_err;
   in.op = (ga_reduce_op)op;
@@ -715,7 +723,7 @@ GPUARRAY_PUBLIC int gpuarray_b200_reduction_plan(int op, int src_tc, int dst_tc,
   in.need_idx = op_writes_idx(in.op);
   in.num_sms = num_sms;
   in.p_src = base;
-  err = normalise(in.kind, in.e, &L, in.need_val ? &d : NULL, in.need_idx ? &d : NULL, &s, red,
+  err = normalise(in.kind, in.e, &L, in.need_val ? &d : NULL, in.need_idx ? &di : NULL, &s, red,
                   reduxLen, reduxList);
   if (err != GA_NO_ERROR) return err;
   memset(out, 0, 20 * sizeof(*out));
@@ -742,6 +750,38 @@ GPUARRAY_PUBLIC int gpuarray_b200_reduction_plan(int op, int src_tc, int dst_tc,
   out[15] = grid[1];
   out[16] = block[0];
   out[17] = block[1];
+  if (layout_out != NULL) *layout_out = L;
+  return GA_NO_ERROR;
+}
+
+GPUARRAY_PUBLIC int gpuarray_b200_reduction_plan(int op, int src_tc, int dst_tc, unsigned int nd,
+                                                 const size_t *dims, const ssize_t *strides,
+                                                 unsigned int reduxLen, const int *reduxList,
+                                                 unsigned long long base, unsigned int num_sms,
+                                                 unsigned long long *out) {
+  return plan_worker(op, src_tc, dst_tc, nd, dims, strides, reduxLen, reduxList, base, num_sms, out,
+                     NULL);
+}
+
+/* As gpuarray_b200_reduction_plan, and also copies the parameter block the
+ * kernel would receive (struct ga__rd_layout of ga_reduce.cuh) into `layout`
+ * (`cap` bytes available); *used receives its size. For tools that run the
+ * kernel templates outside the library. */
+GPUARRAY_PUBLIC int gpuarray_b200_reduction_layout(int op, int src_tc, int dst_tc, unsigned int nd,
+                                                   const size_t *dims, const ssize_t *strides,
+                                                   unsigned int reduxLen, const int *reduxList,
+                                                   unsigned long long base, unsigned int num_sms,
+                                                   unsigned long long *out, void *layout,
+                                                   size_t cap, size_t *used) {
+  rd_layout L;
+  int err;
+  memset(&L, 0, sizeof(L));
+  if (cap < sizeof(L)) return ga_err_set(ga_global_err, GA_VALUE_ERROR, "Layout buffer too small");
+  err = plan_worker(op, src_tc, dst_tc, nd, dims, strides, reduxLen, reduxList, base, num_sms, out,
+                    &L);
+  if (err != GA_NO_ERROR) return err;
+  memcpy(layout, &L, sizeof(L));
+  if (used != NULL) *used = sizeof(L);
   return GA_NO_ERROR;
 }
 

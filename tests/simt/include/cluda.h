@@ -1,0 +1,41 @@
+/* Host stand-in for the kernel-side header, used only by the SIMT emulator in
+ * tests/simt: the kernel templates are compiled for the CPU and their threads
+ * run as cooperative fibers (simt_emul.h). Provides the element types, the
+ * half conversions (IEEE round-to-nearest-even, like the device instructions)
+ * and the few intrinsics the templates use. */
+#ifndef CLUDA_H
+#define CLUDA_H
+#include "simt_emul.h"
+
+typedef unsigned char ga_bool;
+typedef signed char ga_byte;
+typedef unsigned char ga_ubyte;
+typedef short ga_short;
+typedef unsigned short ga_ushort;
+typedef int ga_int;
+typedef unsigned int ga_uint;
+typedef long long ga_long;
+typedef unsigned long long ga_ulong;
+typedef float ga_float;
+typedef double ga_double;
+typedef size_t ga_size;
+typedef ptrdiff_t ga_ssize;
+
+struct ga_half {
+  ga_ushort data;
+};
+
+static inline float ga_half2float(ga_half h) {
+  _Float16 v;
+  memcpy(&v, &h.data, 2);
+  return (float)v;
+}
+static inline ga_half ga_float2half(float f) {
+  const _Float16 v = (_Float16)f; /* round to nearest even */
+  ga_half h;
+  memcpy(&h.data, &v, 2);
+  return h;
+}
+
+static inline void ga__grid_dependency_sync() {}
+#endif
