@@ -68,7 +68,9 @@ GPUARRAY_PUBLIC int gpuarray_b200_elemwise_shapes(unsigned int n, const gpuelemw
  * thread chunk, chunks in flight, rank after collapsing, index width bits, access
  * modes (2 bits per array argument: 0 gather, 1 vector, 2 broadcast, 3 staged
  * through shared memory), tile P, tile Q, P positions per thread, grid x/y/z,
- * block x/y/z, element count. Reference counterpart of the decisions:
+ * block x/y/z, element count. blob_out (may be NULL) receives the layout
+ * parameter block of the strided / transposing kernels (blob_cap words
+ * available, *blob_words its length). Reference counterpart of the decisions:
  * src/gpuarray_elemwise.c:385-442,578-602 and src/gpuarray_kernel.c:38-89. */
 GPUARRAY_PUBLIC int gpuarray_b200_elemwise_plan(unsigned int n, const gpuelemwise_arg *args,
                                                 const unsigned int *nds,
@@ -76,7 +78,9 @@ GPUARRAY_PUBLIC int gpuarray_b200_elemwise_plan(unsigned int n, const gpuelemwis
                                                 const ssize_t *const *strides,
                                                 const unsigned long long *bases, int obj_flags,
                                                 int call_flags, unsigned int num_sms,
-                                                unsigned long long *out);
+                                                unsigned long long *out,
+                                                unsigned long long *blob_out, size_t blob_cap,
+                                                size_t *blob_words);
 
 /* The plan GpuReduction_call would make (kernel variant, split of the reduced
  * extent, launch geometry) for a source of the given shape and byte strides on a

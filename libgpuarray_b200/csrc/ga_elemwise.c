@@ -878,14 +878,18 @@ done:
  * collapsing, index width bits (1: 32-bit indices, 2: 32-bit row offsets),
  * access modes (2 bits per array: 0 gather, 1 vector, 2 broadcast, 3 staged
  * through shared memory), tile P, tile Q, P positions per thread, grid x/y/z,
- * block x/y/z, element count. */
+ * block x/y/z, element count. blob_out (may be NULL) receives the layout
+ * parameter block of the strided / transposing kernels, *blob_words its length
+ * in 8-byte words. */
 GPUARRAY_PUBLIC int gpuarray_b200_elemwise_plan(unsigned int n, const gpuelemwise_arg *args,
                                                 const unsigned int *nds,
                                                 const size_t *const *dims,
                                                 const ssize_t *const *strides,
                                                 const unsigned long long *bases, int obj_flags,
                                                 int call_flags, unsigned int num_sms,
-                                                unsigned long long *out) {
+                                                unsigned long long *out,
+                                                unsigned long long *blob_out, size_t blob_cap,
+                                                size_t *blob_words) {
   struct _gpucontext fake;
   struct _gpudata bufs[32];
   GpuElemwise ge;
@@ -959,6 +963,15 @@ GPUARRAY_PUBLIC int gpuarray_b200_elemwise_plan(unsigned int n, const gpuelemwis
     for (k = 0; k < 3; k++) {
       out[9 + k] = ge.dry_grid[k];
       out[12 + k] = ge.dry_block[k];
+    }
+    /* the layout parameter block of the strided / transposing kernels */
+    if (blob_words != NULL) *blob_words = v->kind == 0 ? 0 : ge.blob_words;
+    if (blob_out != NULL && v->kind != 0) {
+      if (ge.blob_words > blob_cap) {
+        err = ga_err_set(ga_global_err, GA_VALUE_ERROR, "Layout buffer too small");
+        goto done;
+      }
+      memcpy(blob_out, ge.blob, ge.blob_words * sizeof(*blob_out));
     }
   }
 done:

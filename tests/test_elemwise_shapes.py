@@ -182,7 +182,7 @@ def plan(api, specs, obj_flags=0, call_flags=0, sms=148, bases=None):
             dimp[i] = ctypes.cast(d, ctypes.POINTER(ctypes.c_size_t))
             strp[i] = ctypes.cast(s, ctypes.POINTER(ctypes.c_ssize_t))
     out = (ctypes.c_ulonglong * 16)()
-    err = fn(n, args, nds, dimp, strp, addr, obj_flags, call_flags, sms, out)
+    err = fn(n, args, nds, dimp, strp, addr, obj_flags, call_flags, sms, out, None, ctypes.c_size_t(0), None)
     keys = ["kind", "ept", "unroll", "nd", "idx", "modes", "tp", "tq", "pwi", "gx", "gy", "gz",
             "bx", "by", "bz", "n"]
     return err, dict(zip(keys, [int(v) for v in out]))

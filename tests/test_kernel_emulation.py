@@ -209,3 +209,175 @@ def test_column_and_general_kernels_on_the_emulator(api, oracle, rng):
     g = ties(rng, (10, 11, 12))[:, :, ::2]                   # nothing contiguous: general kernel
     check(api, oracle, "MAXANDARGMAX", g, [1], expect={"shape": 2})
     check(api, oracle, "SUM", g, [0, 2], expect={"shape": 2})
+
+
+# ------------------------------------------------------------- elementwise
+
+class _Arg(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char_p), ("typecode", ctypes.c_int), ("flags", ctypes.c_int)]
+
+
+CTYPE = {np.dtype(np.float32): "float", np.dtype(np.float64): "double", np.dtype(np.float16): "ga_half",
+         np.dtype(np.int32): "int", np.dtype(np.uint8): "unsigned char", np.dtype(np.int64): "long long"}
+EW_KEYS = ["kind", "ept", "unroll", "nd", "idx", "modes", "tp", "tq", "pwi", "gx", "gy", "gz",
+           "bx", "by", "bz", "n"]
+EW_ENTRY = ["ga_ew_contig", "ga_ew_strided", "ga_ew_transpose"]
+
+
+def emulate_elemwise(api, expr, spec, arrays, obj_flags=0, call_flags=0, sms=2, preamble=""):
+    """spec: list of (name, dtype, GE flags); arrays: NumPy arrays (views allowed) or Python
+    scalars, in the same order. Runs the call on the emulator, writing into the output arrays."""
+    L = api.lib()
+    n = len(spec)
+    args = (_Arg * n)()
+    nds = (ctypes.c_uint * n)()
+    dimp = (ctypes.POINTER(ctypes.c_size_t) * n)()
+    strp = (ctypes.POINTER(ctypes.c_ssize_t) * n)()
+    addr = (ctypes.c_ulonglong * n)()
+    keep = []
+    for i, ((name, dt, fl), a) in enumerate(zip(spec, arrays)):
+        args[i].name = name.encode()
+        args[i].typecode = api.typecode(np.dtype(dt))
+        args[i].flags = fl
+        if not (fl & api.GE_SCALAR):
+            nds[i] = a.ndim
+            d = (ctypes.c_size_t * max(a.ndim, 1))(*a.shape)
+            s = (ctypes.c_ssize_t * max(a.ndim, 1))(*a.strides)
+            keep += [d, s]
+            dimp[i] = ctypes.cast(d, ctypes.POINTER(ctypes.c_size_t))
+            strp[i] = ctypes.cast(s, ctypes.POINTER(ctypes.c_ssize_t))
+            addr[i] = a.ctypes.data
+    out = (ctypes.c_ulonglong * 16)()
+    blob = (ctypes.c_ulonglong * 1024)()
+    words = ctypes.c_size_t()
+    fn = L.gpuarray_b200_elemwise_plan
+    fn.restype = ctypes.c_int
+    err = fn(n, args, nds, dimp, strp, addr, obj_flags, call_flags, sms, out, blob, ctypes.c_size_t(1024),
+             ctypes.byref(words))
+    assert err == 0, err
+    p = dict(zip(EW_KEYS, [int(v) for v in out]))
+    if p["n"] == 0:
+        return p
+    src_fn = L.gpuarray_b200_elemwise_source
+    src_fn.restype = ctypes.c_void_p
+    src_fn.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_uint, ctypes.POINTER(_Arg), ctypes.c_int,
+                       ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_uint, ctypes.c_int,
+                       ctypes.c_ulonglong, ctypes.c_int, ctypes.c_int]
+    ptr = src_fn(preamble.encode(), expr.encode(), n, args, obj_flags, p["kind"], p["ept"], p["unroll"],
+                 p["nd"], p["idx"], p["modes"], p["tp"], p["tq"])
+    text = ctypes.string_at(ptr).decode()
+    if p["kind"] == 2:
+        import re
+        text = re.sub(r"#define GA_EW_PWI \d+", "#define GA_EW_PWI %d" % p["pwi"], text)
+    # the launcher: layout block (strided / transposing kernels) or n, then pointers, then scalars
+    arr_idx = [i for i, (nm, dt, fl) in enumerate(spec) if not (fl & api.GE_SCALAR)]
+    sc_idx = [i for i, (nm, dt, fl) in enumerate(spec) if fl & api.GE_SCALAR]
+    call = []
+    for k, i in enumerate(arr_idx):
+        ct = CTYPE[np.dtype(spec[i][1])]
+        call.append("(%s *)a->ptr[%d]" % (ct if p["kind"] == 0 else "char", k))
+    for k, i in enumerate(sc_idx):
+        call.append("*(%s *)a->sc[%d]" % (CTYPE[np.dtype(spec[i][1])], k))
+    first = "a->n" if p["kind"] == 0 else "*(const %s *)a->blob" % ("ga__ew_layout" if p["kind"] == 1
+                                                                     else "ga__ewt_layout")
+    text += '''
+struct simt_ew_args { size_t n; const void *blob; void *ptr[32]; void *sc[32]; };
+static void simt_body(void *q) {
+  simt_ew_args *a = (simt_ew_args *)q;
+  %s(%s);
+}
+extern "C" void simt_launch(size_t n, const void *blob, void **ptrs, void **scalars, unsigned np_,
+                            unsigned ns_, unsigned gx, unsigned bx) {
+  simt_ew_args a;
+  a.n = n;
+  a.blob = blob;
+  for (unsigned i = 0; i < np_; i++) a.ptr[i] = ptrs[i];
+  for (unsigned i = 0; i < ns_; i++) a.sc[i] = scalars[i];
+  simt::run_grid(simt_body, &a, simt_dim3{gx, 1, 1}, simt_dim3{bx, 1, 1});
+}
+''' % (EW_ENTRY[p["kind"]], ", ".join([first] + call))
+    tdeps = "".join(open(os.path.join(TEMPLATES, t)).read()
+                    for t in ("ga_ew_common.cuh", "ga_ew_contig.cuh", "ga_ew_strided.cuh", "ga_ew_transpose.cuh"))
+    key = hashlib.sha1((text + tdeps + open(os.path.join(SIMT, "include", "simt_emul.h")).read()).encode()
+                       ).hexdigest()[:16]
+    os.makedirs(BUILD, exist_ok=True)
+    so = os.path.join(BUILD, "e_%s.so" % key)
+    if not os.path.exists(so):
+        src = os.path.join(BUILD, "e_%s.cpp" % key)
+        with open(src, "w") as f:
+            f.write(text)
+        r = subprocess.run(["g++", "-std=c++17", "-O1", "-shared", "-fPIC", "-w", "-I",
+                            os.path.join(SIMT, "include"), "-I", TEMPLATES, src,
+                            os.path.join(SIMT, "simt_runtime.cpp"), "-o", so], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr[-3000:]
+    lib = ctypes.CDLL(so)
+    ptrs = (ctypes.c_void_p * 32)()
+    scs = (ctypes.c_void_p * 32)()
+    for k, i in enumerate(arr_idx):
+        ptrs[k] = arrays[i].ctypes.data
+    hold = []
+    for k, i in enumerate(sc_idx):
+        v = np.array(arrays[i], dtype=spec[i][1])
+        hold.append(v)
+        scs[k] = v.ctypes.data
+    lib.simt_launch(ctypes.c_size_t(p["n"]), blob, ptrs, scs, len(arr_idx), len(sc_idx), p["gx"], p["bx"])
+    return p
+
+
+def test_elementwise_kernels_on_the_emulator(api, rng):
+    R, W, S = api.GE_READ, api.GE_WRITE, api.GE_SCALAR
+    # contiguous, ragged tail (4099 = 1024 vectors + 3), a scalar argument
+    a = rng.standard_normal(4099).astype(np.float32)
+    b = rng.standard_normal(4099).astype(np.float32)
+    o = np.zeros(4099, np.float32)
+    p = emulate_elemwise(api, "o = a * k + b", [("a", np.float32, R), ("k", np.float32, S), ("b", np.float32, R),
+                                                ("o", np.float32, W)], [a, np.float32(3), b, o])
+    assert p["kind"] == 0 and p["ept"] == 4
+    assert np.allclose(o, a * np.float32(3) + b, rtol=1e-6, atol=1e-6)
+    # uint8: 16 elements per chunk, wrap-around arithmetic
+    u = rng.integers(0, 256, 5000).astype(np.uint8)
+    uo = np.zeros(5000, np.uint8)
+    p = emulate_elemwise(api, "o = a + 1", [("a", np.uint8, R), ("o", np.uint8, W)], [u, uo])
+    assert p["ept"] == 16 and (uo == u + np.uint8(1)).all()
+    # float16 storage, float32 arithmetic
+    h = rng.standard_normal(3000).astype(np.float16)
+    ho = np.zeros(3000, np.float16)
+    p = emulate_elemwise(api, "o = a * 2.0f", [("a", np.float16, R), ("o", np.float16, W)], [h, ho],
+                         obj_flags=api.GE_CONVERT_F16)
+    assert p["ept"] == 8 and (ho == (h.astype(np.float32) * 2).astype(np.float16)).all()
+    # strided kernel: row and column broadcasts, a reversed axis, a step-2 gather
+    M, N = 37, 520
+    A = rng.standard_normal((M, N)).astype(np.float32)
+    row = rng.standard_normal((1, N)).astype(np.float32)
+    col = rng.standard_normal((M, 1)).astype(np.float32)
+    O = np.zeros((M, N), np.float32)
+    spec3 = [("a", np.float32, R), ("b", np.float32, R), ("o", np.float32, W)]
+    p = emulate_elemwise(api, "o = a + b", spec3, [A, row, O], call_flags=api.GE_BROADCAST)
+    assert p["kind"] == 1 and (O == A + row).all()
+    p = emulate_elemwise(api, "o = a + b", spec3, [A, col, O], call_flags=api.GE_BROADCAST)
+    assert p["kind"] == 1 and (O == A + col).all()
+    p = emulate_elemwise(api, "o = a + b", spec3, [A[::-1, ::-1], col, O], call_flags=api.GE_BROADCAST)
+    assert (O == A[::-1, ::-1] + col).all()
+    wide = rng.standard_normal((M, 2 * N)).astype(np.float32)
+    p = emulate_elemwise(api, "o = a - b", spec3, [wide[:, ::2], A, O])
+    assert p["kind"] == 1 and (O == wide[:, ::2] - A).all()
+    # three dimensions that do not collapse, ragged innermost extent
+    T = rng.standard_normal((5, 13, 2 * 31)).astype(np.float32)[:, ::2, ::2]
+    TO = np.zeros((5, 7, 31), np.float32)
+    p = emulate_elemwise(api, "o = a * a", [("a", np.float32, R), ("o", np.float32, W)], [T, TO])
+    assert p["kind"] == 1 and p["nd"] == 3 and (TO == T * T).all()
+    # tiled transpose: an fp32 transposed view, and the fp16 NHWC -> NCHW bias + ReLU of config 4 in small
+    B = rng.standard_normal((100, 70)).astype(np.float32)
+    BO = np.zeros((70, 100), np.float32)
+    p = emulate_elemwise(api, "o = a * 2.0f", [("a", np.float32, R), ("o", np.float32, W)], [B.T, BO])
+    assert p["kind"] == 2 and (BO == B.T * 2).all()
+    nhwc = rng.standard_normal((2, 9, 7, 40)).astype(np.float16)
+    x = nhwc.transpose(0, 3, 1, 2)
+    bias = (0.2 * rng.random((1, 40, 1, 1)) - 0.1).astype(np.float16)
+    y = np.zeros((2, 40, 9, 7), np.float16)
+    p = emulate_elemwise(api, "y = fmaxf(x + bias, 0.0f)", [("x", np.float16, R), ("bias", np.float16, R),
+                                                           ("y", np.float16, W)], [x, bias, y],
+                         obj_flags=api.GE_CONVERT_F16, call_flags=api.GE_BROADCAST)
+    assert p["kind"] == 2 and p["pwi"] == 2
+    want = np.maximum(x.astype(np.float32) + bias.astype(np.float32), 0).astype(np.float16)
+    assert (y == want).all()
