@@ -83,10 +83,12 @@ def build_variant(api, op, x, dst_dtype, p):
     return ctypes.CDLL(so)
 
 
-def emulate(api, op, x, axes, dst_dtype=None, sms=2):
-    """Runs the reduction on the emulator; returns (value array or None, index array or None, plan)."""
+def emulate(api, op, x, axes, dst_dtype=None, sms=2, force=None):
+    """Runs the reduction on the emulator; returns (value array or None, index array or None, plan).
+    `force` overrides fields of the plan that only select a build of the kernel (idx64)."""
     dst_dtype = np.dtype(dst_dtype or x.dtype)
     p, layout = plan_and_layout(api, op, x, axes, dst_dtype, sms)
+    p.update(force or {})
     lib = build_variant(api, op, x, dst_dtype, p)
     kept = tuple(d for i, d in enumerate(x.shape) if i not in axes)
     want_val = op not in ("ARGMAX", "ARGMIN")
@@ -109,8 +111,8 @@ def emulate(api, op, x, axes, dst_dtype=None, sms=2):
     return d0, d1, p
 
 
-def check(api, oracle, op, x, axes, dst_dtype=None, expect=None, sms=2):
-    d0, d1, p = emulate(api, op, x, axes, dst_dtype, sms)
+def check(api, oracle, op, x, axes, dst_dtype=None, expect=None, sms=2, force=None):
+    d0, d1, p = emulate(api, op, x, axes, dst_dtype, sms, force)
     if expect:
         for k, v in expect.items():
             assert p[k] == v, (k, p)
@@ -172,6 +174,18 @@ def test_rows_kernel_variants_on_the_emulator(api, oracle, rng):
     big = ties(rng, (3, 4100))
     u = big[:, 1:]
     check(api, oracle, "MAXANDARGMAX", u, [1], expect={"vec": 1})
+
+
+def test_64_bit_index_builds_on_the_emulator(api, oracle, rng):
+    """The builds with 64-bit flat indices (chosen by the planner beyond 2^32
+    reduced elements) run here on small data; the GPU suite runs them at size."""
+    f = {"idx64": 1}
+    check(api, oracle, "MAXANDARGMAX", ties(rng, (40, 6000)), [1], force=f, expect={"lazy": 1})
+    check(api, oracle, "MINANDARGMIN", ties(rng, (2, 40000)), [1], force=f, sms=1)
+    check(api, oracle, "ARGMAX", ties(rng, (300, 24)), [1], force=f, expect={"onerun": 1})
+    check(api, oracle, "MAXANDARGMAX", ties(rng, (23, 4, 64)), [2, 0], force=f)
+    check(api, oracle, "MAXANDARGMAX", ties(rng, (700, 130)), [0], force=f, sms=4, expect={"shape": 1})
+    check(api, oracle, "ARGMIN", ties(rng, (10, 11, 12))[:, :, ::2], [1], force=f, expect={"shape": 2})
 
 
 def test_short_run_variants_on_the_emulator(api, oracle, rng):
