@@ -395,3 +395,47 @@ def test_elementwise_kernels_on_the_emulator(api, rng):
     assert p["kind"] == 2 and p["pwi"] == 2
     want = np.maximum(x.astype(np.float32) + bias.astype(np.float32), 0).astype(np.float16)
     assert (y == want).all()
+
+
+def test_random_reductions_on_the_emulator(api, oracle):
+    """A seeded sweep of shapes, axis lists, layouts, operators and element types
+    through planner + generator + emulator against the oracle."""
+    rng = np.random.default_rng(2024)
+    ops = ["SUM", "MAXANDARGMAX", "MINANDARGMIN", "ARGMAX", "MAX", "PROD", "ANY"]
+    dts = [np.float32, np.float64, np.float16, np.int32, np.int8, np.uint8]
+    seen = set()
+    for _ in range(90):
+        nd = int(rng.integers(1, 5))
+        shape = tuple(int(d) for d in rng.choice([1, 2, 3, 5, 8, 17, 40, 130, 600], size=nd))
+        if np.prod(shape) > 400000 or np.prod(shape) == 0:
+            shape = shape[:1] + (3,) * (nd - 1)
+        dt = dts[int(rng.integers(0, len(dts)))]
+        op = ops[int(rng.integers(0, len(ops)))]
+        if np.dtype(dt).kind == "f":
+            x = (np.round(rng.standard_normal(shape) * 2) / 2).astype(dt)
+        else:
+            lo = -4 if np.dtype(dt).kind == "i" else 0
+            x = rng.integers(lo, 5, shape).astype(dt)
+        r = rng.random()
+        if r < 0.25 and nd > 1:
+            x = np.asfortranarray(x)
+        elif r < 0.5:
+            big = np.zeros(tuple(2 * s + 1 for s in shape), dt)
+            sl = tuple(slice(1, 1 + 2 * s, 2) for s in shape)
+            big[sl] = x
+            x = big[sl]
+        k = int(rng.integers(1, nd + 1))
+        axes = [int(a) for a in rng.permutation(nd)[:k]]
+        dst = None
+        if op == "ANY":
+            dst = np.bool_
+        elif op in ("SUM", "PROD") and np.dtype(dt).kind in "iu":
+            dst = np.int64
+        elif op in ("SUM", "PROD") and dt == np.float16:
+            x = (x / 4).astype(dt) if op == "PROD" else x
+            dst = np.float32                       # keeps the tolerance of the check simple
+        if op == "PROD":
+            x = np.sign(x).astype(dt) if np.dtype(dt).kind != "u" else (x % 2 + 1).astype(dt)
+        p = check(api, oracle, op, x, axes, dst_dtype=dst, sms=int(rng.choice([1, 2, 4])))
+        seen.add((p["shape"], p["onerun"], p["flat"], p["mu"] > 1, p["splits"] > 1))
+    assert len(seen) >= 6                          # the sweep reached a spread of kernel variants
