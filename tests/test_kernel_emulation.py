@@ -108,6 +108,14 @@ def emulate(api, op, x, axes, dst_dtype=None, sms=2, force=None):
     lib.simt_launch(layout, ptr(x), ptr(d0), ptr(d1), ptr(pval), ptr(pidx), ptr(tickets),
                     p["gx"], p["gy"], p["bx"], p["by"])
     assert (tickets == 0).all()                      # arrival counters are handed back at zero
+    if p["splits"] > 1:
+        # a second launch on the same scratch and counters (what back-to-back calls do)
+        first = (None if d0 is None else d0.copy(), None if d1 is None else d1.copy())
+        lib.simt_launch(layout, ptr(x), ptr(d0), ptr(d1), ptr(pval), ptr(pidx), ptr(tickets),
+                        p["gx"], p["gy"], p["bx"], p["by"])
+        assert (tickets == 0).all()
+        assert d0 is None or d0.tobytes() == first[0].tobytes()
+        assert d1 is None or (d1 == first[1]).all()
     return d0, d1, p
 
 
