@@ -186,6 +186,33 @@ int ga_compile_cubin(ga_error_rec *e, const char *src, const char *const *define
   return err;
 }
 
+/* GPUARRAY_B200_SOURCE_LOG=<dir>: every kernel source this process builds or
+ * loads is also written to <dir>/<hash of the text>.src. The collected texts
+ * let `python -m libgpuarray_b200.warm_cache` rebuild the cubin cache on a
+ * machine without a GPU (NVRTC needs none), e.g. after the kernel templates
+ * changed or before a deployment that must not compile at start-up. */
+static void log_source(const char *src) {
+  const char *dir = getenv("GPUARRAY_B200_SOURCE_LOG");
+  char path[4096];
+  FILE *f;
+  size_t len;
+  if (dir == NULL || dir[0] == '\0') return;
+  len = strlen(src);
+  mkdir(dir, 0777);
+  snprintf(path, sizeof(path), "%s/%016llx%016llx.src", dir,
+           (unsigned long long)ga_hash64(src, len, 0),
+           (unsigned long long)ga_hash64(src, len, 0x9e3779b97f4a7c15ULL));
+  f = fopen(path, "rb");
+  if (f != NULL) { /* already there */
+    fclose(f);
+    return;
+  }
+  f = fopen(path, "wb");
+  if (f == NULL) return;
+  fwrite(src, 1, len, f);
+  fclose(f);
+}
+
 int ga_compile(gpucontext *ctx, const char *src, const char *fname, const char *const *defines,
                ga_function *out, char **err_str) {
   uint64_t key[2];
@@ -201,6 +228,7 @@ int ga_compile(gpucontext *ctx, const char *src, const char *fname, const char *
   if (m == NULL) {
     char *bin = NULL;
     size_t bin_sz = 0;
+    if (defines == NULL) log_source(src);
     if (disk_get(ctx->kernel_cache_path, key, &bin, &bin_sz) != 0) {
       err = nvrtc_build(ctx->err, src, defines, &bin, &bin_sz, err_str);
       if (err != GA_NO_ERROR) return err;
