@@ -592,6 +592,7 @@ def run_ours(args, rank, world, local_rank):
                      "frac": per_gpu / peak, "peak_kind": peak_kind, "kernel": "ga_rd_rows",
                      "traffic": TRAFFIC_BYTES_PER_LAUNCH if ROWS == 16384 else None},
         "clocks": clocks,
+        "nvrtc": api.lib().gpuarray_b200_nvrtc_version() / 1000.0,
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu

@@ -44,6 +44,11 @@ GPUARRAY_PUBLIC char *gpuarray_b200_elemwise_source(const char *preamble, const 
 GPUARRAY_PUBLIC char *gpuarray_b200_reduction_source(int op, int src_tc, int dst_tc, int shape,
                                                      int vec, int idx64, int tpo, int group);
 
+/* Version of the NVRTC the library bound, as major * 1000 + minor * 10 (12090 for
+ * 12.9); 0 when none could be loaded. The toolkit's copy under /usr/local/cuda
+ * is preferred over one the process may have loaded already. */
+GPUARRAY_PUBLIC int gpuarray_b200_nvrtc_version(void);
+
 /* The shape work of GpuElemwise_call on plain shape / byte-stride lists, with no
  * device: contiguous-fast-path test (reference check_contig,
  * src/gpuarray_elemwise.c:547-576), rank padding, broadcast, output-defines-

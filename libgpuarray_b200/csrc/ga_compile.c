@@ -330,6 +330,15 @@ int ga_launch(gpucontext *ctx, const ga_function *fn, const unsigned grid[3],
   return GA_NO_ERROR;
 }
 
+/* Version of the NVRTC the library bound (major * 1000 + minor * 10), 0 when it
+ * cannot be loaded. */
+GPUARRAY_PUBLIC int gpuarray_b200_nvrtc_version(void) {
+  int major = 0, minor = 0;
+  if (ga_load_nvrtc(ga_global_err) != GA_NO_ERROR) return 0;
+  if (ga_rtc.p_nvrtcVersion(&major, &minor) != NVRTC_SUCCESS) return 0;
+  return major * 1000 + minor * 10;
+}
+
 /* Test and tooling hook: compile a program for sm_100a without any device.
  * Returns GA_NO_ERROR and the cubin size, or an error with *log (malloc'ed,
  * may be NULL) holding the numbered source and compiler output. */

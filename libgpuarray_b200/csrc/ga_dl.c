@@ -60,9 +60,12 @@ int ga_load_cuda(ga_error_rec *e) {
 
 int ga_load_nvrtc(ga_error_rec *e) {
   static int state = 0;
+  /* The toolkit's own NVRTC first, by path: a bare soname would resolve to
+   * whatever copy the process has loaded already (PyTorch bundles an older
+   * one), and which compiler built a kernel would then depend on import order. */
   static const char *const names[] = {
-      "libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12",
-      "/usr/local/cuda/lib64/libnvrtc.so", NULL};
+      "/usr/local/cuda/lib64/libnvrtc.so.12", "/usr/local/cuda/lib64/libnvrtc.so",
+      "libnvrtc.so.12", "libnvrtc.so", NULL};
   char tried[512];
   void *h = NULL;
   const char *env;
