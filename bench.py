@@ -10,6 +10,10 @@ GPU, values N(0,1) rounded to 1/64 (ties occur), outputs fp32 max + 8-byte
 first-occurrence index. With N GPUs every rank holds its own (16384, 32000)
 slab of a (16384*N, 32000) array: rows shard with no communication (weak
 scaling). Metric: effective HBM GB/s = algorithmic bytes / device time.
+With N > 1 the line's `configs` also holds the STRONG-scaled configurations:
+the same 16384 rows split over the ranks, and the fp64 (2048, 1024, 1024)
+reductions whose reduced leading extent is split and finished by one
+all-reduce, each with its time on one GPU measured in the same run.
 
 The JSON line also carries: `e2e` (same call with HOST input: pinned
 host->device copy of the slab and device->host read of the results inside the
@@ -138,33 +142,54 @@ WORKLOAD = ("cfg3 GpuReduction MAXANDARGMAX, last axis of fp32 (16384, 32000) lo
 
 # --------------------------------------------------------------- reference arm
 
+def host_threads():
+    """Host cores this process may run on (the OpenMP team both CPU legs use)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def bench_config(rows):
+    """`config` of the JSON line: identical in both arms (same workload, same
+    rows, same bytes per step), so nothing measured goes in here."""
+    return {"workload": WORKLOAD, "rows_per_gpu": rows,
+            "bytes_per_step_per_gpu": rows * COLS * 4 + rows * 12,
+            "l2": "2.1 GB input per step exceeds the 126 MB L2; no flush needed"}
+
+
 def run_reference(args, rank):
-    """CPU arm: the oracle's C port of the reference kernel, all host threads."""
+    """CPU arm: the oracle's C port of the reference kernel over the WHOLE
+    (rows, 32000) slab per step, with an OpenMP team of every host core this
+    process may use - set explicitly, because launchers such as
+    torch.distributed.run export OMP_NUM_THREADS=1."""
     if rank != 0:
         return
     from oracle import oracle as O
     O.build()
-    sample_rows = 4096                       # bounded sample: 0.5 GB of the 2.1 GB slab per step
-    x = make_logits(0, sample_rows)
+    rows = args.rows
+    threads = O.set_threads(host_threads())
+    x = make_logits(0, rows)
     for _ in range(args.warmup):
         O.rowmaxarg_f32(x)
     t0 = time.perf_counter()
     for _ in range(args.steps):
         O.rowmaxarg_f32(x)
     dt = (time.perf_counter() - t0) / args.steps
-    nbytes = x.nbytes + sample_rows * 12
+    nbytes = x.nbytes + rows * 12
     val = nbytes / dt / 1e9
-    cores = os.cpu_count()
     emit({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "rows_per_gpu": ROWS,
-                   "sample": "host memory, first %d rows per step" % sample_rows},
-        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": "%d of 16384 rows per step; pygpu-on-pocl (the reference's "
-                                   "CPU path) is unavailable on this box" % sample_rows},
+        "config": bench_config(rows),
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "host_cores": os.cpu_count(),
+                         "omp_num_threads_env": os.environ.get("OMP_NUM_THREADS"),
+                         "sample": "all %d rows per step in host memory, OpenMP team of %d set "
+                                   "explicitly; pygpu-on-pocl (the reference's CPU path) is "
+                                   "unavailable on this box" % (rows, threads)},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     })
 
@@ -215,19 +240,28 @@ def side_configs(api, ctx, torch, stream, once=False):
                                          {torch.float32: np.float32, torch.float16: np.float16,
                                           torch.float64: np.float64}[t.dtype])
 
-    # cfg1: out = a*b + 0.5f, n = 2^24 fp32
+    # cfg1: out = a*b + 0.5f, n = 2^24 fp32. One launch touches 192 MiB, only 1.6 x L2, so
+    # successive launches rotate through NSET distinct (a, b, out) sets: a line is touched
+    # again only after 3 x 192 MiB of other traffic.
+    NSET = 1 if once else 3
     n = 1 << 24
-    ta = torch.rand(n, device="cuda", generator=g) * 2 - 1
-    tb = torch.rand(n, device="cuda", generator=g) * 2 - 1
-    to = torch.empty(n, device="cuda")
+    sets1 = []
+    for _ in range(NSET):
+        ta = torch.rand(n, device="cuda", generator=g) * 2 - 1
+        tb = torch.rand(n, device="cuda", generator=g) * 2 - 1
+        to = torch.empty(n, device="cuda")
+        sets1.append((ta, tb, to, dev_array(ta), dev_array(tb), dev_array(to)))
     torch.cuda.synchronize()
-    ga, gb, go = dev_array(ta), dev_array(tb), dev_array(to)
     ge = api.GpuElemwise(ctx, "out = a * b + 0.5f", [("a", np.float32, R), ("b", np.float32, R),
                                                       ("out", np.float32, W)], nd=1)
-    out["cfg1_elemwise_f32_contig"] = timed(lambda i: ge(ga, gb, go), 3 * 4 * n)
+    out["cfg1_elemwise_f32_contig"] = timed(
+        lambda i: ge(*sets1[i % NSET][3:]), 3 * 4 * n)
+    out["cfg1_elemwise_f32_contig"]["l2"] = "cold: %d buffer sets in rotation" % NSET
+    del sets1
 
-    # cfg2: SUM of fp32 4096x4096 over axis 1 and axis 0
-    nrot = 6                                       # 6 x 64 MiB inputs > 126 MB L2
+    # cfg2: SUM of fp32 4096x4096 over axis 1 and axis 0; cold = six distinct 64 MiB inputs in
+    # rotation (384 MiB > 126 MB L2), warm = the same input every launch (it fits L2)
+    nrot = 6
     txs = [torch.randn(4096, 4096, device="cuda", generator=g) for _ in range(nrot)]
     ts = torch.empty(4096, device="cuda")
     torch.cuda.synchronize()
@@ -238,26 +272,35 @@ def side_configs(api, ctx, torch, stream, once=False):
     l1 = api.lib().gpuarray_b200_launch_count()
     gsum(gs, None, gxs[0], [0])
     l2 = api.lib().gpuarray_b200_launch_count()
-    out["cfg2_sum_axis1"] = timed(lambda i: gsum(gs, None, gxs[i % nrot], [1]),
-                                  4096 * 4096 * 4 + 4096 * 4, launches=int(l1 - l0))
-    out["cfg2_sum_axis0"] = timed(lambda i: gsum(gs, None, gxs[i % nrot], [0]),
-                                  4096 * 4096 * 4 + 4096 * 4, launches=int(l2 - l1))
+    for ax, nl in ((1, int(l1 - l0)), (0, int(l2 - l1))):
+        cold = timed(lambda i: gsum(gs, None, gxs[i % nrot], [ax]),
+                     4096 * 4096 * 4 + 4096 * 4, launches=nl)
+        warm = timed(lambda i: gsum(gs, None, gxs[0], [ax]),
+                     4096 * 4096 * 4 + 4096 * 4, launches=nl)
+        cold["l2"] = "cold: %d inputs in rotation" % nrot
+        cold["l2_warm_us"] = warm["us"]
+        cold["l2_warm_GB/s"] = warm["GB/s"]
+        out["cfg2_sum_axis%d" % ax] = cold
     del txs, gxs
 
-    # cfg4: y = max(x + bias, 0), x an NHWC buffer viewed as NCHW, fp16
-    tbuf = torch.randn(64, 56, 56, 256, device="cuda", generator=g).half()
+    # cfg4: y = max(x + bias, 0), x an NHWC buffer viewed as NCHW, fp16; 196 MiB per launch,
+    # rotated like cfg1
+    sets4 = []
     tbias = (torch.rand(1, 256, 1, 1, device="cuda", generator=g) * 0.2 - 0.1).half()
-    ty = torch.empty(64, 256, 56, 56, device="cuda", dtype=torch.float16)
+    gbias = dev_array(tbias)
+    for _ in range(NSET):
+        tbuf = torch.randn(64, 56, 56, 256, device="cuda", generator=g).half()
+        ty = torch.empty(64, 256, 56, 56, device="cuda", dtype=torch.float16)
+        sets4.append((tbuf, ty, dev_array(tbuf).transpose((0, 3, 1, 2)), dev_array(ty)))
     torch.cuda.synchronize()
-    gbuf = dev_array(tbuf)
-    gxv = gbuf.transpose((0, 3, 1, 2))
-    gbias, gy = dev_array(tbias), dev_array(ty)
     ge4 = api.GpuElemwise(ctx, "y = fmaxf(x + bias, 0.0f)",
                           [("x", np.float16, R), ("bias", np.float16, R), ("y", np.float16, W)],
                           nd=4, convert_f16=True)
     out["cfg4_f16_bias_relu_nhwc_to_nchw"] = timed(
-        lambda i: ge4(gxv, gbias, gy, flags=api.GE_BROADCAST), 2 * tbuf.numel() * 2 + 512)
-    del ta, tb, to, tbuf, ty
+        lambda i: ge4(sets4[i % NSET][2], gbias, sets4[i % NSET][3], flags=api.GE_BROADCAST),
+        2 * 64 * 56 * 56 * 256 * 2 + 512)
+    out["cfg4_f16_bias_relu_nhwc_to_nchw"]["l2"] = "cold: %d buffer sets in rotation" % NSET
+    del sets4
 
     # cfg5: fp64 (2048, 1024, 1024) = 16 GiB: SUM over everything, MIN and MAX over (0, 2)
     try:
@@ -393,16 +436,70 @@ def other_shapes(api, ctx, torch, stream, once=False):
     return out
 
 
-def cfg5_sharded(api, ctx, torch, dist, stream, rank, world):
-    """fp64 (2048, 1024, 1024): each rank owns 2048/world leading planes, reduces
-    them to a partial of the final shape and one gpucomm all-reduce (NCCL on the
-    same stream) finishes. Time = max over ranks of (kernel + all-reduce)."""
+def sharded_configs(api, ctx, torch, dist, stream, rank, world, host_slab, t1_cfg3_us):
+    """The configurations that SPLIT a fixed problem over the ranks (strong
+    scaling), run whenever world > 1. Every time is the max over ranks of a
+    CUDA-event span on the library's stream, launches back to back.
+
+    cfg3_strong: the seed-2 (16384, 32000) logits, rank r owning rows
+      [r*16384/world, (r+1)*16384/world); no communication.
+    cfg5_*_sharded: fp64 (2048, 1024, 1024), rank r owning 2048/world leading
+      planes; per-GPU partial of the final shape, then ONE gpucomm all-reduce
+      (NCCL, same stream). Reported: kernel + all-reduce, the kernel alone, the
+      all-reduce alone, and the same reduction over all 2048 planes on one GPU
+      (x_vs_1gpu = that time / the sharded time).
+    cfg5_f64_maxandargmax_axes02_sharded: (value, global first index) over the
+      sharded extent through GpuReduction_call_sharded."""
+    out = {}
+
+    def span(fn, reps):
+        for _ in range(3):
+            fn()
+        ctx.sync()
+        dist.barrier()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(reps):
+            fn()
+        b.record(stream)
+        ctx.sync()
+        t = torch.tensor([a.elapsed_time(b) / reps], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0]) * 1e3
+
+    # ---- cfg3, rows split
+    rows = ROWS // world
+    full = torch.empty((ROWS, COLS), dtype=torch.float32, device="cuda")
+    if rank == 0:
+        full.copy_(host_slab, non_blocking=False)
+    dist.broadcast(full, 0)
+    mine = full[rank * rows:(rank + 1) * rows]
+    torch.cuda.synchronize()
+    gx = api.GpuArray.from_pointer(ctx, mine.data_ptr(), (rows, COLS), np.float32)
+    gmax = api.GpuArray.empty(ctx, (rows,), np.float32)
+    garg = api.GpuArray.empty(ctx, (rows,), np.uint64)
+    us = span(lambda: api.maxandargmax(gmax, garg, gx, [1]), 50)
+    vm, am = gmax.to_numpy(), garg.to_numpy()
+    ref = mine[:32].cpu().numpy()
+    check = bool((vm[:32] == ref.max(1)).all() and (am[:32] == ref.argmax(1)).all())
+    total = ROWS * COLS * 4 + ROWS * 12
+    out["cfg3_strong"] = {
+        "us": round(us, 2), "GB/s": round(total / us / 1e3, 1), "rows_per_gpu": rows,
+        "x_vs_1gpu": round(t1_cfg3_us / us, 3), "t_1gpu_us": round(t1_cfg3_us, 2),
+        "frac_nominal_8TBs_x_gpus": round(total / us / 1e3 / (NOMINAL_HBM_GBS * world), 3),
+        "collective": "none", "scaling": "strong", "first_rows_check_rank0": check}
+    del gx, mine, full
+
+    # ---- cfg5, leading planes split
     planes = 2048 // world
-    g = torch.Generator(device="cuda").manual_seed(4 + rank)
-    t5 = torch.rand(planes, 1024, 1024, device="cuda", dtype=torch.float64, generator=g)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    t5 = torch.rand(2048, 1024, 1024, device="cuda", dtype=torch.float64, generator=g)
     t5.mul_(2).sub_(1)
     torch.cuda.synchronize()
-    g5 = api.GpuArray.from_pointer(ctx, t5.data_ptr(), (planes, 1024, 1024), np.float64)
+    g_full = api.GpuArray.from_pointer(ctx, t5.data_ptr(), (2048, 1024, 1024), np.float64)
+    shard = t5[rank * planes:(rank + 1) * planes]
+    g5 = api.GpuArray.from_pointer(ctx, shard.data_ptr(), (planes, 1024, 1024), np.float64)
     cid = [api.GpuComm.gen_clique_id(ctx) if rank == 0 else None]
     dist.broadcast_object_list(cid, src=0)
     comm = api.GpuComm(ctx, cid[0], world, rank)
@@ -410,34 +507,47 @@ def cfg5_sharded(api, ctx, torch, dist, stream, rank, world):
     o1 = api.GpuArray.empty(ctx, (), np.float64)
     pk = api.GpuArray.empty(ctx, (1024,), np.float64)
     ok = api.GpuArray.empty(ctx, (1024,), np.float64)
-    ops = {"sum_all": (api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.float64), [0, 1, 2], p1, o1, api.GA_SUM),
-           "min_axes02": (api.GpuReduction(ctx, api.GA_REDUCE_MIN, np.float64), [0, 2], pk, ok, api.GA_MIN),
-           "max_axes02": (api.GpuReduction(ctx, api.GA_REDUCE_MAX, np.float64), [0, 2], pk, ok, api.GA_MAX)}
-    out = {}
+    ops = {"sum_all": (api.GA_REDUCE_SUM, [0, 1, 2], p1, o1, api.GA_SUM),
+           "min_axes02": (api.GA_REDUCE_MIN, [0, 2], pk, ok, api.GA_MIN),
+           "max_axes02": (api.GA_REDUCE_MAX, [0, 2], pk, ok, api.GA_MAX)}
     total_bytes = 2048 * 1024 * 1024 * 8
-    for name, (gr, axes, part, res, cop) in ops.items():
-        def step():
+    for name, (rop, axes, part, res, cop) in ops.items():
+        gr = api.GpuReduction(ctx, rop, np.float64)
+
+        def both():
             gr(part, None, g5, axes)
             comm.all_reduce(part, res, cop)
-        for _ in range(3):
-            step()
-        ctx.sync()
-        dist.barrier()
-        a = torch.cuda.Event(enable_timing=True)
-        b = torch.cuda.Event(enable_timing=True)
-        reps = 10
-        a.record(stream)
-        for _ in range(reps):
-            step()
-        b.record(stream)
-        ctx.sync()
-        t = torch.tensor([a.elapsed_time(b) / reps], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        us = float(t[0]) * 1e3
+        us_both = span(both, 10)
+        us_kernel = span(lambda: gr(part, None, g5, axes), 10)
+        us_comm = span(lambda: comm.all_reduce(part, res, cop), 20)
+        us_one = span(lambda: gr(res, None, g_full, axes), 4)
         out["cfg5_f64_%s_sharded" % name] = {
-            "us": round(us, 2), "GB/s": round(total_bytes / us / 1e3, 1),
-            "frac_nominal_8TBs_x_gpus": round(total_bytes / us / 1e3 / (NOMINAL_HBM_GBS * world), 3),
-            "planes_per_gpu": planes, "collective": "gpucomm_all_reduce (NCCL)"}
+            "us": round(us_both, 2), "GB/s": round(total_bytes / us_both / 1e3, 1),
+            "kernel_only_us": round(us_kernel, 2), "all_reduce_only_us": round(us_comm, 2),
+            "t_1gpu_us": round(us_one, 2), "x_vs_1gpu": round(us_one / us_both, 3),
+            "frac_nominal_8TBs_x_gpus": round(total_bytes / us_both / 1e3 / (NOMINAL_HBM_GBS * world), 3),
+            "planes_per_gpu": planes, "collective": "gpucomm_all_reduce (NCCL), %d B" % res.nbytes,
+            "scaling": "strong"}
+        gr.free()
+
+    # ---- (value, first global index) with the reduced extent sharded
+    if hasattr(api, "reduction_call_sharded"):
+        gr = api.GpuReduction(ctx, api.GA_REDUCE_MAXANDARGMAX, np.float64)
+        gv = api.GpuArray.empty(ctx, (1024,), np.float64)
+        gi = api.GpuArray.empty(ctx, (1024,), np.uint64)
+        us_both = span(lambda: api.reduction_call_sharded(gr, comm, gv, gi, g5, [0, 2],
+                                                          rank * planes, 2048), 10)
+        us_kernel = span(lambda: gr(gv, gi, g5, [0, 2]), 10)
+        us_one = span(lambda: gr(gv, gi, g_full, [0, 2]), 4)
+        out["cfg5_f64_maxandargmax_axes02_sharded"] = {
+            "us": round(us_both, 2), "GB/s": round(total_bytes / us_both / 1e3, 1),
+            "kernel_only_us": round(us_kernel, 2), "t_1gpu_us": round(us_one, 2),
+            "x_vs_1gpu": round(us_one / us_both, 3),
+            "frac_nominal_8TBs_x_gpus": round(total_bytes / us_both / 1e3 / (NOMINAL_HBM_GBS * world), 3),
+            "planes_per_gpu": planes,
+            "collective": "all-reduce of the value, candidate-index kernel, all-reduce MIN of the index",
+            "scaling": "strong"}
+        gr.free()
     ctx.sync()
     comm.free()
     return out
@@ -534,13 +644,16 @@ def run_ours(args, rank, world, local_rank):
         e2e_ms = (time.perf_counter() - t0) * 1e3
 
     sharded = None
-    if world > 1 and args.cfg5_sharded:
-        del gx
-        sharded = cfg5_sharded(api, ctx, torch, dist, stream, rank, world)
     if world > 1:
         t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = float(t[0]), float(t[1])
+    if world > 1 and not args.no_side_configs:
+        del gx
+        # no try/except here: a rank that carried on alone would leave its peers
+        # waiting in a collective; an exception ends the whole launch instead
+        sharded = sharded_configs(api, ctx, torch, dist, stream, rank, world, host,
+                                  ms / args.steps * 1e3)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -557,6 +670,7 @@ def run_ours(args, rank, world, local_rank):
         from oracle import oracle as O
         sample_rows = min(4096, ROWS)
         xs = host.numpy()[:sample_rows]
+        threads = O.set_threads(host_threads())
         O.rowmaxarg_f32(xs)
         best = 1e9
         t_end = time.perf_counter() + 10.0
@@ -571,8 +685,10 @@ def run_ours(args, rank, world, local_rank):
         xs.argmax(1)
         t_np = time.perf_counter() - t0
         sb = xs.nbytes + sample_rows * 12
-        cpu = {"value": sb / best / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
-               "sample": "first %d of %d rows, best of %d passes (~10 s)" % (sample_rows, ROWS, reps),
+        cpu = {"value": sb / best / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+               "host_cores": os.cpu_count(),
+               "sample": "first %d of %d rows, best of %d passes (~10 s), OpenMP team of %d"
+                         % (sample_rows, ROWS, reps, threads),
                "numpy_1core_GBs": sb / t_np / 1e9}
 
     line = {
@@ -580,11 +696,8 @@ def run_ours(args, rank, world, local_rank):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD,
-                   "rows_per_gpu": ROWS,
-                   "bytes_per_step_per_gpu": step_bytes,
-                   "l2": "2.1 GB input per launch exceeds the 126 MB L2; no flush needed",
-                   "frac_of_nominal_8TBs_per_gpu": per_gpu / NOMINAL_HBM_GBS},
+        "config": bench_config(ROWS),
+        "frac_of_nominal_8TBs_per_gpu": per_gpu / NOMINAL_HBM_GBS,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": ROWS * COLS * 4,
                 "d2h_bytes_per_step": ROWS * 12, "steps": e2e_steps},
         "gpu_launches": int(launches),
@@ -656,8 +769,9 @@ def main():
                     help="also time reductions and elementwise calls on shapes outside the five "
                          "named configurations (adds an `other_shapes` object to the line)")
     ap.add_argument("--cfg5-sharded", action="store_true",
-                    help="with N > 1: also time fp64 (2048,1024,1024) SUM / MIN / MAX with the "
-                         "reduced leading axis sharded and one gpucomm all-reduce per result")
+                    help="accepted for compatibility: with N > 1 the sharded configurations "
+                         "(cfg3 rows split, cfg5 planes split + all-reduce) always run unless "
+                         "--no-side-configs is given")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -76,6 +76,9 @@ def lib():
         L.oracle_rowmaxarg_f32.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t,
                                            ctypes.c_void_p, ctypes.c_void_p]
         L.oracle_pcg_fill_f32.argtypes = [ctypes.c_uint64, ctypes.c_void_p, ctypes.c_size_t]
+        L.oracle_set_threads.restype = ctypes.c_int
+        L.oracle_set_threads.argtypes = [ctypes.c_int]
+        L.oracle_threads_used.restype = ctypes.c_int
         _LIB = L
     return _LIB
 
@@ -150,6 +153,13 @@ def minmaxarg(x, axes, is_min=False):
     if rc != 0:
         raise ValueError("oracle_minmaxarg rejected the arguments")
     return vals, idx
+
+
+def set_threads(n):
+    """Fixes the OpenMP team of the timed loops to `n` threads, overriding
+    OMP_NUM_THREADS; returns the team size a parallel region really gets."""
+    lib().oracle_set_threads(int(n))
+    return int(lib().oracle_threads_used())
 
 
 def rowmaxarg_f32(x):

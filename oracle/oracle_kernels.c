@@ -27,6 +27,9 @@
 #include <stdint.h>
 #include <string.h>
 #include <sys/types.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 /* typecodes of include/gpuarray/types.h */
 enum { T_BOOL = 0, T_BYTE, T_UBYTE, T_SHORT, T_USHORT, T_INT, T_UINT, T_LONG, T_ULONG,
@@ -195,6 +198,36 @@ int oracle_minmaxarg(int typecode, int is_min, const void *src, unsigned nd, con
     }
   }
   return 0;
+}
+
+/* Thread team of the timed CPU baseline. oracle_set_threads(n) fixes the team
+ * size whatever OMP_NUM_THREADS says (launchers such as torch.distributed.run
+ * export OMP_NUM_THREADS=1); oracle_threads_used() opens a parallel region
+ * and returns the team size the runtime really gave. Both return 1 when the
+ * file was built without OpenMP. */
+int oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n >= 1) {
+    omp_set_dynamic(0);
+    omp_set_num_threads(n);
+  }
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
+
+int oracle_threads_used(void) {
+  int team = 1;
+#ifdef _OPENMP
+#pragma omp parallel
+  {
+#pragma omp master
+    team = omp_get_num_threads();
+  }
+#endif
+  return team;
 }
 
 /* Row-wise max and first argmax of a C-contiguous float matrix: the cfg-3

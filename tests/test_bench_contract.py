@@ -18,7 +18,8 @@ def run(args, env=None):
 
 
 def test_reference_arm_prints_one_json_line(built):
-    r = run(["--impl", "reference", "--steps", "1", "--warmup", "0"])
+    r = run(["--impl", "reference", "--steps", "1", "--warmup", "0", "--rows", "1024"],
+            env={"OMP_NUM_THREADS": "1"})       # what torch.distributed.run exports
     assert r.returncode == 0, r.stderr[-2000:]
     lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
     assert len(lines) == 1
@@ -26,14 +27,20 @@ def test_reference_arm_prints_one_json_line(built):
     assert d["impl"] == "reference" and d["unit"] == "GB/s" and d["higher_is_better"] is True
     assert d["n_gpus"] == 1 and d["steps"] == 1 and d["warmup"] == 0 and d["value"] > 0
     assert d["vs_baseline"] is None and d["dtype"] == "f32" and d["data"] == "synthetic"
-    assert "MAXANDARGMAX" in d["config"]["workload"] and "sample" in d["config"]
-    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    # `config` holds the workload only (it must equal the product arm's); the sample and
+    # the thread team are described under cpu_baseline
+    assert "MAXANDARGMAX" in d["config"]["workload"] and d["config"]["rows_per_gpu"] == 1024
+    assert set(d["config"]) == {"workload", "rows_per_gpu", "bytes_per_step_per_gpu", "l2"}
+    assert d["cpu_baseline"]["kind"] == "port" and "all 1024 rows" in d["cpu_baseline"]["sample"]
+    # the team is every core the process may use, whatever OMP_NUM_THREADS said
+    assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+    assert d["cpu_baseline"]["omp_num_threads_env"] == "1"
     assert d["cpu_baseline"]["value"] == d["value"]
     assert d["e2e"] == {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
 
 
 def test_reference_arm_under_a_multi_rank_launch_runs_on_rank_zero_only(built):
-    r0 = run(["--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "0"],
+    r0 = run(["--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "0", "--rows", "1024"],
              env={"RANK": "0", "LOCAL_RANK": "0", "WORLD_SIZE": "2"})
     r1 = run(["--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "0"],
              env={"RANK": "1", "LOCAL_RANK": "1", "WORLD_SIZE": "2"})
