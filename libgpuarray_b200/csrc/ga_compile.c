@@ -10,7 +10,7 @@
  * (fused multiply-add on), like the reference which passes only -arch.
  *
  * Caches: per context, a list of loaded modules keyed by a 128-bit hash of
- * (library tag, options, source); optionally a directory of cubin files with
+ * (library tag, options, NVRTC version, in-library headers, source); optionally a directory of cubin files with
  * the same key (GPUARRAY_CACHE_PATH or gpucontext_props_kernel_cache), which
  * can be filled on a machine without a GPU. */
 #include <sys/stat.h>
@@ -26,21 +26,49 @@ struct ga_module {
   struct ga_module *next;
 };
 
+#define GA_STD_OPT "--std=c++17"
+
+/* Everything besides the program text that decides what machine code comes
+ * out: the library's kernel ABI tag, the compiler options, the version of the
+ * NVRTC that is bound (two toolkits give different code for the same text),
+ * and the in-library headers. Computed once per process. */
+static const char *key_prefix(size_t *len) {
+  static char *prefix = NULL;
+  static size_t prefix_len = 0;
+  if (prefix == NULL) {
+    ga_strb sb;
+    unsigned int i;
+    int major = 0, minor = 0;
+    ga_error_rec scratch;
+    memset(&scratch, 0, sizeof(scratch));
+    if (ga_load_nvrtc(&scratch) == GA_NO_ERROR) ga_rtc.p_nvrtcVersion(&major, &minor);
+    ga_strb_init(&sb);
+    ga_strb_printf(&sb, GA_KERNEL_ABI_TAG "\n" GA_ARCH_OPT "\n" GA_STD_OPT "\nnvrtc %d.%d\n", major,
+                   minor);
+    for (i = 0; i < ga_template_count; i++) {
+      uint64_t h = ga_hash64(ga_template_sources[i], strlen(ga_template_sources[i]), 7);
+      ga_strb_printf(&sb, "%s:%016llx\n", ga_template_names[i], (unsigned long long)h);
+    }
+    if (!sb.failed) {
+      prefix_len = sb.len;
+      prefix = sb.s; /* kept for the life of the process */
+    }
+  }
+  *len = prefix_len;
+  return prefix != NULL ? prefix : "";
+}
+
 static void make_key(const char *src, const char *const *defines, uint64_t key[2]) {
   ga_strb sb;
-  unsigned int i;
+  size_t plen;
+  const char *prefix = key_prefix(&plen);
   ga_strb_init(&sb);
-  ga_strb_puts(&sb, GA_KERNEL_ABI_TAG "\n" GA_ARCH_OPT "\n");
+  ga_strb_putn(&sb, prefix, plen);
   if (defines != NULL)
     for (; *defines != NULL; defines++) {
       ga_strb_puts(&sb, *defines);
       ga_strb_puts(&sb, "\n");
     }
-  /* the in-library headers are part of the program text */
-  for (i = 0; i < ga_template_count; i++) {
-    uint64_t h = ga_hash64(ga_template_sources[i], strlen(ga_template_sources[i]), 7);
-    ga_strb_printf(&sb, "%s:%016llx\n", ga_template_names[i], (unsigned long long)h);
-  }
   ga_strb_puts(&sb, src);
   key[0] = ga_hash64(ga_strb_cstr(&sb), sb.len, 0);
   key[1] = ga_hash64(ga_strb_cstr(&sb), sb.len, 0x9e3779b97f4a7c15ULL);
@@ -128,7 +156,7 @@ static int nvrtc_build(ga_error_rec *e, const char *src, const char *const *defi
   if (err != GA_NO_ERROR) return err;
 
   opts[nopts++] = GA_ARCH_OPT;
-  opts[nopts++] = "--std=c++17";
+  opts[nopts++] = GA_STD_OPT;
   if (defines != NULL)
     for (; *defines != NULL && nopts < 63; defines++) opts[nopts++] = *defines;
 

@@ -518,15 +518,45 @@ int gpudata_transfer(gpudata *dst, size_t dstoff, gpudata *src, size_t srcoff, s
   if (sz == 0) return GA_NO_ERROR;
   if (!range_ok(dst, dstoff, sz) || !range_ok(src, srcoff, sz))
     return ga_err_set(ctx->err, GA_VALUE_ERROR, "Copy exceeds a buffer");
-  /* order after the source's work, copy on the destination stream */
-  ga_ctx_enter(src->ctx);
-  ga_cu.p_cuStreamSynchronize(src->ctx->s);
-  ga_ctx_exit(src->ctx);
-  ga_ctx_enter(ctx);
-  CU(cuMemcpyPeerAsync, (dst->ptr + dstoff, ctx->cu, src->ptr + srcoff, src->ctx->cu, sz, ctx->s));
-fail:
-  ga_ctx_exit(ctx);
-  return err;
+  /* Both streams are ordered around the copy with events, no host wait (the
+   * reference brackets both buffers the same way, src/gpuarray_buffer_cuda.c:
+   * 899-946): the copy runs on the destination stream AFTER the work queued
+   * so far on the source stream, and whatever the source context queues next
+   * (a write to the source buffer, a reuse of its block after a release)
+   * runs AFTER the copy has read it. */
+  {
+    CUevent ready = NULL, done = NULL;
+    gpucontext *sctx = src->ctx;
+    CUresult r;
+    const char *what = "cuEventCreate";
+    ga_ctx_enter(sctx);
+    r = ga_cu.p_cuEventCreate(&ready, CU_EVENT_DISABLE_TIMING);
+    if (r == CUDA_SUCCESS) what = "cuEventRecord", r = ga_cu.p_cuEventRecord(ready, sctx->s);
+    ga_ctx_exit(sctx);
+    if (r == CUDA_SUCCESS) {
+      ga_ctx_enter(ctx);
+      what = "cuStreamWaitEvent", r = ga_cu.p_cuStreamWaitEvent(ctx->s, ready, 0);
+      if (r == CUDA_SUCCESS)
+        what = "cuMemcpyPeerAsync",
+        r = ga_cu.p_cuMemcpyPeerAsync(dst->ptr + dstoff, ctx->cu, src->ptr + srcoff, sctx->cu, sz,
+                                      ctx->s);
+      if (r == CUDA_SUCCESS)
+        what = "cuEventCreate", r = ga_cu.p_cuEventCreate(&done, CU_EVENT_DISABLE_TIMING);
+      if (r == CUDA_SUCCESS) what = "cuEventRecord", r = ga_cu.p_cuEventRecord(done, ctx->s);
+      ga_ctx_exit(ctx);
+    }
+    if (r == CUDA_SUCCESS) {
+      ga_ctx_enter(sctx);
+      what = "cuStreamWaitEvent", r = ga_cu.p_cuStreamWaitEvent(sctx->s, done, 0);
+      ga_ctx_exit(sctx);
+    }
+    /* destroying an event that is still pending is allowed: the driver frees
+     * it once it has completed */
+    if (ready != NULL) ga_cu.p_cuEventDestroy(ready);
+    if (done != NULL) ga_cu.p_cuEventDestroy(done);
+    if (r != CUDA_SUCCESS) err = ga_err_cuda(ctx->err, what, r);
+    return err;
+  }
 }
 
 int gpudata_read(void *dst, gpudata *src, size_t srcoff, size_t sz) {

@@ -92,7 +92,7 @@ GA_HIDDEN uint64_t ga_hash64(const void *data, size_t len, uint64_t seed);
   X(cuDevicePrimaryCtxRetain) X(cuDevicePrimaryCtxRelease)                         \
   X(cuCtxPushCurrent) X(cuCtxPopCurrent) X(cuCtxGetCurrent) X(cuCtxSynchronize)    \
   X(cuCtxGetDevice)                                                                \
-  X(cuStreamCreate) X(cuStreamDestroy) X(cuStreamSynchronize)                      \
+  X(cuStreamCreate) X(cuStreamDestroy) X(cuStreamSynchronize) X(cuStreamWaitEvent) \
   X(cuMemAlloc) X(cuMemFree) X(cuMemHostAlloc) X(cuMemFreeHost)                    \
   X(cuMemHostGetDevicePointer) X(cuMemGetInfo) X(cuMemGetAddressRange)             \
   X(cuMemcpyHtoDAsync) X(cuMemcpyDtoHAsync) X(cuMemcpyDtoDAsync) X(cuMemcpyPeerAsync) \

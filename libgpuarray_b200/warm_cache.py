@@ -11,9 +11,6 @@ changed, or before a deployment that must not compile at start-up:
     python -m libgpuarray_b200.warm_cache --pack /tmp/ksrc sources.json.gz
     # 2. anywhere: compile them into a cache directory
     python -m libgpuarray_b200.warm_cache sources.json.gz .kernel_cache -j 8
-
-`libgpuarray_b200/kernel_sources.json.gz` holds the variants of this
-repository's test-suite and benchmark.
 """
 import ctypes
 import gzip
@@ -23,7 +20,6 @@ import os
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-DEFAULT_SOURCES = os.path.join(HERE, "kernel_sources.json.gz")
 
 
 def pack(src_dir, out_path):
@@ -54,7 +50,7 @@ def _compile_many(job):
     return len(texts), bad
 
 
-def warm(sources_path=DEFAULT_SOURCES, cache_dir=None, jobs=None):
+def warm(sources_path, cache_dir=None, jobs=None):
     """Compiles every recorded variant into cache_dir; returns (compiled, failed)."""
     cache_dir = os.path.abspath(cache_dir or os.path.join(os.path.dirname(HERE), ".kernel_cache"))
     os.makedirs(cache_dir, exist_ok=True)
@@ -79,7 +75,10 @@ def main(argv):
         i = argv.index("-j")
         jobs = int(argv[i + 1])
         argv = argv[:i] + argv[i + 2:]
-    src = argv[0] if argv else DEFAULT_SOURCES
+    if not argv:
+        print(__doc__)
+        return 2
+    src = argv[0]
     cache = argv[1] if len(argv) > 1 else None
     done, bad = warm(src, cache, jobs)
     print("compiled %d kernel variants, %d failed" % (done, bad))

@@ -14,7 +14,9 @@ import numpy
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: build_pygpu.py <reference tree>")
+REF = sys.argv[1]
 SITE = os.path.join(HERE, "_ref", "pygpu_site", "pygpu")
 WORK = os.path.join(HERE, "_ref", "pygpu_build")
 EXT = sysconfig.get_config_var("EXT_SUFFIX")

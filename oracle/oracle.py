@@ -43,10 +43,22 @@ _GANAME = {0: "ga_bool", 1: "ga_byte", 2: "ga_ubyte", 3: "ga_short", 4: "ga_usho
            23: "ga_half"}
 
 
+def reference_tree():
+    """Root of the reference checkout used to build oracle/_ref, or None: the
+    GPUARRAY_REFERENCE_TREE environment variable, else a directory named
+    `reference` beside this repository."""
+    cand = os.environ.get("GPUARRAY_REFERENCE_TREE") or os.path.join(
+        os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "src")) else None
+
+
 def build():
-    """Compiles liboracle.so (and oracle/_ref when the reference tree is present)."""
-    r = subprocess.run(["make", "-C", _HERE], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
-                       text=True)
+    """Compiles liboracle.so (and oracle/_ref when a reference tree is found)."""
+    cmd = ["make", "-C", _HERE]
+    ref = reference_tree()
+    if ref is not None:
+        cmd.append("REF=" + ref)
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError("oracle build failed:\n" + r.stdout)
 
