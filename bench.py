@@ -302,6 +302,23 @@ def side_configs(api, ctx, torch, stream, once=False):
     out["cfg4_f16_bias_relu_nhwc_to_nchw"]["l2"] = "cold: %d buffer sets in rotation" % NSET
     del sets4
 
+    # map + reduce in one pass: sum(a * b) over 2^26 fp32 (two 256 MiB inputs read once each;
+    # elementwise-then-reduce would write and re-read a third 256 MiB array)
+    nd = 1 << 26
+    tda = torch.randn(nd, device="cuda", generator=g)
+    tdb = torch.randn(nd, device="cuda", generator=g)
+    tds = torch.empty((), device="cuda")
+    torch.cuda.synchronize()
+    gda, gdb, gds = dev_array(tda), dev_array(tdb), dev_array(tds)
+    mr = api.GpuMapReduction(ctx, "a * b", "a + b", "0", np.float32,
+                             [("a", np.float32, R), ("b", np.float32, R)])
+    out["mapreduce_dot_f32_2^26"] = timed(lambda i: mr(gds, gda, gdb, axes=[0]), 2 * 4 * nd + 4,
+                                           reps=10)
+    ref = float((tda.double() * tdb.double()).sum())
+    scale = float((tda.double() * tdb.double()).abs().sum())
+    out["mapreduce_dot_f32_2^26"]["check"] = bool(abs(float(tds) - ref) <= 1e-6 * 26 * scale)
+    del tda, tdb
+
     # cfg5: fp64 (2048, 1024, 1024) = 16 GiB: SUM over everything, MIN and MAX over (0, 2)
     try:
         planes = 128 if once else 2048

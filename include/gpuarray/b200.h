@@ -91,11 +91,12 @@ GPUARRAY_PUBLIC int gpuarray_b200_elemwise_plan(unsigned int n, const gpuelemwis
  * extent, launch geometry) for a source of the given shape and byte strides on a
  * device with num_sms multiprocessors, computed on the host alone. `base` stands
  * for the address of the source's first element (its alignment decides the
- * vector width); destinations are taken as C-contiguous. out[0..19] = kernel
+ * vector width); destinations are taken as C-contiguous. out[0..23] = kernel
  * shape (0 rows, 1 cols, 2 general), vector width, group size, flattened runs,
  * runs at once, one-run mode, lazy index, byte folding, threads per output
  * (general kernel), 64-bit index, splits, seg, nseg, units, grid x, grid y,
- * block x, block y, outputs, reduced elements per output. No reference
+ * block x, block y (cols: row lanes per CTA), outputs, reduced elements per
+ * output, lean rows loop, three spare words. No reference
  * counterpart (its scheduler is src/gpuarray_reduction.c:673-776). */
 GPUARRAY_PUBLIC int gpuarray_b200_reduction_plan(int op, int src_tc, int dst_tc, unsigned int nd,
                                                  const size_t *dims, const ssize_t *strides,
@@ -113,6 +114,32 @@ GPUARRAY_PUBLIC int gpuarray_b200_reduction_layout(int op, int src_tc, int dst_t
                                                    unsigned long long base, unsigned int num_sms,
                                                    unsigned long long *out, void *layout,
                                                    size_t cap, size_t *used);
+
+/* As gpuarray_b200_reduction_source / _layout, for GpuMapReduction: the source
+ * of one kernel variant (malloc'ed; the caller frees), and what a call would
+ * decide for array arguments given by rank, extents, byte strides and the
+ * address of their first element (alignment only), with the destination taken
+ * as C-contiguous. out[0..13] = kernel shape (0 rows, 1 cols, 2 general),
+ * vector width, group, threads per output, access modes (2 bits per array:
+ * 0 gather, 1 vector, 2 broadcast), splits, seg, nseg, units, grid x, grid y,
+ * block x, block y, outputs. No reference counterpart (the reference renders
+ * one kernel per rank in Python, pygpu/reduction.py:217-239). */
+GPUARRAY_PUBLIC char *gpuarray_b200_mapreduction_source(const char *preamble, const char *map_expr,
+                                                        const char *reduce_expr,
+                                                        const char *neutral, int out_tc,
+                                                        unsigned int n, gpuelemwise_arg *args,
+                                                        int flags, int shape, int vec, int group,
+                                                        int tpo, unsigned long long modes);
+GPUARRAY_PUBLIC int gpuarray_b200_mapreduction_plan(int out_tc, unsigned int n,
+                                                    const gpuelemwise_arg *args,
+                                                    const unsigned int *nds,
+                                                    const size_t *const *dims,
+                                                    const ssize_t *const *strides,
+                                                    const unsigned long long *bases,
+                                                    unsigned int reduxLen, const int *reduxList,
+                                                    int call_flags, unsigned int num_sms,
+                                                    unsigned long long *out, void *layout,
+                                                    size_t cap, size_t *used);
 
 /* Sum of n contiguous float32 values on the current device WITHOUT allocating
  * anything: no cudaMalloc / cudaFree, no library workspace. (No counterpart in

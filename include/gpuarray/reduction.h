@@ -30,6 +30,7 @@
 #define GPUARRAY_REDUCTION_H
 
 #include <gpuarray/array.h>
+#include <gpuarray/elemwise.h>
 
 #ifdef __cplusplus
 extern "C" {
@@ -72,6 +73,76 @@ GPUARRAY_PUBLIC void GpuReduction_free(GpuReduction *gr);
 GPUARRAY_PUBLIC int GpuReduction_call(const GpuReduction *gr, GpuArray *d0, GpuArray *d1,
                                       const GpuArray *s0, unsigned reduxLen,
                                       const int *reduxList, int flags);
+
+/* As GpuReduction_call, for a source that is this GPU's SHARD of a larger array:
+ * along the reduced axis `shard_axis` the source holds coordinates
+ * [shard_lo, shard_lo + s0->dimensions[shard_axis]) of an axis of extent
+ * shard_global, the other ranks of `comm` hold the rest. Every rank calls it
+ * with its own shard and receives the result of the WHOLE array in its
+ * destinations: per-GPU partial, then gpucomm_all_reduce on the context's
+ * stream (the call site of src/gpuarray_collectives_cuda_nccl.c:286-316), no
+ * host round trip.
+ *  - SUM, PROD, PRODNZ, ALL, ANY: one all-reduce (sum / prod / min / max) of the
+ *    partial. AND, OR, XOR: GA_UNSUPPORTED_ERROR (the collectives have no
+ *    bitwise operator).
+ *  - MIN, MAX and the ARG variants: the index written is the flat index in the
+ *    whole reduced extent (shard offset and global radix included); ranks are
+ *    combined with an all-reduce MAX/MIN of the value followed by an all-reduce
+ *    MIN of a candidate index, so the lowest global index wins ties exactly as
+ *    on one GPU, the NaN-first rule and signed zeros included.
+ * comm may be NULL (one rank: no collective), which also serves to test the
+ * path on one GPU. <gpuarray/collectives.h> declares gpucomm. */
+struct _gpucomm;
+GPUARRAY_PUBLIC int GpuReduction_call_sharded(const GpuReduction *gr, struct _gpucomm *comm,
+                                              GpuArray *d0, GpuArray *d1, const GpuArray *s0,
+                                              unsigned reduxLen, const int *reduxList,
+                                              int shard_axis, size_t shard_lo,
+                                              size_t shard_global, int flags);
+
+/* ---- reductions of a mapped expression over several arguments ----
+ *
+ *     out[kept...] = REDUCE over the reduced axes of MAP(arg0, arg1, ..., scalars)
+ *
+ * The C form of pygpu's ReductionKernel (pygpu/reduction.py:137-291; its test
+ * pygpu/tests/test_reduction.py:57-84 reduces a[i]*b[i] with one operand
+ * broadcast). Map and reduction run as ONE pass over memory.
+ *  preamble     code placed before the kernel (may be NULL)
+ *  map_expr     C expression in which every argument appears as a scalar
+ *               variable of its own name (arrays: one element), e.g. "a * b";
+ *               its value keeps its natural C type
+ *  reduce_expr  C expression over `a` and `b` combining two partial results,
+ *               e.g. "a + b", "max(a, b)"; it must be associative and
+ *               commutative (the reference assumes the same)
+ *  neutral      C expression of the neutral element, e.g. "0"
+ *  out_typecode type of the destination AND of the accumulator (float when it
+ *               is GA_HALF and GE_CONVERT_F16 is given)
+ *  n, args      argument descriptors as for GpuElemwise_new; arrays are inputs
+ *               (GE_READ), scalars are passed by value at call time
+ *  flags        GE_CONVERT_F16 or 0
+ * Returns NULL and sets the context's error on failure (the three expressions
+ * are compiled here, so a faulty one is reported by the constructor). */
+typedef struct _GpuMapReduction GpuMapReduction;
+
+GPUARRAY_PUBLIC GpuMapReduction *GpuMapReduction_new(gpucontext *ctx, const char *preamble,
+                                                     const char *map_expr,
+                                                     const char *reduce_expr,
+                                                     const char *neutral, int out_typecode,
+                                                     unsigned int n, gpuelemwise_arg *args,
+                                                     int flags);
+GPUARRAY_PUBLIC void GpuMapReduction_free(GpuMapReduction *mr);
+
+/* Runs the reduction over reduxList[0..reduxLen) of the broadcast shape of the
+ * array arguments.
+ *  out    caller-allocated destination: the non-reduced axes in ascending
+ *         order, elements of out_typecode; offset and strides are honoured
+ *  args   one entry per declared argument: GpuArray * for arrays, pointer to
+ *         a host scalar of the declared type for GE_SCALAR arguments
+ *  flags  GE_BROADCAST lets extents of 1 stretch; GE_PADSHAPE pads lower ranks
+ *         on the left (as in GpuElemwise_call); without them every array must
+ *         have the same shape
+ * A reduction over zero elements writes `neutral`. */
+GPUARRAY_PUBLIC int GpuMapReduction_call(GpuMapReduction *mr, GpuArray *out, void **args,
+                                         unsigned int reduxLen, const int *reduxList, int flags);
 
 #ifdef __cplusplus
 }

@@ -158,6 +158,11 @@ def lib():
     sig("GpuReduction_new", ci, ctypes.POINTER(vp), vp, ci, cu, cu, ci, ci)
     sig("GpuReduction_free", None, vp)
     sig("GpuReduction_call", ci, vp, A, A, A, cu, ctypes.POINTER(ci), ci)
+    sig("GpuReduction_call_sharded", ci, vp, vp, A, A, A, cu, ctypes.POINTER(ci), ci, sz, sz, ci)
+    sig("GpuMapReduction_new", vp, vp, ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p,
+        ctypes.c_char_p, ci, cu, ctypes.POINTER(_ElemwiseArg), ci)
+    sig("GpuMapReduction_free", None, vp)
+    sig("GpuMapReduction_call", ci, vp, A, ctypes.POINTER(vp), cu, ctypes.POINTER(ci), ci)
     for name in ("gpucomm_new", "gpucomm_free", "gpucomm_gen_clique_id", "gpucomm_all_reduce",
                  "gpucomm_get_count", "gpucomm_get_rank"):
         if not hasattr(L, name):
@@ -547,6 +552,80 @@ class GpuReduction:
     def free(self):
         if self.ptr is not None:
             lib().GpuReduction_free(self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            if self.ctx.ptr is not None:
+                self.free()
+        except Exception:
+            pass
+
+
+def reduction_call_sharded(gr, comm, d0, d1, src, axes, shard_lo, shard_global, shard_axis=None):
+    """GpuReduction_call_sharded (include/gpuarray/reduction.h): `src` is this
+    rank's slab [shard_lo, shard_lo + extent) of an axis of extent shard_global;
+    `shard_axis` defaults to the first listed axis. comm=None: no collective."""
+    ax = (ctypes.c_int * max(len(axes), 1))(*axes)
+    _check(gr.ctx.ptr, lib().GpuReduction_call_sharded(
+        gr.ptr, comm.ptr if comm is not None else None,
+        ctypes.byref(d0.ga) if d0 is not None else None,
+        ctypes.byref(d1.ga) if d1 is not None else None, ctypes.byref(src.ga), len(axes), ax,
+        axes[0] if shard_axis is None else shard_axis, shard_lo, shard_global, 0))
+
+
+class GpuMapReduction:
+    """GpuMapReduction_new/_call/_free (include/gpuarray/reduction.h): the
+    reduction of a mapped expression over several broadcastable arguments, the
+    C form of pygpu's ReductionKernel (pygpu/reduction.py:137-291).
+
+    args: sequence of (name, dtype-or-typecode, flags) as for GpuElemwise;
+    arrays are GE_READ, scalars GE_SCALAR."""
+
+    def __init__(self, ctx, map_expr, reduce_expr, neutral, out_dtype, args, preamble="",
+                 convert_f16=False):
+        self.ctx = ctx
+        self.ptr = None
+        n = len(args)
+        self._names = [a[0].encode() for a in args]
+        arr = (_ElemwiseArg * max(n, 1))()
+        self.argspec = []
+        for i, (name, tc, fl) in enumerate(args):
+            if not isinstance(tc, int):
+                tc = typecode(tc)
+            arr[i].name = self._names[i]
+            arr[i].typecode = tc
+            arr[i].flags = fl
+            self.argspec.append((tc, fl))
+        self.out_tc = out_dtype if isinstance(out_dtype, int) else typecode(out_dtype)
+        p = lib().GpuMapReduction_new(ctx.ptr, preamble.encode() if preamble else None,
+                                      map_expr.encode(), reduce_expr.encode(), str(neutral).encode(),
+                                      self.out_tc, n, arr, GE_CONVERT_F16 if convert_f16 else 0)
+        if not p:
+            msg = lib().gpucontext_error(ctx.ptr, -1)
+            raise GpuArrayException(msg.decode(errors="replace"), _last_code(ctx))
+        self.ptr = ctypes.c_void_p(p)
+
+    def __call__(self, out, *args, axes, broadcast=True, padshape=True):
+        flags = (GE_BROADCAST if broadcast else 0) | (GE_PADSHAPE if padshape else 0)
+        n = len(self.argspec)
+        assert len(args) == n
+        ptrs = (ctypes.c_void_p * max(n, 1))()
+        keep = []
+        for i, (a, (tc, fl)) in enumerate(zip(args, self.argspec)):
+            if fl & GE_SCALAR:
+                v = np.array(a, dtype=np_dtype(tc))
+                keep.append(v)
+                ptrs[i] = v.ctypes.data
+            else:
+                ptrs[i] = ctypes.addressof(a.ga)
+        ax = (ctypes.c_int * max(len(axes), 1))(*axes)
+        _check(self.ctx.ptr, lib().GpuMapReduction_call(self.ptr, ctypes.byref(out.ga), ptrs,
+                                                        len(axes), ax, flags))
+
+    def free(self):
+        if self.ptr is not None:
+            lib().GpuMapReduction_free(self.ptr)
             self.ptr = None
 
     def __del__(self):

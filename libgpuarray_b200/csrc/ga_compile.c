@@ -28,34 +28,72 @@ struct ga_module {
 
 #define GA_STD_OPT "--std=c++17"
 
-/* Everything besides the program text that decides what machine code comes
- * out: the library's kernel ABI tag, the compiler options, the version of the
- * NVRTC that is bound (two toolkits give different code for the same text),
- * and the in-library headers. Computed once per process. */
+/* Everything besides the program text and the headers it includes that
+ * decides what machine code comes out: the library's kernel ABI tag, the
+ * compiler options and the version of the NVRTC that is bound (two toolkits
+ * give different code for the same text). Computed once per process. */
 static const char *key_prefix(size_t *len) {
-  static char *prefix = NULL;
+  static char prefix[160];
   static size_t prefix_len = 0;
-  if (prefix == NULL) {
-    ga_strb sb;
-    unsigned int i;
+  if (prefix_len == 0) {
     int major = 0, minor = 0;
     ga_error_rec scratch;
     memset(&scratch, 0, sizeof(scratch));
     if (ga_load_nvrtc(&scratch) == GA_NO_ERROR) ga_rtc.p_nvrtcVersion(&major, &minor);
-    ga_strb_init(&sb);
-    ga_strb_printf(&sb, GA_KERNEL_ABI_TAG "\n" GA_ARCH_OPT "\n" GA_STD_OPT "\nnvrtc %d.%d\n", major,
-                   minor);
-    for (i = 0; i < ga_template_count; i++) {
-      uint64_t h = ga_hash64(ga_template_sources[i], strlen(ga_template_sources[i]), 7);
-      ga_strb_printf(&sb, "%s:%016llx\n", ga_template_names[i], (unsigned long long)h);
-    }
-    if (!sb.failed) {
-      prefix_len = sb.len;
-      prefix = sb.s; /* kept for the life of the process */
-    }
+    prefix_len = (size_t)snprintf(prefix, sizeof(prefix),
+                                  GA_KERNEL_ABI_TAG "\n" GA_ARCH_OPT "\n" GA_STD_OPT "\nnvrtc %d.%d\n",
+                                  major, minor);
   }
   *len = prefix_len;
-  return prefix != NULL ? prefix : "";
+  return prefix;
+}
+
+#define GA_MAX_TEMPLATES 32
+
+/* bit j of the result: in-library header j is named by an #include "..." of `text` */
+static unsigned int includes_of(const char *text) {
+  unsigned int mask = 0, j;
+  const char *p = text;
+  while ((p = strstr(p, "#include \"")) != NULL) {
+    const char *name = p + 10, *end = strchr(name, '"');
+    if (end == NULL) break;
+    for (j = 0; j < ga_template_count && j < GA_MAX_TEMPLATES; j++)
+      if (strlen(ga_template_names[j]) == (size_t)(end - name) &&
+          strncmp(ga_template_names[j], name, (size_t)(end - name)) == 0)
+        mask |= 1u << j;
+    p = end;
+  }
+  return mask;
+}
+
+/* The in-library headers a program pulls in are part of its text: the key
+ * holds a hash of every header reachable from the program's #include lines
+ * (and of no other, so that editing one template leaves the cached kernels of
+ * the others valid). Header hashes and their include sets are computed once. */
+static void append_header_hashes(ga_strb *sb, const char *src) {
+  static int ready = 0;
+  static uint64_t hash[GA_MAX_TEMPLATES];
+  static unsigned int direct[GA_MAX_TEMPLATES];
+  unsigned int reach, frontier, j;
+  if (!ready) {
+    for (j = 0; j < ga_template_count && j < GA_MAX_TEMPLATES; j++) {
+      hash[j] = ga_hash64(ga_template_sources[j], strlen(ga_template_sources[j]), 7);
+      direct[j] = includes_of(ga_template_sources[j]);
+    }
+    ready = 1;
+  }
+  reach = 0;
+  frontier = includes_of(src);
+  while (frontier != 0) {
+    unsigned int next = 0;
+    reach |= frontier;
+    for (j = 0; j < ga_template_count && j < GA_MAX_TEMPLATES; j++)
+      if (frontier & (1u << j)) next |= direct[j];
+    frontier = next & ~reach;
+  }
+  for (j = 0; j < ga_template_count && j < GA_MAX_TEMPLATES; j++)
+    if (reach & (1u << j))
+      ga_strb_printf(sb, "%s:%016llx\n", ga_template_names[j], (unsigned long long)hash[j]);
 }
 
 static void make_key(const char *src, const char *const *defines, uint64_t key[2]) {
@@ -69,6 +107,7 @@ static void make_key(const char *src, const char *const *defines, uint64_t key[2
       ga_strb_puts(&sb, *defines);
       ga_strb_puts(&sb, "\n");
     }
+  append_header_hashes(&sb, src);
   ga_strb_puts(&sb, src);
   key[0] = ga_hash64(ga_strb_cstr(&sb), sb.len, 0);
   key[1] = ga_hash64(ga_strb_cstr(&sb), sb.len, 0x9e3779b97f4a7c15ULL);

@@ -26,6 +26,8 @@ enum { SHAPE_ROWS = 0, SHAPE_COLS = 1, SHAPE_GENERAL = 2 };
 
 typedef struct rd_variant {
   int shape, vec, idx64, tpo, dst_tc, write_val, write_idx, group, flat, mu, onerun, fast8, lazy;
+  int simple; /* rows: lean one-run-per-warp loop */
+  int by;     /* cols: row lanes per CTA (0 = RD_BY) */
   ga_function fn;
   struct rd_variant *next;
 } rd_variant;
@@ -40,6 +42,10 @@ struct _GpuReduction {
   size_t scratch_sz;
   gpudata *tickets;      /* arrival counters, zero between launches */
   size_t tickets_sz;
+  /* helpers of sharded (value, index) calls, built on first use */
+  GpuReduction *sh_pair; /* MIN/MAXANDARG* operator that produces the local pair */
+  GpuElemwise *sh_e1, *sh_e2, *sh_e3;
+  int sh_e3_key;         /* (has value << 8) | (has index << 9) | index typecode of sh_e3 */
 };
 
 /* Normalised problem; field order matches struct ga__rd_layout. */
@@ -52,7 +58,15 @@ typedef struct rd_layout {
   unsigned long long rmul[RD_MAXD];
   unsigned long long splits, inner, seg, nseg, units, tiles;
   unsigned int dv[4];
+  unsigned long long ioff, early, nan_first;
 } rd_layout;
+
+/* One reduced axis of the source is a shard of a longer axis held by several
+ * GPUs: this rank's slab starts at coordinate `lo` of `global` along it. */
+typedef struct rd_shard {
+  int axis;
+  unsigned long long lo, global;
+} rd_shard;
 
 static int op_is_pair(ga_reduce_op op) {
   return op == GA_REDUCE_MIN || op == GA_REDUCE_MAX || op == GA_REDUCE_ARGMIN ||
@@ -149,11 +163,13 @@ static char *gen_source(const GpuReduction *gr, const rd_variant *v) {
                       "#define GA_RD_THREADS %d\n#define GA_RD_TPO %d\n"
                       "#define GA_RD_BY %d\n#define GA_RD_GROUP %d\n#define GA_RD_FLAT %d\n"
                       "#define GA_RD_MU %d\n#define GA_RD_ONERUN %d\n#define GA_RD_FAST8 %d\n#define GA_RD_LAZY %d\n"
+                      "#define GA_RD_SIMPLE %d\n"
                       "#define %s\n"
                       "#include \"ga_reduce.cuh\"\n",
                  gr->kind, tc_is_float(gr->src_tc), v->write_val, v->write_idx,
                  v->idx64 ? "unsigned long long" : "unsigned int", v->vec, RD_THREADS, v->tpo,
-                 RD_BY, v->group ? v->group : RD_THREADS, v->flat, v->mu ? v->mu : 1, v->onerun, v->fast8, v->lazy,
+                 v->by ? v->by : RD_BY, v->group ? v->group : RD_THREADS, v->flat, v->mu ? v->mu : 1,
+                 v->onerun, v->fast8, v->lazy, v->simple,
                  v->shape == SHAPE_ROWS   ? "GA_RD_BUILD_ROWS"
                  : v->shape == SHAPE_COLS ? "GA_RD_BUILD_COLS"
                                           : "GA_RD_BUILD_GENERAL");
@@ -174,7 +190,8 @@ static rd_variant *get_variant(GpuReduction *gr, const rd_variant *want, int *er
         v->tpo == want->tpo && v->dst_tc == want->dst_tc &&
         v->write_val == want->write_val && v->write_idx == want->write_idx &&
         v->group == want->group && v->flat == want->flat && v->mu == want->mu &&
-        v->onerun == want->onerun && v->fast8 == want->fast8 && v->lazy == want->lazy)
+        v->onerun == want->onerun && v->fast8 == want->fast8 && v->lazy == want->lazy &&
+        v->simple == want->simple && v->by == want->by)
       return v;
   v = malloc(sizeof(*v));
   if (v == NULL) {
@@ -219,10 +236,13 @@ GPUARRAY_PUBLIC char *gpuarray_b200_reduction_source(int op, int src_tc, int dst
   v.vec = vec;
   v.idx64 = idx64;
   v.tpo = tpo;
-  v.group = group & 0xffff; /* bits 16-19: runs at once, bit 20: one-run mode, bit 21: flattened */
+  v.group = group & 0xffff; /* bits 16-19: runs at once, bit 20: one-run mode, bit 21: flattened,
+                               bit 22: lean one-run-per-warp loop, bits 24-29: row lanes (cols) */
   v.mu = (group >> 16) & 0xf;
   v.onerun = (group >> 20) & 1;
   v.flat = (group >> 21) & 1;
+  v.simple = (group >> 22) & 1;
+  v.by = (group >> 24) & 0x3f;
   v.dst_tc = dst_tc;
   v.write_val = op_writes_val(gr.op);
   v.write_idx = op_writes_idx(gr.op);
@@ -267,6 +287,10 @@ void GpuReduction_free(GpuReduction *gr) {
   }
   if (gr->scratch != NULL) gpudata_release(gr->scratch);
   if (gr->tickets != NULL) gpudata_release(gr->tickets);
+  GpuReduction_free(gr->sh_pair);
+  GpuElemwise_free(gr->sh_e1);
+  GpuElemwise_free(gr->sh_e2);
+  GpuElemwise_free(gr->sh_e3);
   free(gr);
   ga_ctx_unref(ctx);
 }
@@ -303,13 +327,15 @@ static long long ll_abs(long long v) { return v < 0 ? -v : v; }
 /* Fills nf/nr, dims, strides, weights and totals of `L`. */
 static int normalise(int kind, ga_error_rec *e, rd_layout *L, const GpuArray *d0,
                      const GpuArray *d1, const GpuArray *s, const unsigned char *red,
-                     unsigned reduxLen, const int *reduxList) {
+                     unsigned reduxLen, const int *reduxList, const rd_shard *sh,
+                     unsigned long long *span) {
   unsigned i, k, n;
   unsigned long long mul;
 
   memset(L, 0, sizeof(*L));
   L->nf_total = 1;
   L->nr_total = 1;
+  L->nan_first = (sh == NULL || sh->lo == 0) ? 1 : 0;
 
   /* kept axes, ascending; destination axis k pairs with the k-th kept axis */
   for (i = 0, k = 0, n = 0; i < s->nd; i++) {
@@ -350,7 +376,11 @@ static int normalise(int kind, ga_error_rec *e, rd_layout *L, const GpuArray *d0
     for (i = reduxLen; i > 0; i--) {
       unsigned ax = (unsigned)reduxList[i - 1];
       size_t dsz = s->dimensions[ax];
+      const int sharded = sh != NULL && sh->axis == (int)ax;
       L->nr_total *= dsz;
+      /* the flat index counts in the extents of the WHOLE array: a sharded axis
+       * weighs its global extent, and the slab's first coordinate is an offset */
+      if (sharded && kind == 1) L->ioff = sh->lo * mul;
       if (dsz != 1) {
         if (m == 64)
           return ga_err_set(e, GA_UNSUPPORTED_ERROR, "More than 64 reduced axes");
@@ -359,8 +389,9 @@ static int normalise(int kind, ga_error_rec *e, rd_layout *L, const GpuArray *d0
         w[m] = kind == 1 ? mul : 0;
         m++;
       }
-      mul *= dsz;
+      mul *= sharded ? sh->global : dsz;
     }
+    if (span != NULL) *span = mul; /* flat indices run over [0, span) */
     /* traversal order = memory order: largest |stride| outermost (stable insertion sort) */
     for (i = 1; i < m; i++) {
       unsigned long long td = dim[i], tw = w[i];
@@ -441,10 +472,12 @@ static int all_multiple(const long long *v, unsigned n, long long m) {
 }
 
 /* Tuning for experiments: GPUARRAY_B200_RD="ctas_per_sm,seg_vectors,cta_min_vectors,
- * cols_ctas_per_sm,onerun_ctas_per_sm,onerun_loads_per_lane,onerun_outputs_at_once,
- * lazy_index (0/1),lazy_min_vectors_per_lane". The
+ * cols_ctas_per_sm (0 = the lanes rule),onerun_ctas_per_sm,onerun_loads_per_lane,
+ * onerun_outputs_at_once,lazy_index (0/1),lazy_min_vectors_per_lane,cols_row_lanes (0 = rule),
+ * lean_rows (0/1),cols_early_rows". The
  * defaults are the best of sweeps on a B200. */
-static unsigned rd_cols_ctas_per_sm = 3;
+static unsigned rd_cols_ctas_per_sm = 0, rd_cols_by = 0;
+static unsigned rd_simple = 1, rd_cols_early = 4;
 static unsigned rd_onerun_ctas_per_sm = 3, rd_onerun_lpl = 4, rd_onerun_mu = 0, rd_lazy = 1, rd_lazy_min = 32;
 
 static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_bytes) {
@@ -454,9 +487,9 @@ static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_
   if (!parsed) {
     const char *env = getenv("GPUARRAY_B200_RD");
     if (env != NULL)
-      sscanf(env, "%u,%u,%u,%u,%u,%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm,
-             &rd_onerun_ctas_per_sm, &rd_onerun_lpl, &rd_onerun_mu, &rd_lazy, &rd_lazy_min);
-    if (rd_cols_ctas_per_sm == 0) rd_cols_ctas_per_sm = 3;
+      sscanf(env, "%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm,
+             &rd_onerun_ctas_per_sm, &rd_onerun_lpl, &rd_onerun_mu, &rd_lazy, &rd_lazy_min,
+             &rd_cols_by, &rd_simple, &rd_cols_early);
     *warp_bytes = t_warp;
     if (t_ctas == 0) t_ctas = 32;
     if (t_seg == 0) t_seg = 8;
@@ -474,6 +507,8 @@ typedef struct rd_plan_in {
   int src_tc, dst_tc, need_val, need_idx;
   unsigned num_sms;
   unsigned long long p_src; /* address of the source's first element (alignment only) */
+  unsigned long long idx_span; /* flat indices run over [0, idx_span): the reduced element
+                                  count, or that of the whole array when the source is a shard */
 } rd_plan_in;
 
 /* Chooses the kernel variant, the split of the reduced extent and the launch
@@ -493,7 +528,7 @@ static int rd_plan(const rd_plan_in *in, rd_layout *L, rd_variant *want, unsigne
   want->dst_tc = in->dst_tc;
   want->write_val = in->need_val;
   want->write_idx = in->need_idx;
-  want->idx64 = L->nr_total >= 0xffffffffULL;
+  want->idx64 = L->nr_total >= 0xffffffffULL || in->idx_span >= 0xffffffffULL;
   want->vec = 1;
   want->tpo = 1;
   L->splits = 1;
@@ -619,15 +654,39 @@ static int rd_plan(const rd_plan_in *in, rd_layout *L, rd_variant *want, unsigne
     L->tiles = (L->inner + 32ULL * vec - 1) / (32ULL * vec);
     ko = L->nf_total / L->inner;
     nwork = ko * L->tiles;
-    s = ((unsigned long long)in->num_sms * rd_cols_ctas_per_sm + nwork - 1) / nwork;
-    if (s > (L->nr_total + RD_BY * 8 - 1) / (RD_BY * 8)) s = (L->nr_total + RD_BY * 8 - 1) / (RD_BY * 8);
-    if (s > 1024) s = 1024;
+    {
+      /* Row lanes per CTA (by) times splits = the row lanes that share one column tile.
+       * Measured on B200 (fp32 4096 x 4096 over axis 0, 32 tiles): what counts is that
+       * every thread walks about 16 rows and that the whole grid is resident at once
+       * (2048 threads per SM); 16 lanes x 16 splits 14.1 us, 32 x 8 14.3 us, 8 x 32 14.4 us,
+       * 8 x 14 17.2 us, 32 x 10 (two waves) 18.9 us. 16 lanes keep the shared exchange of
+       * the widest states (16 bytes x 4 x 32 x 16) within the static limit. */
+      unsigned long long lanes_fit = ((unsigned long long)in->num_sms * 64) / nwork; /* warps */
+      unsigned long long lanes_want = (L->nr_total + 15) / 16, lanes;
+      unsigned by = rd_cols_by ? rd_cols_by : RD_BY;
+      if (rd_cols_by == 0 && lanes_want >= 128 && lanes_fit >= 32) by = 16;
+      lanes = lanes_want < lanes_fit ? lanes_want : lanes_fit;
+      if (rd_cols_ctas_per_sm != 0) /* experiment knob: CTAs per SM instead */
+        lanes = (((unsigned long long)in->num_sms * rd_cols_ctas_per_sm + nwork - 1) / nwork) * by;
+      s = lanes / by;
+      if (s < 1) s = 1;
+      if (s > (L->nr_total + by * 8 - 1) / (by * 8)) s = (L->nr_total + by * 8 - 1) / (by * 8);
+      if (s > 1024) s = 1024;
+      want->by = (int)by;
+      block[1] = by;
+      /* L2 hints ahead of the dependency wait: one reduced dimension, no outer kept
+       * position, fully vectorised rows (so every tile row starts on 16 bytes). Measured
+       * on B200 (fp32 4096 x 4096 over axis 0, 16 lanes x 16 splits): 14.2 -> 13.4 us with
+       * 4 rows per lane; 8 rows give the same, 16 rows and hints issued AFTER the wait
+       * are slower than none. */
+      if (L->nr == 1 && ko == 1 && (size_t)vec * elsize == 16 && rd_cols_early != 0)
+        L->early = rd_cols_early;
+    }
     L->splits = s ? s : 1;
     L->units = nwork; /* tickets: one per column tile */
     grid[0] = nwork > 0x7fffffffULL ? 0x7fffffffu : (unsigned)nwork;
     grid[1] = (unsigned)L->splits;
     block[0] = 32;
-    block[1] = RD_BY;
   } else {
     /* --- arbitrary strides --- */
     unsigned long long groups_per_block, blocks;
@@ -647,6 +706,12 @@ static int rd_plan(const rd_plan_in *in, rd_layout *L, rd_variant *want, unsigne
   if (in->kind == 1 && want->shape == SHAPE_ROWS && !want->onerun && !want->flat && want->mu <= 1 &&
       rd_lazy && L->seg / (unsigned)want->vec / (unsigned)(want->group ? want->group : RD_THREADS) >= rd_lazy_min)
     want->lazy = 1;
+  /* one run per output, a warp each, nothing split: the lean loop (GA_RD_SIMPLE). Measured on
+   * B200, fp32 4096 x 4096 over axis 1, launches back to back: 13.8 -> see the profile notes */
+  if (want->shape == SHAPE_ROWS && rd_simple && want->group == 32 && L->splits == 1 && L->nr == 1 &&
+      L->nseg == 1 && !want->onerun && !want->flat && want->mu <= 1 && !want->lazy &&
+      L->nf_total < 0xffffffffULL && L->inner < 0x7fffffffULL)
+    want->simple = 1;
   /* whole-word arithmetic on vectors of 1-byte elements (see ga__fold_lanes) */
   if (elsize == 1 && want->vec % 4 == 0 && want->shape == SHAPE_ROWS) {
     if (in->op == GA_REDUCE_SUM && !tc_is_float(want->dst_tc) &&
@@ -662,10 +727,11 @@ static int rd_plan(const rd_plan_in *in, rd_layout *L, rd_variant *want, unsigne
  * the given shape and byte strides on a device with `num_sms` SMs, without any
  * device. Destinations are taken as C-contiguous. `base` stands for the
  * address of the source's first element (its alignment decides vector width).
- * out[0..19] = shape (0 rows, 1 cols, 2 general), vec, group, flat, runs at
+ * out[0..23] = shape (0 rows, 1 cols, 2 general), vec, group, flat, runs at
  * once, one-run mode, lazy index, byte folding, threads per output (general),
- * 64-bit index, splits, seg, nseg, units, grid x, grid y, block x, block y,
- * outputs, reduced elements per output. Returns a GA_* code. */
+ * 64-bit index, splits, seg, nseg, units, grid x, grid y, block x, block y
+ * (cols: row lanes per CTA), outputs, reduced elements per output, lean rows
+ * loop, three spare words. Returns a GA_* code. */
 static int plan_worker(int op, int src_tc, int dst_tc, unsigned int nd, const size_t *dims,
                        const ssize_t *strides, unsigned int reduxLen, const int *reduxList,
                        unsigned long long base, unsigned int num_sms, unsigned long long *out,
@@ -724,9 +790,9 @@ static int plan_worker(int op, int src_tc, int dst_tc, unsigned int nd, const si
   in.num_sms = num_sms;
   in.p_src = base;
   err = normalise(in.kind, in.e, &L, in.need_val ? &d : NULL, in.need_idx ? &di : NULL, &s, red,
-                  reduxLen, reduxList);
+                  reduxLen, reduxList, NULL, &in.idx_span);
   if (err != GA_NO_ERROR) return err;
-  memset(out, 0, 20 * sizeof(*out));
+  memset(out, 0, 24 * sizeof(*out));
   out[18] = L.nf_total;
   out[19] = L.nr_total;
   if (L.nf_total == 0 || L.nr_total == 0) return GA_NO_ERROR;
@@ -750,6 +816,7 @@ static int plan_worker(int op, int src_tc, int dst_tc, unsigned int nd, const si
   out[15] = grid[1];
   out[16] = block[0];
   out[17] = block[1];
+  out[20] = (unsigned long long)want.simple;
   if (layout_out != NULL) *layout_out = L;
   return GA_NO_ERROR;
 }
@@ -785,8 +852,8 @@ GPUARRAY_PUBLIC int gpuarray_b200_reduction_layout(int op, int src_tc, int dst_t
   return GA_NO_ERROR;
 }
 
-int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const GpuArray *s0,
-                      unsigned reduxLen, const int *reduxList, int flags) {
+static int rd_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const GpuArray *s0,
+                   unsigned reduxLen, const int *reduxList, int flags, const rd_shard *sh) {
   GpuReduction *gr = (GpuReduction *)cgr;
   gpucontext *ctx;
   unsigned char red[64];
@@ -795,6 +862,7 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
   unsigned i, ndd;
   unsigned grid[3] = {1, 1, 1}, block[3] = {RD_THREADS, 1, 1};
   int err = GA_NO_ERROR, need_val, need_idx;
+  unsigned long long idx_span = 0;
   CUdeviceptr p_src, p_d0 = 0, p_d1 = 0, p_val = 0, p_idx = 0, p_tic = 0;
   void *params[7];
   (void)flags;
@@ -850,7 +918,11 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
       return ga_err_set(ctx->err, GA_VALUE_ERROR, "Index destination must hold 8-byte integers");
   }
 
-  err = normalise(gr->kind, ctx->err, &L, d0, d1, s0, red, reduxLen, reduxList);
+  if (sh != NULL && (sh->axis < 0 || (unsigned)sh->axis >= s0->nd || !red[sh->axis] ||
+                     sh->lo + s0->dimensions[sh->axis] > sh->global))
+    return ga_err_set(ctx->err, GA_VALUE_ERROR,
+                      "The sharded axis must be a reduced axis and the slab must lie inside it");
+  err = normalise(gr->kind, ctx->err, &L, d0, d1, s0, red, reduxLen, reduxList, sh, &idx_span);
   if (err != GA_NO_ERROR) return err;
   if (L.nf_total == 0) return GA_NO_ERROR;
   if (L.nr_total == 0 && gr->kind == 1)
@@ -870,6 +942,7 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
     in.need_idx = need_idx;
     in.num_sms = ctx->num_sms;
     in.p_src = p_src;
+    in.idx_span = idx_span;
     err = rd_plan(&in, &L, &want, grid, block);
     if (err != GA_NO_ERROR) return err;
   }
@@ -893,6 +966,224 @@ int GpuReduction_call(const GpuReduction *cgr, GpuArray *d0, GpuArray *d1, const
   params[5] = &p_idx;
   params[6] = &p_tic;
   return ga_launch(ctx, &v1->fn, grid, block, 0, params);
+}
+
+int GpuReduction_call(const GpuReduction *gr, GpuArray *d0, GpuArray *d1, const GpuArray *s0,
+                      unsigned reduxLen, const int *reduxList, int flags) {
+  return rd_call(gr, d0, d1, s0, reduxLen, reduxList, flags, NULL);
+}
+
+/* ------------------------------------------ reduced extent sharded over GPUs */
+
+/* In-place all-reduce of a contiguous array (no-op without a communicator). */
+static int sh_all_reduce(GpuArray *a, int opcode, gpucomm *comm) {
+  if (comm == NULL) return GA_NO_ERROR;
+  return GpuArray_all_reduce(a, a, opcode, comm);
+}
+
+static int sh_elemwise(gpucontext *ctx, GpuElemwise **slot, const char *expr, unsigned n,
+                       gpuelemwise_arg *args, int convert_f16) {
+  if (*slot != NULL) return GA_NO_ERROR;
+  *slot = GpuElemwise_new(ctx, "", expr, n, args, 0, convert_f16 ? GE_CONVERT_F16 : 0);
+  return *slot != NULL ? GA_NO_ERROR : ctx->err->code;
+}
+
+/* (value, index) operators when ONE reduced axis is sharded over the ranks of
+ * `comm`: the reference's collectives have no pair operator
+ * (src/gpuarray_collectives_cuda_nccl.c:158-185: sum, prod, max, min), so the
+ * combination is two all-reduces of existing operators around three small
+ * elementwise kernels, everything enqueued on the context's stream with no
+ * host round trip:
+ *   1. the local kernel writes (v, i): i already is the flat index in the WHOLE
+ *      reduced extent (the shard's offset and the global radix are folded into
+ *      the kernel's index weights); a shard that does not hold element 0 does
+ *      not apply the NaN-first rule;
+ *   2. w = v with a NaN (only possible on the rank that holds element 0, where
+ *      it is the final answer) replaced by the winning infinity; p = payload
+ *      bits of v: bit 0 "not a NaN", bit 1 "negative zero";
+ *   3. all-reduce MAX (MIN) of w                                   -> best
+ *   4. c = (w == best and i valid) ? (i << 2 | p) : all-ones
+ *   5. all-reduce MIN of c: the lowest global index wins ties, and since every
+ *      index belongs to exactly one rank the two payload bits of the winner
+ *      travel with it                                              -> r
+ *   6. index = r >> 2; value = NaN if payload bit 0 is clear, else best with
+ *      the winner's sign when best is zero.
+ * Bit-exact with the single-GPU kernel on the whole array, ties, NaN-first and
+ * signed zeros included (the NaN written is the canonical quiet NaN). */
+static int sharded_pair(GpuReduction *gr, gpucomm *comm, GpuArray *d0, GpuArray *d1,
+                        const GpuArray *s0, unsigned reduxLen, const int *reduxList,
+                        const rd_shard *sh) {
+  gpucontext *ctx = gr->ctx;
+  const int is_min = op_is_min(gr->op), isf = tc_is_float(gr->src_tc), tc = gr->src_tc;
+  const int half = tc == GA_HALF;
+  const GpuArray *shape_of = d0 != NULL ? d0 : d1;
+  GpuArray v, i, w, p, c;
+  int have[5] = {0, 0, 0, 0, 0}, err, k;
+  void *args[5];
+
+  if (gr->sh_pair == NULL) {
+    err = GpuReduction_new(&gr->sh_pair, ctx, is_min ? GA_REDUCE_MINANDARGMIN : GA_REDUCE_MAXANDARGMAX,
+                           0, 0, tc, 0);
+    if (err != GA_NO_ERROR) return err;
+  }
+#define SH_TMP(arr, slot, typecode)                                                            \
+  err = GpuArray_empty(&arr, ctx, typecode, shape_of->nd, shape_of->dimensions, GA_C_ORDER);   \
+  if (err != GA_NO_ERROR) goto done;                                                           \
+  have[slot] = 1;
+  SH_TMP(v, 0, tc)
+  SH_TMP(i, 1, GA_ULONG)
+  SH_TMP(c, 4, GA_ULONG)
+  err = rd_call(gr->sh_pair, &v, &i, s0, reduxLen, reduxList, 0, sh);
+  if (err != GA_NO_ERROR) goto done;
+
+  if (isf) {
+    gpuelemwise_arg a1[3] = {{"v", tc, GE_READ}, {"w", tc, GE_WRITE}, {"p", GA_UBYTE, GE_WRITE}};
+    SH_TMP(w, 2, tc)
+    SH_TMP(p, 3, GA_UBYTE)
+    err = sh_elemwise(ctx, &gr->sh_e1,
+                      is_min ? "w = (v != v) ? -INFINITY : v; "
+                               "p = ((v != v) ? 0 : 1) | ((v == 0 && signbit(v)) ? 2 : 0)"
+                             : "w = (v != v) ? INFINITY : v; "
+                               "p = ((v != v) ? 0 : 1) | ((v == 0 && signbit(v)) ? 2 : 0)",
+                      3, a1, half);
+    if (err != GA_NO_ERROR) goto done;
+    args[0] = &v; args[1] = &w; args[2] = &p;
+    err = GpuElemwise_call(gr->sh_e1, args, 0);
+    if (err != GA_NO_ERROR) goto done;
+  }
+  {
+    GpuArray *best = isf ? &w : &v; /* the all-reduce runs in place */
+    GpuArray wl; /* the local values, kept for step 4 */
+    int have_wl = 0;
+    if (comm != NULL) {
+      err = GpuArray_copy(&wl, best, GA_C_ORDER);
+      if (err != GA_NO_ERROR) goto done;
+      have_wl = 1;
+      err = sh_all_reduce(best, is_min ? GA_MIN : GA_MAX, comm);
+    }
+    if (err == GA_NO_ERROR) {
+      if (isf) {
+        gpuelemwise_arg a2[5] = {{"w", tc, GE_READ}, {"b", tc, GE_READ}, {"i", GA_ULONG, GE_READ},
+                                 {"p", GA_UBYTE, GE_READ}, {"c", GA_ULONG, GE_WRITE}};
+        err = sh_elemwise(ctx, &gr->sh_e2,
+                          "c = (w == b && i != 18446744073709551615ULL) ? ((i << 2) | p) "
+                          ": 18446744073709551615ULL", 5, a2, half);
+        args[0] = have_wl ? &wl : best; args[1] = best; args[2] = &i; args[3] = &p; args[4] = &c;
+      } else {
+        gpuelemwise_arg a2[4] = {{"w", tc, GE_READ}, {"b", tc, GE_READ}, {"i", GA_ULONG, GE_READ},
+                                 {"c", GA_ULONG, GE_WRITE}};
+        err = sh_elemwise(ctx, &gr->sh_e2,
+                          "c = (w == b && i != 18446744073709551615ULL) ? ((i << 2) | 1) "
+                          ": 18446744073709551615ULL", 4, a2, 0);
+        args[0] = have_wl ? &wl : best; args[1] = best; args[2] = &i; args[3] = &c;
+      }
+      if (err == GA_NO_ERROR) err = GpuElemwise_call(gr->sh_e2, args, 0);
+    }
+    if (have_wl) GpuArray_clear(&wl);
+    if (err != GA_NO_ERROR) goto done;
+    err = sh_all_reduce(&c, GA_MIN, comm);
+    if (err != GA_NO_ERROR) goto done;
+    {
+      /* step 6, written straight into the caller's destinations (any strides) */
+      gpuelemwise_arg a3[4];
+      unsigned n3 = 0;
+      const int key = (d0 != NULL ? 1 << 8 : 0) | (d1 != NULL ? 1 << 9 : 0) |
+                      (d1 != NULL ? d1->typecode : 0);
+      char expr[256];
+      a3[n3].name = "b"; a3[n3].typecode = tc; a3[n3].flags = GE_READ; args[n3++] = best;
+      a3[n3].name = "r"; a3[n3].typecode = GA_ULONG; a3[n3].flags = GE_READ; args[n3++] = &c;
+      expr[0] = '\0';
+      if (d0 != NULL) {
+        a3[n3].name = "o"; a3[n3].typecode = tc; a3[n3].flags = GE_WRITE; args[n3++] = d0;
+        strcat(expr, isf ? "o = ((r & 1) == 0) ? NAN : ((b == 0) ? ((r & 2) ? -fabs(b) : fabs(b)) : b)"
+                         : "o = b");
+      }
+      if (d1 != NULL) {
+        a3[n3].name = "j"; a3[n3].typecode = d1->typecode; a3[n3].flags = GE_WRITE; args[n3++] = d1;
+        strcat(expr, d0 != NULL ? "; j = r >> 2" : "j = r >> 2");
+      }
+      if (gr->sh_e3 != NULL && gr->sh_e3_key != key) {
+        GpuElemwise_free(gr->sh_e3);
+        gr->sh_e3 = NULL;
+      }
+      err = sh_elemwise(ctx, &gr->sh_e3, expr, n3, a3, half);
+      if (err != GA_NO_ERROR) goto done;
+      gr->sh_e3_key = key;
+      err = GpuElemwise_call(gr->sh_e3, args, 0);
+    }
+  }
+done:
+#undef SH_TMP
+  {
+    GpuArray *tmp[5] = {&v, &i, &w, &p, &c};
+    for (k = 0; k < 5; k++)
+      if (have[k]) GpuArray_clear(tmp[k]);
+  }
+  return err;
+}
+
+int GpuReduction_call_sharded(const GpuReduction *cgr, gpucomm *comm, GpuArray *d0, GpuArray *d1,
+                              const GpuArray *s0, unsigned reduxLen, const int *reduxList,
+                              int shard_axis, size_t shard_lo, size_t shard_global, int flags) {
+  GpuReduction *gr = (GpuReduction *)cgr;
+  gpucontext *ctx;
+  rd_shard sh;
+  int err, opcode;
+  if (gr == NULL) return GA_INVALID_ERROR;
+  ctx = gr->ctx;
+  if (s0 == NULL) return ga_err_set(ctx->err, GA_INVALID_ERROR, "Source array is NULL");
+  if (shard_axis < 0 || (unsigned)shard_axis >= s0->nd)
+    return ga_err_set(ctx->err, GA_VALUE_ERROR, "The sharded axis is out of range");
+  sh.axis = shard_axis;
+  sh.lo = shard_lo;
+  sh.global = shard_global;
+  if (gr->kind == 1) {
+    if (!op_writes_val(gr->op)) d0 = NULL;
+    if (!op_writes_idx(gr->op)) d1 = NULL;
+    if (d0 == NULL && d1 == NULL)
+      return ga_err_set(ctx->err, GA_INVALID_ERROR, "Destination is NULL");
+    if ((op_writes_val(gr->op) && d0 == NULL) || (op_writes_idx(gr->op) && d1 == NULL))
+      return ga_err_set(ctx->err, GA_INVALID_ERROR, "Destination is NULL");
+    return sharded_pair(gr, comm, d0, d1, s0, reduxLen, reduxList, &sh);
+  }
+  /* accumulating operators: per-GPU partial of the final shape, ONE all-reduce */
+  switch (gr->op) {
+  case GA_REDUCE_SUM: opcode = GA_SUM; break;
+  case GA_REDUCE_PROD: case GA_REDUCE_PRODNZ: opcode = GA_PROD; break;
+  case GA_REDUCE_ALL: opcode = GA_MIN; break; /* destinations hold 0 / 1 */
+  case GA_REDUCE_ANY: opcode = GA_MAX; break;
+  default:
+    return ga_err_set(ctx->err, GA_UNSUPPORTED_ERROR,
+                      "Bitwise reductions cannot be combined across GPUs: the collectives offer "
+                      "sum, prod, min and max only");
+  }
+  if (d0 == NULL) return ga_err_set(ctx->err, GA_INVALID_ERROR, "Value destination is NULL");
+  {
+    GpuArray tmp, view;
+    GpuArray *part = d0;
+    int use_tmp = !(GpuArray_IS_C_CONTIGUOUS(d0) || GpuArray_IS_F_CONTIGUOUS(d0));
+    if (use_tmp) {
+      err = GpuArray_empty(&tmp, ctx, d0->typecode, d0->nd, d0->dimensions, GA_C_ORDER);
+      if (err != GA_NO_ERROR) return err;
+      part = &tmp;
+    }
+    err = rd_call(gr, part, NULL, s0, reduxLen, reduxList, flags, &sh);
+    if (err == GA_NO_ERROR && comm != NULL) {
+      if (part->typecode == GA_BOOL) { /* the collectives know no bool: same bytes as unsigned */
+        err = GpuArray_view(&view, part);
+        if (err == GA_NO_ERROR) {
+          view.typecode = GA_UBYTE;
+          err = GpuArray_all_reduce(&view, &view, opcode, comm);
+          GpuArray_clear(&view);
+        }
+      } else {
+        err = GpuArray_all_reduce(part, part, opcode, comm);
+      }
+    }
+    if (err == GA_NO_ERROR && use_tmp) err = GpuArray_move(d0, &tmp);
+    if (use_tmp) GpuArray_clear(&tmp);
+  }
+  return err;
 }
 
 /* ------------------------------------------------- GpuArray_maxandargmax */

@@ -167,6 +167,17 @@ static __device__ __forceinline__ ga_half atom_xchg_eg(ga_half *p, ga_half v) {
  * first access to global memory, which then waits until the predecessor has
  * completed and its writes are visible. Releasing right after lets the
  * successor do the same with us. Both are no-ops under an ordinary launch. */
+/* Asks the memory system to bring [p, p + bytes) into L2 (p 16-byte aligned,
+ * bytes a multiple of 16). A hint without architectural effect: nothing is
+ * loaded into registers or L1, and L2 is the point of coherence, so issuing it
+ * BEFORE ga__grid_dependency_sync() is safe even when the previous kernel of
+ * the stream is still writing the very same lines - the loads that follow the
+ * wait see its data. It lets a kernel's first DRAM reads overlap the tail of
+ * its predecessor. */
+static __device__ __forceinline__ void ga__prefetch_l2(const void *p, unsigned int bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 static __device__ __forceinline__ void ga__grid_dependency_sync() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

@@ -57,8 +57,22 @@
 #ifndef GA_RD_ONERUN
 #define GA_RD_ONERUN 0 /* rows: every output is one short contiguous run and nothing is split */
 #endif
+#ifndef GA_RD_SIMPLE
+#define GA_RD_SIMPLE 0 /* rows: every output is ONE contiguous run owned by one warp, nothing is
+                          split, fewer than 2^32 outputs: a lean loop with 32-bit indices */
+#endif
+#ifndef GA_RD_UNROLL
+#define GA_RD_UNROLL 8 /* vectors a thread has in flight in the streaming loops */
+#endif
+#ifndef GA_RD_MINB
+#define GA_RD_MINB 0 /* rows, cols: CTAs per SM the register allocation must leave room for
+                        (0 = no constraint). Small grids ask for twice their own residency so
+                        that the NEXT launch of the stream finds free slots while this one runs
+                        (programmatic dependent launch). */
+#endif
 
 #define GA_RD_MAXD 8
+static constexpr int ga__rd_unroll = GA_RD_UNROLL; /* `#pragma unroll` takes a constant, not a macro */
 typedef unsigned long long ga__u64;
 typedef long long ga__i64;
 
@@ -81,6 +95,13 @@ struct ga__rd_layout {
   ga__u64 units;             /* rows: units per output */
   ga__u64 tiles;             /* cols: column tiles per contiguous kept run */
   unsigned int dv[4];        /* rows: divisor, multiplier, shifts for idx / (inner / VEC) */
+  ga__u64 ioff;              /* added to every flat index written (a shard's offset in the
+                                whole reduced extent; 0 otherwise) */
+  ga__u64 early;             /* cols: reduced positions whose tile row a row lane asks into L2
+                                before waiting for the previous kernel (0 = none) */
+  ga__u64 nan_first;         /* 1: a NaN in the first reduced element is the result (the
+                                reference's rule); 0 for a shard that does not hold the first
+                                element of the whole reduced extent */
 };
 
 /* exact n / d for 32-bit n with the constants the host derived from d */
@@ -211,7 +232,7 @@ static __device__ __forceinline__ void ga__emit(const ga__rd_layout &L, const ch
   {
     const GA_RD_SRC_T raw = *reinterpret_cast<const GA_RD_SRC_T *>(src + ga__foff(L, L.fsrc, o));
     const GA_RD_X_T first = GA_RD_LOAD(raw);
-    if (first != first) {
+    if (L.nan_first != 0 && first != first) {
       s.v = first;
       s.i = 0;
     }
@@ -221,7 +242,9 @@ static __device__ __forceinline__ void ga__emit(const ga__rd_layout &L, const ch
   *reinterpret_cast<GA_RD_DST_T *>(d0 + ga__foff(L, L.fdst0, o)) = GA_RD_STORE(s.v);
 #endif
 #if GA_RD_KIND == 1 && GA_RD_WRITE_IDX
-  *reinterpret_cast<ga__i64 *>(d1 + ga__foff(L, L.fdst1, o)) = (ga__i64)s.i;
+  /* "no element" (a shard of NaNs only) stays all-ones whatever the offset */
+  *reinterpret_cast<ga__u64 *>(d1 + ga__foff(L, L.fdst1, o)) =
+      (s.i == GA__IDX_NONE) ? ~(ga__u64)0 : (ga__u64)s.i + L.ioff;
 #endif
 }
 
@@ -421,7 +444,9 @@ static __device__ __forceinline__ void ga__row_decode(const ga__rd_layout &L, co
  * be part of a warp (GA_RD_GROUP = 1..32 lanes, sized so that a lane still
  * sees about two vectors of the run) and has each group work on GA_RD_MU
  * outputs at once, one accumulator per output. */
-#if GA_RD_MU > 1
+#if GA_RD_MINB > 0
+#define GA__RD_ROWS_BOUNDS __launch_bounds__(GA_RD_THREADS, GA_RD_MINB)
+#elif GA_RD_MU > 1
 #define GA__RD_ROWS_BOUNDS __launch_bounds__(GA_RD_THREADS, 3) /* room for the extra loads in flight */
 #else
 #define GA__RD_ROWS_BOUNDS __launch_bounds__(GA_RD_THREADS)
@@ -442,7 +467,39 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
   const ga__u64 ngroups = (ga__u64)gridDim.x * (GA_RD_THREADS / GA_RD_GROUP);
   const ga__u64 rounds = (nwork + ngroups - 1) / ngroups;
 
-#if GA_RD_ONERUN
+#if GA_RD_SIMPLE
+  /* A warp per output, one contiguous run each, nothing split. Few live values besides
+   * the vectors in flight: the kernel needs about half the registers of the general
+   * loop below, so the CTAs of the NEXT launch of the stream find room to become
+   * resident while this grid still runs (they wait in ga__grid_dependency_sync) and
+   * start the moment it completes. */
+  {
+    const unsigned int nout = (unsigned int)L.nf_total;
+    const unsigned int len = (unsigned int)L.inner, nv = len / GA_RD_VEC;
+    const unsigned int wl = threadIdx.x & 31u;
+    const unsigned int nwarps = gridDim.x * (GA_RD_THREADS / 32);
+    for (unsigned int o = blockIdx.x * (GA_RD_THREADS / 32) + (threadIdx.x >> 5); o < nout;
+         o += nwarps) {
+      const char *base = src + ga__foff(L, L.fsrc, o);
+      const ga__rd_pack<GA_RD_VEC> *pv = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(base);
+      ga__state st[GA_RD_VEC];
+#pragma unroll
+      for (int j = 0; j < GA_RD_VEC; j++) st[j] = ga__init();
+#pragma unroll ga__rd_unroll
+      for (unsigned int i = wl; i < nv; i += 32) {
+        const ga__rd_pack<GA_RD_VEC> t = pv[i];
+        ga__fold_lanes(st, t, (GA_RD_IDX_T)(i * GA_RD_VEC) * imul, imul);
+      }
+      for (unsigned int i = nv * GA_RD_VEC + wl; i < len; i += 32)
+        ga__take(st[0], GA_RD_LOAD(reinterpret_cast<const GA_RD_SRC_T *>(base)[i]),
+                 (GA_RD_IDX_T)i * imul);
+#pragma unroll
+      for (int j = 1; j < GA_RD_VEC; j++) ga__merge(st[0], st[j]);
+      const ga__state tot = ga__warp_reduce(st[0]);
+      if (wl == 0) ga__emit(L, src, d0, d1, o, tot);
+    }
+  }
+#elif GA_RD_ONERUN
   {
     const unsigned int len = (unsigned int)L.inner, nv = len / GA_RD_VEC;
     for (ga__u64 it = 0; it < rounds; it += GA_RD_MU) {
@@ -566,7 +623,7 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
         {
           GA_RD_X_T bv = (GA_RD_X_T)(GA_RD_IDENT);
           unsigned int bi = lane; /* where to look if nothing beats the identity */
-#pragma unroll 8
+#pragma unroll ga__rd_unroll
           for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
             const ga__rd_pack<GA_RD_VEC> t = pv[i];
             GA_RD_X_T m = GA_RD_LOAD(t.v[0]);
@@ -600,7 +657,7 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
           }
         }
 #else
-#pragma unroll 8
+#pragma unroll ga__rd_unroll
         for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
           const ga__rd_pack<GA_RD_VEC> t = pv[i];
           ga__fold_lanes(st, t, fbase + (GA_RD_IDX_T)(i * GA_RD_VEC) * imul, imul);
@@ -687,9 +744,28 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
 
 /* ------------------------------------------------------------------ cols */
 #if defined(GA_RD_BUILD_COLS)
-extern "C" __global__ void __launch_bounds__(32 * GA_RD_BY)
+#if GA_RD_MINB > 0
+#define GA__RD_COLS_BOUNDS __launch_bounds__(32 * GA_RD_BY, GA_RD_MINB)
+#else
+#define GA__RD_COLS_BOUNDS __launch_bounds__(32 * GA_RD_BY)
+#endif
+extern "C" __global__ void GA__RD_COLS_BOUNDS
 ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, char *d1,
            GA_RD_ACC_T *pval, GA_RD_IDX_T *pidx, unsigned int *tickets) {
+  if (L.early != 0 && threadIdx.x == 0 && blockIdx.x < L.tiles) {
+    /* The first rows this row lane will walk, for the CTA's first column tile (only when
+     * there is one reduced dimension and no outer kept position: the host sets `early`).
+     * An L2 hint, issued before the wait so that the first DRAM reads overlap the
+     * previous kernel's tail (see ga__prefetch_l2). */
+    const ga__u64 c0 = (ga__u64)blockIdx.x * 32 * GA_RD_VEC;
+    const ga__u64 left = L.inner - c0;
+    const unsigned int nb = (unsigned int)((left < 32 * GA_RD_VEC ? left : 32 * GA_RD_VEC) *
+                                           sizeof(GA_RD_SRC_T)) & ~15u;
+    const ga__u64 step = L.splits * GA_RD_BY;
+    ga__u64 j = (ga__u64)blockIdx.y * GA_RD_BY + threadIdx.y;
+    for (ga__u64 n = 0; n < L.early && j < L.nr_total && nb != 0; n++, j += step)
+      ga__prefetch_l2(src + (ga__i64)j * L.rsrc[0] + (ga__i64)(c0 * sizeof(GA_RD_SRC_T)), nb);
+  }
   ga__grid_dependency_sync();
   __shared__ ga__state sm[GA_RD_BY][GA_RD_VEC][32];
   __shared__ int sm_last;
@@ -741,7 +817,7 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
         GA_RD_IDX_T f = (GA_RD_IDX_T)j0 * (GA_RD_IDX_T)L.rmul[0];
         /* only the last block can be ragged */
         const unsigned int full = (cnt > 0 && j0 + (ga__u64)(cnt - 1) * jstep >= L.nr_total) ? cnt - 1 : cnt;
-#pragma unroll 8
+#pragma unroll ga__rd_unroll
         for (unsigned int n = 0; n < full; n++) {
           const ga__rd_pack<GA_RD_VEC> t = *reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(p);
 #pragma unroll

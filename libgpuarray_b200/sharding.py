@@ -85,3 +85,38 @@ def finish_minmaxarg(allreduce, local_val, local_global_idx, is_min=False):
         best = np.where(has_nan_first, np.array(np.nan, val.dtype), best)
         best_idx = np.where(has_nan_first, 0, best_idx)
     return best, best_idx
+
+
+def finish_minmaxarg_packed(allreduce, local_val, local_global_idx, is_min=False):
+    """The protocol GpuReduction_call_sharded runs on the device
+    (csrc/ga_reduction.c, sharded_pair), restated on the host so that it can be
+    tested over any all-reduce: TWO collectives instead of the three of
+    finish_minmaxarg. Every global index belongs to exactly one rank, so two
+    payload bits ride in the low bits of the candidate index and arrive with
+    the winner: bit 0 "the value is not a NaN", bit 1 "the value is -0.0".
+    A NaN can only come from the rank holding element 0 (the other shards do
+    not apply the NaN-first rule) and is then the answer; it enters the value
+    all-reduce as the winning infinity. local_global_idx uses
+    18446744073709551615 (all ones) for "no element" (a shard of NaNs only)."""
+    val = np.ascontiguousarray(local_val)
+    idx = np.ascontiguousarray(local_global_idx).astype(np.uint64)
+    none = np.uint64(0xFFFFFFFFFFFFFFFF)
+    if val.dtype.kind == "f":
+        nan = np.isnan(val)
+        work = np.where(nan, np.array(-np.inf if is_min else np.inf, val.dtype), val)
+        pay = np.where(nan, 0, 1).astype(np.uint64) | \
+            np.where((val == 0) & np.signbit(val), 2, 0).astype(np.uint64)
+    else:
+        work = val
+        pay = np.ones(val.shape, np.uint64)
+    best = allreduce(work.copy(), "min" if is_min else "max")
+    cand = np.where((work == best) & (idx != none), (idx << np.uint64(2)) | pay, none)
+    r = allreduce(cand, "min")
+    out_idx = (r >> np.uint64(2)).astype(np.int64)
+    if val.dtype.kind == "f":
+        out_val = np.where((r & np.uint64(1)) == 0, np.array(np.nan, val.dtype),
+                           np.where(best == 0, np.where((r & np.uint64(2)) != 0, -np.abs(best), np.abs(best)),
+                                    best)).astype(val.dtype)
+    else:
+        out_val = best
+    return out_val, out_idx

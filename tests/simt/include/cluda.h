@@ -38,4 +38,5 @@ static inline ga_half ga_float2half(float f) {
 }
 
 static inline void ga__grid_dependency_sync() {}
+static inline void ga__prefetch_l2(const void *, unsigned int) {}
 #endif

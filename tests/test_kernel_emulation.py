@@ -22,7 +22,7 @@ SIMT = os.path.join(ROOT, "tests", "simt")
 TEMPLATES = os.path.join(ROOT, "libgpuarray_b200", "csrc", "templates")
 BUILD = os.path.join(ROOT, "libgpuarray_b200", "build", "simt")
 KEYS = ["shape", "vec", "group", "flat", "mu", "onerun", "lazy", "fast8", "tpo", "idx64", "splits",
-        "seg", "nseg", "units", "gx", "gy", "bx", "by", "nf", "nr"]
+        "seg", "nseg", "units", "gx", "gy", "bx", "by", "nf", "nr", "simple"]
 ENTRY = ["ga_rd_rows", "ga_rd_cols", "ga_rd_general"]
 
 LAUNCHER = r'''
@@ -47,7 +47,7 @@ def plan_and_layout(api, op, x, axes, dst_dtype, sms):
     fn = L.gpuarray_b200_reduction_layout
     fn.restype = ctypes.c_int
     nd = x.ndim
-    out = (ctypes.c_ulonglong * 20)()
+    out = (ctypes.c_ulonglong * 24)()
     layout = ctypes.create_string_buffer(4096)
     used = ctypes.c_size_t()
     err = fn(getattr(api, "GA_REDUCE_" + op), api.typecode(x.dtype), api.typecode(np.dtype(dst_dtype)),
@@ -61,7 +61,8 @@ def plan_and_layout(api, op, x, axes, dst_dtype, sms):
 def build_variant(api, op, x, dst_dtype, p):
     L = api.lib()
     L.gpuarray_b200_reduction_source.restype = ctypes.c_void_p
-    group = p["group"] | (p["mu"] << 16) | (p["onerun"] << 20) | (p["flat"] << 21)
+    group = p["group"] | (p["mu"] << 16) | (p["onerun"] << 20) | (p["flat"] << 21) | \
+        (p.get("simple", 0) << 22) | ((p["by"] if p["shape"] == 1 else 0) << 24)
     ptr = L.gpuarray_b200_reduction_source(getattr(api, "GA_REDUCE_" + op), api.typecode(x.dtype),
                                            api.typecode(np.dtype(dst_dtype)), p["shape"], p["vec"],
                                            p["idx64"], p["tpo"], group)

@@ -23,6 +23,9 @@ def _ngpus():
 
 
 def _worker(rank, world, q_id, q_err):
+    """Every collective is enqueued BEFORE anything is checked: a rank that
+    failed an assertion between two collectives would leave its peer's NCCL
+    kernel waiting on the GPU for a rank that has already left."""
     try:
         os.environ["NCCL_NVLS_ENABLE"] = "0"
         from libgpuarray_b200 import api, sharding
@@ -35,73 +38,111 @@ def _worker(rank, world, q_id, q_err):
         else:
             cid = q_id.get(timeout=120)
         comm = api.GpuComm(ctx, cid, world, rank)
-
-        def allreduce(arr, op):
-            src = api.GpuArray.from_numpy(ctx, arr)
-            dst = api.GpuArray.empty(ctx, arr.shape, arr.dtype)
-            comm.all_reduce(src, dst, {"sum": api.GA_SUM, "prod": api.GA_PROD,
-                                       "max": api.GA_MAX, "min": api.GA_MIN}[op])
-            return dst.to_numpy()
+        got = {}
 
         rng = np.random.default_rng(11)
         x = (2 * rng.random((64, 48, 256)) - 1)                  # fp64, same on both ranks
         lo, hi = sharding.shard_bounds(x.shape[0], world, rank)
         g = api.GpuArray.from_numpy(ctx, x[lo:hi])
 
-        # SUM over everything: per-GPU partial + one all-reduce
+        # SUM over everything, MIN / MAX over axes (0, 2): per-GPU partial + one all-reduce,
+        # through the sharded entry point of the C API
         d = api.GpuArray.empty(ctx, (), np.float64)
-        api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.float64)(d, None, g, [0, 1, 2])
-        tot = sharding.finish_accumulate(allreduce, d.to_numpy().reshape(1), "sum")[0]
-        ref = float(np.sum(x.astype(np.longdouble)))
-        assert abs(tot - ref) <= 1e-12 * np.log2(x.size) * np.abs(x).sum()
-
-        # MIN / MAX over axes (0, 2)
-        for name, op, red in (("min", api.GA_REDUCE_MIN, "min"), ("max", api.GA_REDUCE_MAX, "max")):
+        api.reduction_call_sharded(api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.float64), comm, d, None,
+                                   g, [0, 1, 2], lo, 64)
+        got["sum"] = d
+        for name, op in (("min", api.GA_REDUCE_MIN), ("max", api.GA_REDUCE_MAX)):
             dk = api.GpuArray.empty(ctx, (48,), np.float64)
-            api.GpuReduction(ctx, op, np.float64)(dk, None, g, [0, 2])
-            out = sharding.finish_accumulate(allreduce, dk.to_numpy(), red)
-            want = x.min(axis=(0, 2)) if name == "min" else x.max(axis=(0, 2))
-            assert (out == want).all()
+            api.reduction_call_sharded(api.GpuReduction(ctx, op, np.float64), comm, dk, None, g, [0, 2],
+                                       lo, 64)
+            got[name] = dk
 
-        # MAXANDARGMAX over (0, 2) with ties: lowest global index wins
+        # (value, first global index) over (0, 2) and (2, 0) with ties, a NaN as the first
+        # element of the whole extent, a NaN at the start of the second slab, signed zeros
         xt = np.round(x * 8) / 8
+        xt[0, 3, 0] = np.nan
+        xt[32, 4, 0] = np.nan
+        xt[:, 6, :] = -1.0
+        xt[40, 6, 3] = -0.0
+        xt[10, 6, 200] = 0.0
         gt = api.GpuArray.from_numpy(ctx, xt[lo:hi])
-        v = api.GpuArray.empty(ctx, (48,), np.float64)
-        i = api.GpuArray.empty(ctx, (48,), np.int64)
-        api.GpuReduction(ctx, api.GA_REDUCE_MAXANDARGMAX, np.float64)(v, i, gt, [0, 2])
-        gi = sharding.global_flat_index(i.to_numpy(), lo, hi - lo, 0, [64, 256])
-        bv, bi = sharding.finish_minmaxarg(allreduce, v.to_numpy(), gi)
-        wv, wi = O.minmaxarg(xt, [0, 2])
-        assert (bv == wv).all() and (bi == wi).all()
-        # the other collectives of the reference's interface
-        # (src/gpuarray/collectives.h): reduce to a root, reduce-scatter,
-        # broadcast, all-gather
+        for tag, opname, axes in (("maxarg02", "MAXANDARGMAX", [0, 2]), ("minarg20", "MINANDARGMIN", [2, 0])):
+            v = api.GpuArray.empty(ctx, (48,), np.float64)
+            i = api.GpuArray.empty(ctx, (48,), np.int64)
+            api.reduction_call_sharded(api.GpuReduction(ctx, getattr(api, "GA_REDUCE_" + opname), np.float64),
+                                       comm, v, i, gt, axes, lo, 64, shard_axis=0)
+            got[tag] = (v, i)
+
+        # the other collectives of the reference's interface (src/gpuarray/collectives.h):
+        # reduce to a root, reduce-scatter, broadcast, all-gather
         a = np.arange(6 * world, dtype=np.float32).reshape(world, 6) + 100 * rank
         ga = api.GpuArray.from_numpy(ctx, a)
-        if rank == 1:
-            res = api.GpuArray.empty(ctx, a.shape, np.float32)
-            comm.reduce(ga, res, api.GA_SUM, 1)
-            want = sum(np.arange(6 * world, dtype=np.float32).reshape(world, 6) + 100 * r
-                       for r in range(world))
-            assert (res.to_numpy() == want).all()
-        else:
-            comm.reduce(ga, None, api.GA_SUM, 1)
+        res = api.GpuArray.empty(ctx, a.shape, np.float32)
+        comm.reduce(ga, res if rank == 1 else None, api.GA_SUM, 1)
         part = api.GpuArray.empty(ctx, (6,), np.float32)
         comm.reduce_scatter(ga, part, api.GA_MAX)
-        assert (part.to_numpy() == a[rank] - 100 * rank + 100 * (world - 1)).all()
         b = api.GpuArray.from_numpy(ctx, np.full(5, rank + 7, np.int32))
         comm.broadcast(b, 0)
-        assert (b.to_numpy() == 7).all()
         mine = api.GpuArray.from_numpy(ctx, np.full(3, rank, np.int64))
         everyone = api.GpuArray.empty(ctx, (world, 3), np.int64)
         comm.all_gather(mine, everyone)
-        assert (everyone.to_numpy() == np.arange(world)[:, None]).all()
         ctx.sync()
+
+        # ---- nothing below enqueues a collective
+        tot = float(got["sum"].to_numpy())
+        ref = float(np.sum(x.astype(np.longdouble)))
+        assert abs(tot - ref) <= 1e-12 * np.log2(x.size) * np.abs(x).sum()
+        assert (got["min"].to_numpy() == x.min(axis=(0, 2))).all()
+        assert (got["max"].to_numpy() == x.max(axis=(0, 2))).all()
+        for tag, is_min, axes in (("maxarg02", False, [0, 2]), ("minarg20", True, [2, 0])):
+            bv, bi = got[tag][0].to_numpy(), got[tag][1].to_numpy()
+            wv, wi = O.minmaxarg(xt, axes, is_min=is_min)
+            assert (bi == wi).all(), (tag, bi, wi)
+            nan = np.isnan(wv)
+            assert (np.isnan(bv) == nan).all() and bv[~nan].tobytes() == wv[~nan].tobytes(), tag
+        if rank == 1:
+            want = sum(np.arange(6 * world, dtype=np.float32).reshape(world, 6) + 100 * r
+                       for r in range(world))
+            assert (res.to_numpy() == want).all()
+        assert (part.to_numpy() == a[rank] - 100 * rank + 100 * (world - 1)).all()
+        assert (b.to_numpy() == 7).all()
+        assert (everyone.to_numpy() == np.arange(world)[:, None]).all()
         comm.free()
         ctx.close()
     except Exception as e:
         import traceback
         q_err.put("rank %d: %s\n%s" % (rank, e, traceback.format_exc()))
+
+
+def _transfer_worker(q_err):
+    """One process, two contexts: a cross-GPU transfer followed at once by an
+    overwrite and a release of the source. The copy is ordered on both streams
+    with events (ga_context.c, gpudata_transfer), so it must carry the old
+    contents."""
+    try:
+        import ctypes
+        from libgpuarray_b200 import api
+        c0 = api.Context(0, kernel_cache=os.path.join(ROOT, ".kernel_cache"))
+        c1 = api.Context(1, kernel_cache=os.path.join(ROOT, ".kernel_cache"))
+        L = api.lib()
+        L.GpuArray_transfer.restype = ctypes.c_int
+        L.GpuArray_transfer.argtypes = [ctypes.POINTER(api._GpuArrayStruct), ctypes.POINTER(api._GpuArrayStruct)]
+        n = 1 << 26                                              # 256 MiB: the copy takes a while
+        for rep in range(3):
+            src = api.GpuArray.from_numpy(c0, np.full(n, rep + 1, np.float32))
+            dst = api.GpuArray.empty(c1, (n,), np.float32)
+            assert L.GpuArray_transfer(ctypes.byref(dst.ga), ctypes.byref(src.ga)) == 0
+            src.memset(0)                                        # overwrite ...
+            src.clear()                                          # ... and release the source at once
+            again = api.GpuArray.empty(c0, (n,), np.float32)     # the freed block is handed out again
+            again.memset(0xFF)
+            out = dst.to_numpy()
+            assert (out == rep + 1).all(), (rep, out[:4], out[-4:])
+        c0.close()
+        c1.close()
+    except Exception as e:
+        import traceback
+        q_err.put("transfer: %s\n%s" % (e, traceback.format_exc()))
 
 
 @pytest.mark.skipif(_ngpus() < 2, reason="needs two GPUs")
@@ -114,7 +155,7 @@ def test_sharded_reduction_with_gpucomm():
     for p in procs:
         p.start()
     for p in procs:
-        p.join(timeout=300)
+        p.join(timeout=180)
     hung = [p for p in procs if p.is_alive()]
     for p in hung:
         p.kill()
@@ -124,3 +165,21 @@ def test_sharded_reduction_with_gpucomm():
     assert not hung, "rank hung"
     assert not msgs, "\n".join(msgs)
     assert all(p.exitcode == 0 for p in procs)
+
+
+@pytest.mark.skipif(_ngpus() < 2, reason="needs two GPUs")
+def test_cross_gpu_transfer_is_ordered_on_both_streams():
+    import torch.multiprocessing as mp
+    m = mp.get_context("spawn")
+    q_err = m.Queue()
+    p = m.Process(target=_transfer_worker, args=(q_err,))
+    p.start()
+    p.join(timeout=180)
+    if p.is_alive():
+        p.kill()
+        pytest.fail("transfer worker hung")
+    msgs = []
+    while not q_err.empty():
+        msgs.append(q_err.get())
+    assert not msgs, "\n".join(msgs)
+    assert p.exitcode == 0

@@ -66,9 +66,9 @@ def test_reference_python_elemwise_tests(built):
 
 def test_pygpu_reductions_through_the_engine(built):
     """ndgpuarray.sum/prod/all/any with libgpuarray_b200.pygpu_compat installed, and
-    the reference's pygpu/tests/test_reduction.py on top of it. Two of its cases
-    cannot apply: the map-expression kernel (needs pygpu's mako template) and the
-    check that float16 raises NotImplementedError (float16 works here)."""
+    the reference's pygpu/tests/test_reduction.py on top of it, its map-expression
+    case with a broadcast operand (red_broadcast) included. One case cannot apply:
+    the check that float16 raises NotImplementedError (float16 works here)."""
     import ast
     import re
     r = run_driver(["--reductions", "pygpu.tests.test_reduction"])
@@ -76,6 +76,6 @@ def test_pygpu_reductions_through_the_engine(built):
     m = re.search(r"pass=(\d+) fail=(\d+) skip=(\d+)", r.stdout)
     names = dict(ast.literal_eval(re.search(r"FAILED_NAMES (.*)", r.stdout).group(1)))
     print(r.stdout[-1500:])
-    unexpected = {k: v for k, v in names.items() if k not in ("red_broadcast", "test_reduction_f16")}
+    unexpected = {k: v for k, v in names.items() if k != "test_reduction_f16"}
     assert not unexpected, r.stdout[-6000:]
     assert int(m.group(1)) >= 150

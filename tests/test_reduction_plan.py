@@ -9,7 +9,7 @@ import pytest
 
 SHAPE_ROWS, SHAPE_COLS, SHAPE_GENERAL = 0, 1, 2
 KEYS = ["shape", "vec", "group", "flat", "mu", "onerun", "lazy", "fast8", "tpo", "idx64", "splits",
-        "seg", "nseg", "units", "gx", "gy", "bx", "by", "nf", "nr"]
+        "seg", "nseg", "units", "gx", "gy", "bx", "by", "nf", "nr", "simple"]
 
 
 def plan(api, op, dt, dims, strides, axes, base=0x7f0000000000, sms=148, dst=None):
@@ -21,7 +21,7 @@ def plan(api, op, dt, dims, strides, axes, base=0x7f0000000000, sms=148, dst=Non
                    ctypes.POINTER(ctypes.c_int), ctypes.c_ulonglong, ctypes.c_uint,
                    ctypes.POINTER(ctypes.c_ulonglong)]
     nd = len(dims)
-    out = (ctypes.c_ulonglong * 20)()
+    out = (ctypes.c_ulonglong * 24)()
     tc = api.typecode(np.dtype(dt))
     dtc = api.typecode(np.dtype(dst)) if dst is not None else tc
     err = fn(getattr(api, "GA_REDUCE_" + op), tc, dtc, nd, (ctypes.c_size_t * nd)(*dims),
@@ -71,8 +71,10 @@ def test_named_configurations_get_the_intended_kernels(api):
     # cfg2: rows and columns
     err, p = plan(api, "SUM", np.float32, [4096, 4096], c_strides([4096, 4096], 4), [1])
     assert err == 0 and p["shape"] == SHAPE_ROWS and p["splits"] == 1 and p["gx"] == 512
+    assert p["simple"] == 1                      # one run per output, a warp each: the lean loop
     err, p = plan(api, "SUM", np.float32, [4096, 4096], c_strides([4096, 4096], 4), [0])
-    assert err == 0 and p["shape"] == SHAPE_COLS and p["gx"] == 32 and p["splits"] == 14
+    # 16 row lanes x 16 splits: every thread walks 16 rows, the grid is resident at once
+    assert err == 0 and p["shape"] == SHAPE_COLS and p["gx"] == 32 and p["splits"] == 16 and p["by"] == 16
     # cfg5: full sum by CTA groups, 4 per SM; MIN over (0, 2) by warps with shares >= 24 KiB
     dims = [2048, 1024, 1024]
     err, p = plan(api, "SUM", np.float64, dims, c_strides(dims, 8), [0, 1, 2])

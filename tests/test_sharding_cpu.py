@@ -26,7 +26,12 @@ def _free_port():
 
 
 def _allreduce(arr, op):
-    t = torch.from_numpy(np.ascontiguousarray(arr).copy())
+    arr = np.ascontiguousarray(arr)
+    if arr.dtype == np.uint64:
+        # gloo has no unsigned 64-bit type: flipping the top bit maps uint64 order onto int64 order
+        flip = np.uint64(1 << 63)
+        return _allreduce((arr ^ flip).view(np.int64), op).view(np.uint64) ^ flip
+    t = torch.from_numpy(arr.copy())
     dist.all_reduce(t, op={"sum": dist.ReduceOp.SUM, "prod": dist.ReduceOp.PRODUCT,
                            "min": dist.ReduceOp.MIN, "max": dist.ReduceOp.MAX}[op])
     return t.numpy()
@@ -76,6 +81,39 @@ def _worker(rank, world, port, errors):
                 assert bv.tobytes() == wv.tobytes() or \
                     (np.isnan(bv) == np.isnan(wv)).all() and \
                     (bv[~np.isnan(bv)] == wv[~np.isnan(wv)]).all()
+
+        # the two-collective protocol of GpuReduction_call_sharded (payload bits in the
+        # candidate index). Local results as the device kernel gives them: global flat
+        # indices, the NaN-first rule only on the shard that holds element 0, all-ones for
+        # "no element".
+        z = x.copy()
+        z[:, 4, :] = -1.0
+        z[7, 4, 2] = -0.0                            # first zero is negative ...
+        z[9, 4, 5] = 0.0                             # ... a positive one follows (another rank at world 3)
+        z[6, 0, 0] = np.nan                          # NaN at the start of a later slab: not a result
+        none = np.uint64(0xFFFFFFFFFFFFFFFF)
+        for axes, pos in (([0, 2], 0), ([2, 0], 1)):
+            for is_min in (False, True):
+                zz = -z if is_min else z
+                sl = zz[lo:hi]
+                if hi > lo:
+                    ident = np.float32(np.inf if is_min else -np.inf)
+                    loc = sl if lo == 0 else np.where(np.isnan(sl), ident, sl)
+                    lv, li = O.minmaxarg(loc, axes, is_min=is_min)
+                    redux = [zz.shape[a] for a in axes]
+                    lgi = sharding.global_flat_index(li, lo, hi - lo, pos, redux).astype(np.uint64)
+                    if lo != 0:                      # a shard of NaNs only has no element to offer
+                        allnan = np.isnan(sl).all(axis=(0, 2))
+                        lgi = np.where(allnan, none, lgi)
+                else:
+                    lv = np.full(5, np.inf if is_min else -np.inf, np.float32)
+                    lgi = np.full(5, none, np.uint64)
+                bv, bi = sharding.finish_minmaxarg_packed(_allreduce, lv, lgi, is_min=is_min)
+                wv, wi = O.minmaxarg(zz, axes, is_min=is_min)
+                assert (bi == wi).all(), (axes, is_min, bi, wi)
+                nanmask = np.isnan(wv)
+                assert (np.isnan(bv) == nanmask).all()
+                assert bv[~nanmask].tobytes() == wv[~nanmask].tobytes(), (axes, is_min, bv, wv)
         dist.destroy_process_group()
     except Exception as e:                           # surfaces in the parent
         import traceback
