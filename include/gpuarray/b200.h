@@ -70,7 +70,9 @@ GPUARRAY_PUBLIC int gpuarray_b200_elemwise_shapes(unsigned int n, const gpuelemw
  * extents, byte strides and the address of their first element (alignment only).
  * obj_flags as for GpuElemwise_new, call_flags as for GpuElemwise_call.
  * out[0..15] = kernel (0 contiguous, 1 strided, 2 tiled transpose), elements per
- * thread chunk, chunks in flight, rank after collapsing, index width bits, access
+ * thread chunk, chunks in flight (tiled transpose: 2 marks the build that stages
+ * with 16-byte asynchronous copies and reads back with transposing matrix
+ * loads, 1 the word-staged build), rank after collapsing, index width bits, access
  * modes (2 bits per array argument: 0 gather, 1 vector, 2 broadcast, 3 staged
  * through shared memory), tile P, tile Q, P positions per thread, grid x/y/z,
  * block x/y/z, element count. blob_out (may be NULL) receives the layout

@@ -120,9 +120,10 @@ static void gen_prologue(const GpuElemwise *ge, ga_strb *sb, const ew_variant *v
                  v->ept, v->unroll, GA_EW_THREADS, v->idx32 ? "unsigned int" : "size_t",
                  v->idx32 & 1, (v->idx32 >> 1) & 1, v->nd ? v->nd : 1,
                  ge->narray ? ge->narray : 1);
-  if (v->kind == 2)
-    ga_strb_printf(sb, "#define GA_EW_TP %d\n#define GA_EW_TQ %d\n#define GA_EW_PWI %d\n", v->tp,
-                   v->tq, v->pwi > 0 ? v->pwi : 1);
+  if (v->kind == 2) /* unroll == 2 marks the cp.async + ldmatrix build of the tiled transpose */
+    ga_strb_printf(sb, "#define GA_EW_TP %d\n#define GA_EW_TQ %d\n#define GA_EW_PWI %d\n"
+                       "#define GA_EW_LDSM %d\n", v->tp, v->tq,
+                   v->unroll == 2 ? 1 : (v->pwi > 0 ? v->pwi : 1), v->unroll == 2 ? 1 : 0);
 
   /* The expression sees each argument as a scalar variable of its own name. */
   ga_strb_puts(sb, "static __device__ __forceinline__ void ga_ew_apply(");
@@ -706,20 +707,32 @@ static int call_transpose(GpuElemwise *ge, void **args, size_t n, unsigned int n
    * the staged reads are long contiguous bursts; 64 along Q; shrink until the
    * staged tiles fit the 48 KiB of static shared memory. */
   {
-    int tp = 32, tq = 64, tpmax = 256;
+    int tp = 32, tq = 64, tpmax = 256, ldsm = want.ept == 8 && getenv("GPUARRAY_B200_NO_LDSM") == NULL;
     /* measured on B200: 256 x 64 for 2-byte staged elements (cfg4: 35.8 us,
      * 128 x 64: 38.3); 128 x 32 for 4 bytes and more (fp32 8192 x 4096
      * transpose: 49.0 us, 128 x 64: 53.2) */
     for (i = 0, k = 0; i < ge->n; i++) {
       if (!is_array(&ge->args[i])) continue;
-      if (((want.modes >> (2 * k)) & 3) == 3 && gpuarray_get_elsize(ge->args[i].typecode) >= 4) {
-        tpmax = 128;
-        tq = 32;
+      if (((want.modes >> (2 * k)) & 3) == 3) {
+        if (gpuarray_get_elsize(ge->args[i].typecode) >= 4) {
+          tpmax = 128;
+          tq = 32;
+        }
+        if (gpuarray_get_elsize(ge->args[i].typecode) != 2) ldsm = 0;
       }
       k++;
     }
     if (tq < want.ept) tq = want.ept;
     while (tp < tpmax && (size_t)tp < ge->dims[pdim_ax]) tp *= 2;
+    /* Every staged input has 2-byte elements: asynchronous 16-byte copies into swizzled
+     * rows and transposing matrix loads (ga_ew_transpose.cuh, GA_EW_LDSM). Tiles of
+     * 256 x 32: measured on B200 (cfg4, one tile per CTA) 32.4 us against 33.1 us for
+     * 256 x 64, and 36.1 us for the word-staged build. */
+    if (ldsm && tp >= 64) {
+      tq = 32;
+      want.unroll = 2;
+      want.pwi = 1;
+    }
     for (;;) {
       smem = 0;
       for (i = 0, k = 0; i < ge->n; i++) {
@@ -727,12 +740,13 @@ static int call_transpose(GpuElemwise *ge, void **args, size_t n, unsigned int n
         if (((want.modes >> (2 * k)) & 3) == 3) {
           size_t es = gpuarray_get_elsize(ge->args[i].typecode);
           size_t wsz = es > 4 ? 8 : 4, pw = es < 4 ? 4 / es : 1;
-          smem += (size_t)tq * ((size_t)tp / pw + 1) * wsz;
+          smem += want.unroll == 2 ? (size_t)tq * (size_t)tp * 2
+                                   : (size_t)tq * ((size_t)tp / pw + 1) * wsz;
         }
         k++;
       }
       if (smem <= 40 * 1024) break;
-      if (tp > 32) tp /= 2;
+      if (tp > (want.unroll == 2 ? 64 : 32)) tp /= 2;
       else if (tq > 32) tq /= 2;
       else break;
     }
@@ -746,7 +760,7 @@ static int call_transpose(GpuElemwise *ge, void **args, size_t n, unsigned int n
     const char *env = getenv("GPUARRAY_B200_EWT");
     int etp = 0, etq = 0;
     if (env != NULL && sscanf(env, "%d,%d", &etp, &etq) == 2 && etp >= 8 && etq >= want.ept &&
-        etq % want.ept == 0) {
+        etq % want.ept == 0 && (want.unroll != 2 || (etp % 64 == 0 && etq % 32 == 0))) {
       want.tp = etp;
       want.tq = etq;
     }

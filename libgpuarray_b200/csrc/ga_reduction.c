@@ -681,6 +681,10 @@ static int rd_plan(const rd_plan_in *in, rd_layout *L, rd_variant *want, unsigne
        * are slower than none. */
       if (L->nr == 1 && ko == 1 && (size_t)vec * elsize == 16 && rd_cols_early != 0)
         L->early = rd_cols_early;
+      /* the lean walk: one reduced dimension, one contiguous kept run, 32-bit counters */
+      if (rd_simple && L->nr == 1 && ko == 1 && L->nr_total < 0x7fffffffULL &&
+          L->inner < 0x7fffffffULL)
+        want->simple = 1;
     }
     L->splits = s ? s : 1;
     L->units = nwork; /* tickets: one per column tile */

@@ -178,6 +178,30 @@ static __device__ __forceinline__ void ga__prefetch_l2(const void *p, unsigned i
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
+/* 16 bytes from global to shared memory without passing through registers
+ * (both addresses 16-byte aligned); ga__cp_async_wait_all() waits for the
+ * calling thread's copies - a barrier then makes everyone's visible. */
+static __device__ __forceinline__ void ga__cp_async16(void *smem, const void *gmem) {
+  const unsigned int s = (unsigned int)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+static __device__ __forceinline__ void ga__cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+/* Four 8 x 8 matrices of 16-bit elements from shared memory, TRANSPOSED on the
+ * way: lanes 8m .. 8m+7 give the (16-byte aligned) addresses of the eight
+ * 16-byte rows of matrix m; lane i receives, in r[m], elements
+ * [2*(i%4)][i/4] (low half) and [2*(i%4)+1][i/4] (high half) of matrix m.
+ * Every lane of the warp must execute it. */
+static __device__ __forceinline__ void ga__ldsm_x4_trans(const void *row, unsigned int r[4]) {
+  const unsigned int s = (unsigned int)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s)
+               : "memory");
+}
+
 static __device__ __forceinline__ void ga__grid_dependency_sync() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

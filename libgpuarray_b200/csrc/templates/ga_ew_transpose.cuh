@@ -25,10 +25,25 @@
  *   2  input with stride 0 along Q: one scalar load per P position
  *   0  anything else: scalar access with its own strides
  *
+ * GA_EW_LDSM = 1 (every staged input has 2-byte elements, GA_EW_EPT == 8, TP a
+ * multiple of 64, TQ of 32): the tile goes to shared memory with 16-byte
+ * asynchronous copies (cp.async, no registers in between) into unpadded rows
+ * whose 16-byte chunks are XOR-swizzled by the row, and comes back with
+ * ldmatrix.x4.trans: one instruction hands a thread 8 consecutive Q positions
+ * of one P position, i.e. one 128-bit store. A warp covers 8 P positions x 32
+ * Q positions per step. Both the copies (8 lanes fill one 128-byte row
+ * segment) and the matrix loads (the 8 rows of a matrix are 8 distinct chunk
+ * columns) are free of bank conflicts.
+ *
  * Needs the definitions listed in ga_ew_contig.cuh plus GA_EW_ND (>= 2),
- * GA_EW_NARR, GA_EW_TP, GA_EW_TQ, GA_EW_PWI (P positions per thread).
+ * GA_EW_NARR, GA_EW_TP, GA_EW_TQ, GA_EW_PWI (P positions per thread; 1 with
+ * GA_EW_LDSM).
  */
 #include "ga_ew_common.cuh"
+
+#ifndef GA_EW_LDSM
+#define GA_EW_LDSM 0
+#endif
 
 #define GA_EWT_NOUT ((GA_EW_ND > 2) ? (GA_EW_ND - 2) : 1)
 
@@ -70,14 +85,64 @@ static __device__ __forceinline__ void ga__stage_map(const int i, int &q, int &v
 #define GA__ARG_ARR(k, n, S, C, R, W, M) n##_c[kk][e],
 #define GA__ARG_SC(n, T) n##_s,
 
+#if GA_EW_LDSM
+/* chunk swizzle of tile row q: the 8 rows one ldmatrix matrix takes (q = 8a + 2m + b for
+ * a = 0..3, b = 0..1, fixed m) get 8 different values */
+static __device__ __forceinline__ int ga__swz(const int q) { return (((q >> 3) & 3) << 1) | (q & 1); }
+#define GA__SMEM(k, n, S, C, R, W, M) \
+  alignas(128) __shared__ unsigned char n##_sm[(M == 3) ? GA_EW_TQ * GA_EW_TP * 2 : 16];
+#else
 #define GA__SMEM(k, n, S, C, R, W, M) \
   __shared__ GA__WT(S) n##_sm[(M == 3) ? GA_EW_TQ : 1][(M == 3) ? GA__PITCHW(S) : 1];
+#endif
 
 #define GA__BASE(k, n, S, C, R, W, M) long long n##_base = 0;
 #define GA__BASE_STEP(k, n, S, C, R, W, M) n##_base += (long long)pos * L.stro[k][d];
 #define GA__BASE_FIN(k, n, S, C, R, W, M) \
   char *const n##_t = n##_p + n##_base + (long long)p0 * L.strp[k] + (long long)q0 * L.strq[k];
 
+#if GA_EW_LDSM
+/* stage a mode-3 input: 16-byte asynchronous copies along P into swizzled rows */
+#define GA__STAGE(k, n, S, C, R, W, M)                                                        \
+  if (M == 3) {                                                                               \
+    constexpr int CH = GA_EW_TP / 8; /* 16-byte chunks per tile row */                        \
+    const long long sq_ = L.strq[k];                                                          \
+    const bool al_ = (((unsigned long long)n##_t) % 16 == 0) && (sq_ % 16 == 0) &&            \
+                     (pn == GA_EW_TP);                                                        \
+    if (al_) {                                                                                \
+      _Pragma("unroll") for (int k_ = 0; k_ < (GA_EW_TQ * CH + GA_EW_THREADS - 1) / GA_EW_THREADS; k_++) { \
+        const int i_ = threadIdx.x + k_ * GA_EW_THREADS;                                      \
+        const int q_ = i_ / CH, c_ = i_ - q_ * CH;                                            \
+        if (i_ < GA_EW_TQ * CH && q_ < qn)                                                    \
+          ga__cp_async16(n##_sm + q_ * (GA_EW_TP * 2) + ((c_ ^ ga__swz(q_)) << 4),            \
+                         n##_t + (long long)q_ * sq_ + c_ * 16);                              \
+      }                                                                                       \
+    } else {                                                                                  \
+      for (int i_ = threadIdx.x; i_ < GA_EW_TQ * GA_EW_TP; i_ += GA_EW_THREADS) {             \
+        const int q_ = i_ / GA_EW_TP, p_ = i_ - q_ * GA_EW_TP;                                \
+        if (q_ < qn && p_ < pn)                                                               \
+          *reinterpret_cast<S *>(n##_sm + q_ * (GA_EW_TP * 2) +                               \
+                                 (((p_ >> 3) ^ ga__swz(q_)) << 4) + (p_ & 7) * 2) =           \
+              *reinterpret_cast<const S *>(n##_t + (long long)q_ * sq_ + p_ * 2);             \
+      }                                                                                       \
+    }                                                                                         \
+  }
+/* the thread's 8 consecutive Q positions of P position pl, by one transposing matrix load
+ * (executed by every lane, in or out of range: the addresses stay inside the tile) */
+#define GA__LOAD3(k, n, S, C, R, W, M)                                                        \
+  if (R && M == 3) {                                                                          \
+    const int lane_ = threadIdx.x & 31, m_ = lane_ >> 3, rho_ = lane_ & 7;                    \
+    const int q_ = qbase + 8 * (rho_ >> 1) + 2 * m_ + (rho_ & 1);                             \
+    unsigned int r_[4];                                                                       \
+    ga__ldsm_x4_trans(n##_sm + q_ * (GA_EW_TP * 2) + (((pl >> 3) ^ ga__swz(q_)) << 4), r_);   \
+    _Pragma("unroll") for (int j_ = 0; j_ < 4; j_++) {                                        \
+      S two_[2];                                                                              \
+      memcpy(two_, &r_[j_], 4);                                                               \
+      n##_c[0][2 * j_] = ga__conv<C, S>::in(two_[0]);                                         \
+      n##_c[0][2 * j_ + 1] = ga__conv<C, S>::in(two_[1]);                                     \
+    }                                                                                         \
+  }
+#else
 /* stage a mode-3 input: 128-bit loads along P, one row per Q position */
 #define GA__STAGE(k, n, S, C, R, W, M)                                                        \
   if (M == 3) {                                                                               \
@@ -119,22 +184,33 @@ static __device__ __forceinline__ void ga__stage_map(const int i, int &q, int &v
     }                                                                                         \
   }
 
+#endif /* GA_EW_LDSM */
+
 #define GA__DECL(k, n, S, C, R, W, M) C n##_c[GA_EW_PWI][GA_EW_EPT];
+
+#if GA_EW_LDSM
+#define GA__LOAD_STAGED(k, n, S, C, R, W, M) /* done by GA__LOAD3 before the range test */
+#else
+#define GA__LOAD_STAGED(k, n, S, C, R, W, M)                                                  \
+  {                                                                                           \
+    typedef GA__WT(S) W_;                                                                     \
+    constexpr int PW = GA__PW(S);                                                             \
+    _Pragma("unroll") for (int e = 0; e < GA_EW_EPT; e++) {                                   \
+      _Pragma("unroll") for (int w_ = 0; w_ < GA_EW_PWI / PW; w_++) {                         \
+        const W_ word_ = n##_sm[ql + e][pl / PW + w_];                                        \
+        S tmp_[PW];                                                                           \
+        memcpy(tmp_, &word_, sizeof(W_));                                                     \
+        _Pragma("unroll") for (int j_ = 0; j_ < PW; j_++)                                     \
+          n##_c[w_ * PW + j_][e] = ga__conv<C, S>::in(tmp_[j_]);                              \
+      }                                                                                       \
+    }                                                                                         \
+  }
+#endif
 
 #define GA__LOAD(k, n, S, C, R, W, M)                                                         \
   if (R) {                                                                                    \
     if (M == 3) {                                                                             \
-      typedef GA__WT(S) W_;                                                                   \
-      constexpr int PW = GA__PW(S);                                                           \
-      _Pragma("unroll") for (int e = 0; e < GA_EW_EPT; e++) {                                 \
-        _Pragma("unroll") for (int w_ = 0; w_ < GA_EW_PWI / PW; w_++) {                       \
-          const W_ word_ = n##_sm[ql + e][pl / PW + w_];                                      \
-          S tmp_[PW];                                                                         \
-          memcpy(tmp_, &word_, sizeof(W_));                                                   \
-          _Pragma("unroll") for (int j_ = 0; j_ < PW; j_++)                                   \
-            n##_c[w_ * PW + j_][e] = ga__conv<C, S>::in(tmp_[j_]);                            \
-        }                                                                                     \
-      }                                                                                       \
+      GA__LOAD_STAGED(k, n, S, C, R, W, M)                                                    \
     } else {                                                                                  \
       _Pragma("unroll") for (int kk = 0; kk < GA_EW_PWI; kk++) {                              \
         if (pl + kk < pn) {                                                                   \
@@ -204,6 +280,31 @@ ga_ew_transpose(const __grid_constant__ ga__ewt_layout L
 #endif
     GA_EW_ARRAYS(GA__BASE_FIN)
     GA_EW_ARRAYS(GA__STAGE)
+#if GA_EW_LDSM
+    ga__cp_async_wait_all();
+    __syncthreads();
+    {
+      /* a warp step: 8 P positions (one 16-byte chunk column) x 32 Q positions */
+      constexpr int NG = GA_EW_TP / 8, NUNITS = NG * (GA_EW_TQ / 32);
+      const int lane = threadIdx.x & 31;
+#pragma unroll 2
+      for (int u = threadIdx.x >> 5; u < NUNITS; u += GA_EW_THREADS / 32) {
+        const int g_ = u % NG, qbase = (u / NG) * 32;
+        const int pl = 8 * g_ + (lane >> 2), ql = qbase + 8 * (lane & 3);
+        GA_EW_ARRAYS(GA__DECL)
+        GA_EW_ARRAYS(GA__LOAD3)
+        if (pl < pn && ql < qn) {
+          GA_EW_ARRAYS(GA__LOAD)
+#pragma unroll
+          for (int e = 0; e < GA_EW_EPT; e++) {
+            constexpr int kk = 0;
+            ga_ew_apply(GA_EW_ARRAYS(GA__ARG_ARR) GA_EW_SCALARS(GA__ARG_SC) 0);
+          }
+          GA_EW_ARRAYS(GA__STORE)
+        }
+      }
+    }
+#else
     __syncthreads();
     for (int it = threadIdx.x; it < PG * QG; it += GA_EW_THREADS) {
       /* lanes: QL chunks along Q x 8 groups along P (see the header comment) */
@@ -222,6 +323,7 @@ ga_ew_transpose(const __grid_constant__ ga__ewt_layout L
         GA_EW_ARRAYS(GA__STORE)
       }
     }
+#endif
     __syncthreads();
   }
 }

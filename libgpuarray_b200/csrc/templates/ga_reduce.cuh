@@ -746,6 +746,9 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
 #if defined(GA_RD_BUILD_COLS)
 #if GA_RD_MINB > 0
 #define GA__RD_COLS_BOUNDS __launch_bounds__(32 * GA_RD_BY, GA_RD_MINB)
+#elif GA_RD_SIMPLE && GA_RD_KIND == 0
+/* the lean walk fits 32 registers: a full complement of resident threads per SM */
+#define GA__RD_COLS_BOUNDS __launch_bounds__(32 * GA_RD_BY, 2048 / (32 * GA_RD_BY))
 #else
 #define GA__RD_COLS_BOUNDS __launch_bounds__(32 * GA_RD_BY)
 #endif
@@ -770,6 +773,90 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
   __shared__ ga__state sm[GA_RD_BY][GA_RD_VEC][32];
   __shared__ int sm_last;
   const unsigned tx = threadIdx.x, ty = threadIdx.y;
+#if GA_RD_SIMPLE
+  /* One reduced dimension, one contiguous kept run and nothing else (the host checks):
+   * a pointer walking down the rows with 32-bit counters. Half the registers of the
+   * general loop below, so all CTAs of the grid are resident at once and the next
+   * launch of the stream finds room beside them. */
+  {
+    const unsigned int tile = blockIdx.x, split = blockIdx.y, S = (unsigned int)L.splits;
+    const unsigned int kc = (unsigned int)L.inner, nrows = (unsigned int)L.nr_total;
+    const unsigned int col0 = (tile * 32 + tx) * GA_RD_VEC;
+    const bool live = col0 < kc;
+    ga__state st[GA_RD_VEC];
+#pragma unroll
+    for (int j = 0; j < GA_RD_VEC; j++) st[j] = ga__init();
+    if (live) {
+      unsigned int j = split * GA_RD_BY + ty;
+      const unsigned int jstep = S * GA_RD_BY;
+      const char *p = src + (ga__i64)j * L.rsrc[0] + (ga__i64)col0 * (ga__i64)sizeof(GA_RD_SRC_T);
+      const ga__i64 step = (ga__i64)jstep * L.rsrc[0];
+      const GA_RD_IDX_T rm = (GA_RD_IDX_T)L.rmul[0];
+#pragma unroll ga__rd_unroll
+      for (; j < nrows; j += jstep) {
+        const ga__rd_pack<GA_RD_VEC> t = *reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(p);
+#pragma unroll
+        for (int k = 0; k < GA_RD_VEC; k++) ga__take(st[k], GA_RD_LOAD(t.v[k]), (GA_RD_IDX_T)j * rm);
+        p += step;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < GA_RD_VEC; k++) sm[ty][k][tx] = st[k];
+    __syncthreads();
+    if (ty < GA_RD_VEC && live) {
+      ga__state tot = sm[0][ty][tx];
+#pragma unroll
+      for (int y = 1; y < GA_RD_BY; y++) ga__merge(tot, sm[y][ty][tx]);
+      if (S == 1) {
+        ga__emit(L, src, d0, d1, col0 + ty, tot);
+      } else {
+        pval[(ga__u64)split * L.nf_total + col0 + ty] = tot.v;
+#if GA_RD_KIND == 1
+        pidx[(ga__u64)split * L.nf_total + col0 + ty] = tot.i;
+#endif
+      }
+    }
+    if (S > 1) {
+      __syncthreads();
+      if (tx == 0 && ty == 0) sm_last = ga__take_ticket(&tickets[tile], S) ? 1 : 0;
+      __syncthreads();
+      if (sm_last) {
+        ga__state fin[GA_RD_VEC];
+#pragma unroll
+        for (int k = 0; k < GA_RD_VEC; k++) fin[k] = ga__init();
+        if (live) {
+          for (unsigned int sp = ty; sp < S; sp += GA_RD_BY) {
+            GA_RD_ACC_T pv[GA_RD_VEC];
+            ga__ldcg_block<(int)(GA_RD_VEC * sizeof(GA_RD_ACC_T))>(pv, &pval[(ga__u64)sp * L.nf_total + col0]);
+#if GA_RD_KIND == 1
+            GA_RD_IDX_T pi[GA_RD_VEC];
+            ga__ldcg_block<(int)(GA_RD_VEC * sizeof(GA_RD_IDX_T))>(pi, &pidx[(ga__u64)sp * L.nf_total + col0]);
+#endif
+#pragma unroll
+            for (int k = 0; k < GA_RD_VEC; k++) {
+              ga__state t;
+              t.v = pv[k];
+#if GA_RD_KIND == 1
+              t.i = pi[k];
+#endif
+              ga__merge(fin[k], t);
+            }
+          }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < GA_RD_VEC; k++) sm[ty][k][tx] = fin[k];
+        __syncthreads();
+        if (ty < GA_RD_VEC && live) {
+          ga__state tot = sm[0][ty][tx];
+#pragma unroll
+          for (int y = 1; y < GA_RD_BY; y++) ga__merge(tot, sm[y][ty][tx]);
+          ga__emit(L, src, d0, d1, col0 + ty, tot);
+        }
+      }
+    }
+  }
+#else
   const ga__u64 kc = L.inner;                 /* contiguous kept run */
   const ga__u64 ko_total = L.nf_total / kc;   /* outer kept positions */
   const ga__u64 nwork = ko_total * L.tiles;
@@ -907,6 +994,7 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
     }
     __syncthreads();
   }
+#endif /* !GA_RD_SIMPLE */
 }
 #endif
 

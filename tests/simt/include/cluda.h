@@ -39,4 +39,20 @@ static inline ga_half ga_float2half(float f) {
 
 static inline void ga__grid_dependency_sync() {}
 static inline void ga__prefetch_l2(const void *, unsigned int) {}
+static inline void ga__cp_async16(void *smem, const void *gmem) { memcpy(smem, gmem, 16); }
+static inline void ga__cp_async_wait_all() {}
+/* ldmatrix.x4.trans: lane 8m + rho publishes the address of row rho of matrix m; lane i
+ * reads elements [2*(i%4)][i/4] and [2*(i%4)+1][i/4] of each matrix */
+static inline void ga__ldsm_x4_trans(const void *row, unsigned int r[4]) {
+  const unsigned lane = simt::cur->linear % 32;
+  for (int m = 0; m < 4; m++) {
+    unsigned short e[2];
+    for (int k = 0; k < 2; k++) {
+      const unsigned src = 8 * m + 2 * (lane % 4) + k;
+      const unsigned long long a = simt::exchange((unsigned long long)(uintptr_t)row, src);
+      memcpy(&e[k], (const char *)(uintptr_t)a + 2 * (lane / 4), 2);
+    }
+    r[m] = (unsigned int)e[0] | ((unsigned int)e[1] << 16);
+  }
+}
 #endif

@@ -212,13 +212,15 @@ def test_plans_of_the_named_elementwise_configurations(api):
     big = (1 << 31) + 64
     err, p = plan(api, [(np.uint8, R, (big,), [1]), (np.uint8, W, (big,), [1])])
     assert err == 0 and p["idx"] & 1 == 0
-    # config 4: fp16 NHWC view -> NCHW: tiled transpose, 256 x 64 tile, 2 P positions per thread
+    # config 4: fp16 NHWC view -> NCHW: tiled transpose through cp.async + ldmatrix (unroll == 2
+    # marks that build), 256 x 32 tile, one P position x 8 Q positions per thread
     x = (np.float16, R, (64, 256, 56, 56), [1605632, 2, 28672, 512])
     bias = (np.float16, R, (1, 256, 1, 1), [512, 2, 2, 2])
     y = (np.float16, W, (64, 256, 56, 56), cs((64, 256, 56, 56), 2))
     err, p = plan(api, [x, bias, y], obj_flags=api.GE_CONVERT_F16, call_flags=api.GE_BROADCAST)
-    assert err == 0 and p["kind"] == 2 and (p["tp"], p["tq"], p["pwi"], p["nd"]) == (256, 64, 2, 3)
-    assert modes(p, 3)[0] == 3 and p["gx"] == 64 * 1 * 49                  # 64 images x (256/256) x (3136/64)
+    assert err == 0 and p["kind"] == 2 and (p["tp"], p["tq"], p["pwi"], p["nd"]) == (256, 32, 1, 3)
+    assert p["unroll"] == 2
+    assert modes(p, 3)[0] == 3 and p["gx"] == 64 * 1 * 98                  # 64 images x (256/256) x (3136/32)
     # an fp32 transposed view: 128 x 32 tiles
     M, N = 8192, 4096
     a_t = (np.float32, R, (N, M), [4, 4 * N])

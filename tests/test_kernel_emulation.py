@@ -241,7 +241,8 @@ class _Arg(ctypes.Structure):
 
 
 CTYPE = {np.dtype(np.float32): "float", np.dtype(np.float64): "double", np.dtype(np.float16): "ga_half",
-         np.dtype(np.int32): "int", np.dtype(np.uint8): "unsigned char", np.dtype(np.int64): "long long"}
+         np.dtype(np.int32): "int", np.dtype(np.uint8): "unsigned char", np.dtype(np.int64): "long long",
+         np.dtype(np.int16): "short"}
 EW_KEYS = ["kind", "ept", "unroll", "nd", "idx", "modes", "tp", "tq", "pwi", "gx", "gy", "gz",
            "bx", "by", "bz", "n"]
 EW_ENTRY = ["ga_ew_contig", "ga_ew_strided", "ga_ew_transpose"]
@@ -401,9 +402,25 @@ def test_elementwise_kernels_on_the_emulator(api, rng):
     p = emulate_elemwise(api, "y = fmaxf(x + bias, 0.0f)", [("x", np.float16, R), ("bias", np.float16, R),
                                                            ("y", np.float16, W)], [x, bias, y],
                          obj_flags=api.GE_CONVERT_F16, call_flags=api.GE_BROADCAST)
-    assert p["kind"] == 2 and p["pwi"] == 2
+    assert p["kind"] == 2 and p["unroll"] == 2 and p["pwi"] == 1     # cp.async + ldmatrix build
     want = np.maximum(x.astype(np.float32) + bias.astype(np.float32), 0).astype(np.float16)
     assert (y == want).all()
+    # the same with full tiles (64 channels, aligned rows: the 16-byte copy path) and a ragged Q edge
+    nhwc = rng.standard_normal((2, 5, 9, 128)).astype(np.float16)
+    x = nhwc.transpose(0, 3, 1, 2)
+    bias = (0.2 * rng.random((1, 128, 1, 1)) - 0.1).astype(np.float16)
+    y = np.zeros((2, 128, 5, 9), np.float16)
+    p = emulate_elemwise(api, "y = fmaxf(x + bias, 0.0f)", [("x", np.float16, R), ("bias", np.float16, R),
+                                                           ("y", np.float16, W)], [x, bias, y],
+                         obj_flags=api.GE_CONVERT_F16, call_flags=api.GE_BROADCAST)
+    assert p["kind"] == 2 and p["unroll"] == 2 and p["tp"] == 128
+    want = np.maximum(x.astype(np.float32) + bias.astype(np.float32), 0).astype(np.float16)
+    assert (y == want).all()
+    # int16 through the same path, Q extent a multiple of 8 (vector stores)
+    a16 = rng.integers(-300, 300, (64, 72)).astype(np.int16)
+    o16 = np.zeros((72, 64), np.int16)
+    p = emulate_elemwise(api, "o = a + 1", [("a", np.int16, R), ("o", np.int16, W)], [a16.T, o16])
+    assert p["kind"] == 2 and p["unroll"] == 2 and (o16 == a16.T + 1).all()
 
 
 def test_random_reductions_on_the_emulator(api, oracle):
