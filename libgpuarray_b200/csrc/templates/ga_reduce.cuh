@@ -248,6 +248,19 @@ static __device__ __forceinline__ void ga__emit(const ga__rd_layout &L, const ch
 #endif
 }
 
+/* ga__emit when there is ONE kept dimension (the lean column walk): for accumulating
+ * operators the offset is a single multiply - no coordinate decoding, no first-element
+ * check - which also spares the kernel a spill */
+static __device__ __forceinline__ void ga__emit_lean(const ga__rd_layout &L, const char *src,
+                                                     char *d0, char *d1, const unsigned int o,
+                                                     const ga__state &s) {
+#if GA_RD_KIND == 0
+  *reinterpret_cast<GA_RD_DST_T *>(d0 + (ga__i64)o * L.fdst0[0]) = GA_RD_STORE(s.v);
+#else
+  ga__emit(L, src, d0, d1, o, s);
+#endif
+}
+
 template <typename T>
 static __device__ __forceinline__ T ga__ldcg(const T *p) {
   T r;
@@ -474,9 +487,14 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
    * resident while this grid still runs (they wait in ga__grid_dependency_sync) and
    * start the moment it completes. */
   {
+    /* SIGNED loop counters on purpose (the host keeps every extent below 2^31): signed
+     * overflow being undefined lets the compiler derive the trip count of a strided loop
+     * and batch the loads of the unrolled body; with unsigned counters it must allow for
+     * wrap-around and does not (measured in the column walk, fp32 4096 x 4096:
+     * 14.9 -> 14.45 us). */
     const unsigned int nout = (unsigned int)L.nf_total;
-    const unsigned int len = (unsigned int)L.inner, nv = len / GA_RD_VEC;
-    const unsigned int wl = threadIdx.x & 31u;
+    const int len = (int)L.inner, nv = len / GA_RD_VEC;
+    const int wl = (int)(threadIdx.x & 31u);
     const unsigned int nwarps = gridDim.x * (GA_RD_THREADS / 32);
     for (unsigned int o = blockIdx.x * (GA_RD_THREADS / 32) + (threadIdx.x >> 5); o < nout;
          o += nwarps) {
@@ -486,11 +504,11 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
 #pragma unroll
       for (int j = 0; j < GA_RD_VEC; j++) st[j] = ga__init();
 #pragma unroll ga__rd_unroll
-      for (unsigned int i = wl; i < nv; i += 32) {
+      for (int i = wl; i < nv; i += 32) {
         const ga__rd_pack<GA_RD_VEC> t = pv[i];
         ga__fold_lanes(st, t, (GA_RD_IDX_T)(i * GA_RD_VEC) * imul, imul);
       }
-      for (unsigned int i = nv * GA_RD_VEC + wl; i < len; i += 32)
+      for (int i = nv * GA_RD_VEC + wl; i < len; i += 32)
         ga__take(st[0], GA_RD_LOAD(reinterpret_cast<const GA_RD_SRC_T *>(base)[i]),
                  (GA_RD_IDX_T)i * imul);
 #pragma unroll
@@ -787,13 +805,14 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
 #pragma unroll
     for (int j = 0; j < GA_RD_VEC; j++) st[j] = ga__init();
     if (live) {
-      unsigned int j = split * GA_RD_BY + ty;
-      const unsigned int jstep = S * GA_RD_BY;
+      /* signed counters: see the note in ga_rd_rows */
+      const int jstep = (int)(S * GA_RD_BY), jend = (int)nrows;
+      int j = (int)(split * GA_RD_BY + ty);
       const char *p = src + (ga__i64)j * L.rsrc[0] + (ga__i64)col0 * (ga__i64)sizeof(GA_RD_SRC_T);
       const ga__i64 step = (ga__i64)jstep * L.rsrc[0];
       const GA_RD_IDX_T rm = (GA_RD_IDX_T)L.rmul[0];
 #pragma unroll ga__rd_unroll
-      for (; j < nrows; j += jstep) {
+      for (; j < jend; j += jstep) {
         const ga__rd_pack<GA_RD_VEC> t = *reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(p);
 #pragma unroll
         for (int k = 0; k < GA_RD_VEC; k++) ga__take(st[k], GA_RD_LOAD(t.v[k]), (GA_RD_IDX_T)j * rm);
@@ -808,7 +827,7 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
 #pragma unroll
       for (int y = 1; y < GA_RD_BY; y++) ga__merge(tot, sm[y][ty][tx]);
       if (S == 1) {
-        ga__emit(L, src, d0, d1, col0 + ty, tot);
+        ga__emit_lean(L, src, d0, d1, col0 + ty, tot);
       } else {
         pval[(ga__u64)split * L.nf_total + col0 + ty] = tot.v;
 #if GA_RD_KIND == 1
@@ -851,7 +870,7 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
           ga__state tot = sm[0][ty][tx];
 #pragma unroll
           for (int y = 1; y < GA_RD_BY; y++) ga__merge(tot, sm[y][ty][tx]);
-          ga__emit(L, src, d0, d1, col0 + ty, tot);
+          ga__emit_lean(L, src, d0, d1, col0 + ty, tot);
         }
       }
     }
