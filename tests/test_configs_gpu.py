@@ -135,3 +135,52 @@ def test_config5_fp64_16gib_properties(api, ctx):
         api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.float64)(d, None, gx[lo:hi], [0, 1, 2])
         parts.append(float(d.to_numpy()))
     assert parts[0] + parts[1] == want
+
+
+def test_config5_named_input_full_size(api, ctx):
+    """Configuration 5 on its NAMED input: seed 4, x = 2 * U[0, 1) - 1 in fp64, shape
+    (2048, 1024, 1024), generated on the host in axis-0 chunks (one PCG64 stream, so the
+    chunks are consecutive pieces of the one array) and uploaded chunk by chunk.
+    SUM over all axes against a chunked long-double sum with the stated bound
+    |err| <= 1e-12 * log2(n) * sum|x|; MIN and MAX over axes (0, 2) bit-exact against
+    NumPy; MAXANDARGMAX over (0, 2): the value is MAX's and the element at the returned
+    flat index is that value."""
+    free = ctx.prop_size(10)
+    if free < 20 * (1 << 30):
+        pytest.skip("needs 20 GiB of free device memory")
+    rng = np.random.Generator(np.random.PCG64(4))
+    gx = api.GpuArray.empty(ctx, (2048, 1024, 1024), np.float64)
+    planes = 64
+    total = np.longdouble(0)
+    total_abs = np.longdouble(0)
+    mn = np.full(1024, np.inf)
+    mx = np.full(1024, -np.inf)
+    first_plane_of_max = np.zeros(1024, np.int64)
+    for lo in range(0, 2048, planes):
+        chunk = rng.random((planes, 1024, 1024))
+        chunk *= 2
+        chunk -= 1
+        gx[lo:lo + planes].write(chunk)
+        total += chunk.sum(dtype=np.longdouble)
+        total_abs += np.abs(chunk).sum(dtype=np.longdouble)
+        mn = np.minimum(mn, chunk.min(axis=(0, 2)))
+        cmx = chunk.max(axis=(0, 2))
+        mx = np.where(cmx > mx, cmx, mx)
+    n = 2048 * 1024 * 1024
+    d = api.GpuArray.empty(ctx, (), np.float64)
+    api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.float64)(d, None, gx, [0, 1, 2])
+    got = np.longdouble(float(d.to_numpy()))
+    assert abs(got - total) <= np.longdouble(1e-12) * np.log2(n) * total_abs, (got, total)
+    dk = api.GpuArray.empty(ctx, (1024,), np.float64)
+    api.GpuReduction(ctx, api.GA_REDUCE_MIN, np.float64)(dk, None, gx, [0, 2])
+    assert dk.to_numpy().tobytes() == mn.tobytes()
+    api.GpuReduction(ctx, api.GA_REDUCE_MAX, np.float64)(dk, None, gx, [0, 2])
+    assert dk.to_numpy().tobytes() == mx.tobytes()
+    di = api.GpuArray.empty(ctx, (1024,), np.int64)
+    api.GpuReduction(ctx, api.GA_REDUCE_MAXANDARGMAX, np.float64)(dk, di, gx, [0, 2])
+    idx = di.to_numpy()
+    assert dk.to_numpy().tobytes() == mx.tobytes() and (idx >= 0).all() and (idx < 2048 * 1024).all()
+    # the element the index points at: (i, j, k) with flat = i * 1024 + k
+    for j in (0, 1, 511, 1023):
+        i, k = divmod(int(idx[j]), 1024)
+        assert float(gx[i:i + 1, j:j + 1, k:k + 1].to_numpy().reshape(())) == mx[j]
