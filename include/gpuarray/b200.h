@@ -154,9 +154,14 @@ GPUARRAY_PUBLIC int gpuarray_b200_mapreduction_plan(int out_tc, unsigned int n,
  *   src, dst     device pointers (src 16-byte aligned); dst receives one float
  *   n            at most GPUARRAY_B200_NOALLOC_MAX_ELEMS, else GA_XLARGE_ERROR
  *   cuda_stream  a CUstream / cudaStream_t (NULL: the default stream)
- * The first call on a device resolves the block's device address; make it
- * before any stream capture. Calls share the block: do not let two of them
- * overlap on the GPU. Returns a GA_* code; text via gpucontext_error(NULL, 0). */
+ * The first call on a device resolves the block's device address (threads
+ * racing to make it are serialised); make it before any stream capture. The
+ * address is cached for the life of the process: a cudaDeviceReset() or a
+ * reset of the primary context invalidates it, do not call this entry point
+ * after one. src and dst must be device memory of the CURRENT device, or
+ * GA_VALUE_ERROR is returned before anything is queued. Calls share the
+ * block: do not let two of them overlap on the GPU. Returns a GA_* code; text
+ * via gpucontext_error(NULL, 0). */
 #define GPUARRAY_B200_NOALLOC_MAX_ELEMS (1ULL << 32)
 GPUARRAY_PUBLIC int gpuarray_b200_sum_f32_noalloc(const float *src, size_t n, float *dst,
                                                   void *cuda_stream);

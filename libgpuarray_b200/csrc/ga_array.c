@@ -644,6 +644,22 @@ int GpuArray_concatenate(GpuArray *r, const GpuArray **as, size_t n, unsigned in
  * src/gpuarray_array.c:425-546). `a` and `i` are C-contiguous, `v` may have
  * any strides. With check_error the error word is read back (a host
  * synchronisation) and an out-of-range index gives GA_VALUE_ERROR. */
+typedef struct take1_entry {
+  int a_tc, v_tc, i_tc;
+  unsigned int nd;
+  ga_function fn;
+  struct take1_entry *next;
+} take1_entry;
+
+void ga_take1_cache_free(gpucontext *ctx) {
+  take1_entry *e = (take1_entry *)ctx->take1_cache, *n;
+  ctx->take1_cache = NULL;
+  for (; e != NULL; e = n) {
+    n = e->next;
+    free(e);
+  }
+}
+
 int GpuArray_take1(GpuArray *a, const GpuArray *v, const GpuArray *i, int check_error) {
   gpucontext *ctx = GpuArray_context(a);
   ga_strb sb;
@@ -687,19 +703,40 @@ int GpuArray_take1(GpuArray *a, const GpuArray *v, const GpuArray *i, int check_
     return ga_err_set(ctx->err, GA_UNSUPPORTED_ERROR, "Unsupported element or index type");
   if (n0 == 0 || n1 == 0) return GA_NO_ERROR;
 
-  ga_strb_init(&sb);
-  ga_strb_printf(&sb,
-                 "#include \"cluda.h\"\n#define GA_TK_R_T %s\n#define GA_TK_V_T %s\n"
-                 "#define GA_TK_I_T %s\n#define GA_TK_ND %u\n#include \"ga_take1.cuh\"\n",
-                 ga_ctype(a->typecode), ga_ctype(v->typecode), ga_ctype(i->typecode), v->nd);
-  if (sb.failed) {
-    ga_strb_free(&sb);
-    return ga_err_set(ctx->err, GA_MEMORY_ERROR, "Out of memory");
+  {
+    /* the gather kernel of this (types, rank): built once per context, so that a call
+     * costs no source generation, hashing or module look-up */
+    take1_entry *te;
+    for (te = (take1_entry *)ctx->take1_cache; te != NULL; te = te->next)
+      if (te->a_tc == a->typecode && te->v_tc == v->typecode && te->i_tc == i->typecode &&
+          te->nd == v->nd)
+        break;
+    if (te == NULL) {
+      ga_strb_init(&sb);
+      ga_strb_printf(&sb,
+                     "#include \"cluda.h\"\n#define GA_TK_R_T %s\n#define GA_TK_V_T %s\n"
+                     "#define GA_TK_I_T %s\n#define GA_TK_ND %u\n#include \"ga_take1.cuh\"\n",
+                     ga_ctype(a->typecode), ga_ctype(v->typecode), ga_ctype(i->typecode), v->nd);
+      if (sb.failed) {
+        ga_strb_free(&sb);
+        return ga_err_set(ctx->err, GA_MEMORY_ERROR, "Out of memory");
+      }
+      err = ga_compile(ctx, ga_strb_cstr(&sb), "ga_take1", NULL, &fn, NULL);
+      ga_strb_free(&sb);
+      if (err != GA_NO_ERROR) return err;
+      fn.dependent_ok = 1;
+      te = calloc(1, sizeof(*te));
+      if (te == NULL) return ga_err_sys(ctx->err, "calloc");
+      te->a_tc = a->typecode;
+      te->v_tc = v->typecode;
+      te->i_tc = i->typecode;
+      te->nd = v->nd;
+      te->fn = fn;
+      te->next = (take1_entry *)ctx->take1_cache;
+      ctx->take1_cache = te;
+    }
+    fn = te->fn;
   }
-  err = ga_compile(ctx, ga_strb_cstr(&sb), "ga_take1", NULL, &fn, NULL);
-  ga_strb_free(&sb);
-  if (err != GA_NO_ERROR) return err;
-  fn.dependent_ok = 1;
 
   blob[0] = n0;
   blob[1] = n1;

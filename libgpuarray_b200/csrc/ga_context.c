@@ -275,6 +275,7 @@ void gpucontext_deref(gpucontext *ctx) {
   ga_ctx_enter(ctx);
   ga_extcopy_cache_free(ctx);
   ga_maxandargmax_cache_free(ctx);
+  ga_take1_cache_free(ctx);
   ga_ctx_exit(ctx);
   ga_ctx_unref(ctx);
 }

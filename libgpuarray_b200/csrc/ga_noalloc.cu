@@ -58,6 +58,8 @@
 #define GA_RD_BUILD_ROWS
 #include "ga_reduce.cuh"
 
+#include <pthread.h>
+
 extern "C" {
 #include <gpuarray/error.h>
 #include <gpuarray/b200.h>
@@ -76,8 +78,23 @@ extern "C" int ga_err_fmt(struct ga_error_rec *e, int code, const char *fmt, ...
 static __device__ __align__(256) unsigned char ga_noalloc_scratch[GA_NOALLOC_SCRATCH_BYTES];
 
 #define GA_NOALLOC_MAX_DEVICES 64
+/* filled once per device under setup_lock, published through `ready` */
 static unsigned char *scratch_of_device[GA_NOALLOC_MAX_DEVICES];
 static int sms_of_device[GA_NOALLOC_MAX_DEVICES];
+static int ready[GA_NOALLOC_MAX_DEVICES];
+static pthread_mutex_t setup_lock = PTHREAD_MUTEX_INITIALIZER;
+
+/* true when `p` is device (or managed) memory of device `dev`; queries the driver's
+ * bookkeeping only, allocates nothing */
+static int on_device(const void *p, int dev) {
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  if (at.type == cudaMemoryTypeManaged) return 1;
+  return at.type == cudaMemoryTypeDevice && at.device == dev;
+}
 
 static int cuda_fail(const char *what, cudaError_t e) {
   return ga_err_fmt(NULL, GA_IMPL_ERROR, "%s: %s: %s", what, cudaGetErrorName(e),
@@ -106,14 +123,30 @@ extern "C" GPUARRAY_PUBLIC int gpuarray_b200_sum_f32_noalloc(const float *src, s
   if (dev < 0 || dev >= GA_NOALLOC_MAX_DEVICES)
     return ga_err_fmt(NULL, GA_VALUE_ERROR, "device ordinal %d out of range", dev);
 
-  if (scratch_of_device[dev] == NULL) {
-    /* once per device, with that device current: the device address of the block */
+  /* nothing is queued for pointers that do not live on the current device */
+  if ((n != 0 && !on_device(src, dev)) || !on_device(dst, dev))
+    return ga_err_fmt(NULL, GA_VALUE_ERROR,
+                      "gpuarray_b200_sum_f32_noalloc: src and dst must be device memory of the "
+                      "current device (%d)", dev);
+
+  if (!__atomic_load_n(&ready[dev], __ATOMIC_ACQUIRE)) {
+    /* once per device, with that device current: the device address of the block. Two
+     * threads making their first call together are serialised here. */
     void *p = NULL;
-    ce = cudaGetSymbolAddress(&p, ga_noalloc_scratch);
-    if (ce != cudaSuccess) return cuda_fail("cudaGetSymbolAddress", ce);
-    ce = cudaDeviceGetAttribute(&sms_of_device[dev], cudaDevAttrMultiProcessorCount, dev);
-    if (ce != cudaSuccess) return cuda_fail("cudaDeviceGetAttribute", ce);
-    scratch_of_device[dev] = (unsigned char *)p;
+    int sms = 0;
+    pthread_mutex_lock(&setup_lock);
+    if (!ready[dev]) {
+      ce = cudaGetSymbolAddress(&p, ga_noalloc_scratch);
+      if (ce == cudaSuccess) ce = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      if (ce != cudaSuccess) {
+        pthread_mutex_unlock(&setup_lock);
+        return cuda_fail("set-up of the built-in scratch block", ce);
+      }
+      scratch_of_device[dev] = (unsigned char *)p;
+      sms_of_device[dev] = sms;
+      __atomic_store_n(&ready[dev], 1, __ATOMIC_RELEASE);
+    }
+    pthread_mutex_unlock(&setup_lock);
   }
   scratch = scratch_of_device[dev];
 

@@ -149,6 +149,10 @@ static char *gen_source(const GpuReduction *gr, const rd_variant *v) {
   ga_strb_printf(&sb, "#define GA_RD_MAP(x) %s\n#define GA_RD_COMBINE(a, b) %s\n"
                       "#define GA_RD_IDENT %s\n#define GA_RD_BETTER(b, a) %s\n",
                  map, combine, ident, op_is_min(gr->op) ? "((b) < (a))" : "((b) > (a))");
+  /* float16 sums accumulated in float: widen-and-add in one instruction */
+  if (gr->op == GA_REDUCE_SUM && gr->src_tc == GA_HALF &&
+      (v->dst_tc == GA_HALF || v->dst_tc == GA_FLOAT))
+    ga_strb_puts(&sb, "#define GA_RD_ADD_RAW(acc, raw) ga__add_f32_f16((acc), (raw))\n");
   if (gr->kind == 1) {
     const int mn = op_is_min(gr->op);
     if (gr->src_tc == GA_DOUBLE)
@@ -474,10 +478,10 @@ static int all_multiple(const long long *v, unsigned n, long long m) {
 /* Tuning for experiments: GPUARRAY_B200_RD="ctas_per_sm,seg_vectors,cta_min_vectors,
  * cols_ctas_per_sm (0 = the lanes rule),onerun_ctas_per_sm,onerun_loads_per_lane,
  * onerun_outputs_at_once,lazy_index (0/1),lazy_min_vectors_per_lane,cols_row_lanes (0 = rule),
- * lean_rows (0/1),cols_early_rows". The
+ * lean_rows (0/1),cols_early_rows,lazy_min_vectors_per_lane_short_runs". The
  * defaults are the best of sweeps on a B200. */
 static unsigned rd_cols_ctas_per_sm = 0, rd_cols_by = 0;
-static unsigned rd_simple = 1, rd_cols_early = 4;
+static unsigned rd_simple = 1, rd_cols_early = 4, rd_lazy_onerun_min = 3;
 static unsigned rd_onerun_ctas_per_sm = 3, rd_onerun_lpl = 4, rd_onerun_mu = 0, rd_lazy = 1, rd_lazy_min = 32;
 
 static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_bytes) {
@@ -487,9 +491,9 @@ static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_
   if (!parsed) {
     const char *env = getenv("GPUARRAY_B200_RD");
     if (env != NULL)
-      sscanf(env, "%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm,
+      sscanf(env, "%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm,
              &rd_onerun_ctas_per_sm, &rd_onerun_lpl, &rd_onerun_mu, &rd_lazy, &rd_lazy_min,
-             &rd_cols_by, &rd_simple, &rd_cols_early);
+             &rd_cols_by, &rd_simple, &rd_cols_early, &rd_lazy_onerun_min);
     *warp_bytes = t_warp;
     if (t_ctas == 0) t_ctas = 32;
     if (t_seg == 0) t_seg = 8;
@@ -709,6 +713,11 @@ static int rd_plan(const rd_plan_in *in, rd_layout *L, rd_variant *want, unsigne
    * look at the winning vector, hence the threshold. */
   if (in->kind == 1 && want->shape == SHAPE_ROWS && !want->onerun && !want->flat && want->mu <= 1 &&
       rd_lazy && L->seg / (unsigned)want->vec / (unsigned)(want->group ? want->group : RD_THREADS) >= rd_lazy_min)
+    want->lazy = 1;
+  /* ... and over one short run per output when a lane still sees several vectors (measured on
+   * B200, ARGMAX of fp32 (2^17, 512): see the profile notes) */
+  if (in->kind == 1 && want->shape == SHAPE_ROWS && want->onerun && rd_lazy && want->vec > 1 &&
+      L->inner / (unsigned)want->vec / (unsigned)want->group >= rd_lazy_onerun_min)
     want->lazy = 1;
   /* one run per output, a warp each, nothing split: the lean loop (GA_RD_SIMPLE). Measured on
    * B200, fp32 4096 x 4096 over axis 1, launches back to back: 13.8 -> see the profile notes */

@@ -178,6 +178,7 @@ struct _gpucontext {
   void *extcopy_cache;
   /* lazily created MAXANDARGMAX operators keyed by source type (ga_reduction.c) */
   void *maxandargmax_cache;
+  void *take1_cache;        /* compiled gather kernels by (types, rank): ga_array.c */
 };
 
 #define GA_BUF_EXTERNAL 0x10000    /* memory not owned (cuda_make_buf) */
@@ -250,6 +251,7 @@ GA_HIDDEN int ga_array_is_f_contiguous(const GpuArray *a);
 GA_HIDDEN int ga_array_in_bounds(const GpuArray *a);
 GA_HIDDEN void ga_extcopy_cache_free(gpucontext *ctx);
 GA_HIDDEN void ga_maxandargmax_cache_free(gpucontext *ctx);
+GA_HIDDEN void ga_take1_cache_free(gpucontext *ctx);
 
 /* Name of the C type used in kernel source for a typecode, or NULL. */
 GA_HIDDEN const char *ga_ctype(int typecode);

@@ -65,6 +65,14 @@ static __device__ __forceinline__ ga_half ga_float2half(float f) {
   return h;
 }
 
+/* acc + h with h widened exactly and ONE rounding: the same value as
+ * acc + ga_half2float(h), in one instruction instead of a conversion and an add */
+static __device__ __forceinline__ float ga__add_f32_f16(float acc, ga_half h) {
+  float r;
+  asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(r) : "h"(h.data), "f"(acc));
+  return r;
+}
+
 /* ---- constants ---- */
 #ifdef NAN
 #undef NAN

@@ -140,6 +140,18 @@ static __device__ __forceinline__ void ga__take(ga__state &s, const GA_RD_X_T x,
 #endif
 }
 
+/* fold one source element as stored; operators that can consume the storage form
+ * directly define GA_RD_ADD_RAW(acc, raw) (float16 sums: one mixed-precision add instead
+ * of a conversion and an add, same value) */
+static __device__ __forceinline__ void ga__take_raw(ga__state &s, const GA_RD_SRC_T raw,
+                                                    const GA_RD_IDX_T f) {
+#if defined(GA_RD_ADD_RAW) && GA_RD_KIND == 0
+  s.v = GA_RD_ADD_RAW(s.v, raw);
+#else
+  ga__take(s, GA_RD_LOAD(raw), f);
+#endif
+}
+
 static __device__ __forceinline__ void ga__merge(ga__state &a, const ga__state &b) {
 #if GA_RD_KIND == 0
   a.v = GA_RD_COMBINE(a.v, b.v);
@@ -399,8 +411,7 @@ static __device__ __forceinline__ void ga__fold_lanes(ga__state *st,
   ga__fold_words(st[0], t);
 #else
 #pragma unroll
-  for (int j = 0; j < GA_RD_VEC; j++)
-    ga__take(st[j], GA_RD_LOAD(t.v[j]), f0 + (GA_RD_IDX_T)j * imul);
+  for (int j = 0; j < GA_RD_VEC; j++) ga__take_raw(st[j], t.v[j], f0 + (GA_RD_IDX_T)j * imul);
 #endif
 }
 
@@ -413,8 +424,7 @@ static __device__ __forceinline__ void ga__fold_one(ga__state &s,
   ga__fold_words(s, t);
 #else
 #pragma unroll
-  for (int j = 0; j < GA_RD_VEC; j++)
-    ga__take(s, GA_RD_LOAD(t.v[j]), f0 + (GA_RD_IDX_T)j * imul);
+  for (int j = 0; j < GA_RD_VEC; j++) ga__take_raw(s, t.v[j], f0 + (GA_RD_IDX_T)j * imul);
 #endif
 }
 
@@ -535,6 +545,62 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
         st[k] = ga__init();
         base[k] = src + ga__foff(L, L.fsrc, w[k]);
       }
+#if GA_RD_LAZY
+      /* (value, index) operators: scan values only, keeping per output the best value and
+       * the first vector that reached it; the element, its bit pattern and its index are
+       * recovered from that vector afterwards (same two-step rule as the long-run scan
+       * further down, same result as comparing pairs element by element) */
+      {
+        GA_RD_X_T bv[GA_RD_MU];
+        unsigned int bi[GA_RD_MU];
+#pragma unroll
+        for (int k = 0; k < GA_RD_MU; k++) {
+          bv[k] = (GA_RD_X_T)(GA_RD_IDENT);
+          bi[k] = lane;
+        }
+#pragma unroll 2
+        for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
+          ga__rd_pack<GA_RD_VEC> t[GA_RD_MU];
+#pragma unroll
+          for (int k = 0; k < GA_RD_MU; k++)
+            t[k] = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(base[k])[i];
+#pragma unroll
+          for (int k = 0; k < GA_RD_MU; k++) {
+            GA_RD_X_T m = GA_RD_LOAD(t[k].v[0]);
+#pragma unroll
+            for (int j = 1; j < GA_RD_VEC; j++) m = GA_RD_PICK(m, GA_RD_LOAD(t[k].v[j]));
+            if (GA_RD_BETTER(m, bv[k])) {
+              bv[k] = m;
+              bi[k] = i;
+            }
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < GA_RD_MU; k++) {
+          if (bi[k] < nv) {
+            const ga__rd_pack<GA_RD_VEC> t = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(base[k])[bi[k]];
+            ga__state loc = ga__init();
+#pragma unroll
+            for (int j = GA_RD_VEC - 1; j >= 0; j--) {
+              const GA_RD_X_T x = GA_RD_LOAD(t.v[j]);
+              if (x == bv[k]) { /* first match last: it keeps its own bit pattern (+-0) */
+                loc.v = x;
+                loc.i = (GA_RD_IDX_T)(bi[k] * GA_RD_VEC + (unsigned)j) * imul;
+              }
+            }
+            if (loc.i == GA__IDX_NONE) {
+              /* nothing beat the identity and the first vector does not hold it (NaNs):
+               * the long way over this lane's vectors */
+              for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
+                const ga__rd_pack<GA_RD_VEC> u = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(base[k])[i];
+                ga__fold_one(loc, u, (GA_RD_IDX_T)(i * GA_RD_VEC) * imul, imul);
+              }
+            }
+            ga__merge(st[k], loc);
+          }
+        }
+      }
+#else
 #pragma unroll 2
       for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {
         ga__rd_pack<GA_RD_VEC> t[GA_RD_MU];
@@ -545,6 +611,7 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
         for (int k = 0; k < GA_RD_MU; k++)
           ga__fold_one(st[k], t[k], (GA_RD_IDX_T)(i * GA_RD_VEC) * imul, imul);
       }
+#endif
       for (unsigned int i = nv * GA_RD_VEC + lane; i < len; i += GA_RD_GROUP) {
 #pragma unroll
         for (int k = 0; k < GA_RD_MU; k++)
@@ -673,6 +740,32 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
             }
             ga__merge(st[0], loc);
           }
+        }
+#elif GA_RD_FAST8 == 1 || GA_RD_FAST8 == 2
+        /* byte sums staged in 32 bits: the dot products of up to 2^15 vectors (at most
+         * 2^15 * 16 * 255 < 2^31) go into one 32-bit partial, which is widened to the
+         * accumulator once - one wide add per block instead of one per vector */
+        for (unsigned int ib = lane; ib < nv; ib += GA_RD_GROUP * 32768u) {
+          const unsigned int iend = (nv - ib > GA_RD_GROUP * 32768u) ? ib + GA_RD_GROUP * 32768u : nv;
+#if GA_RD_FAST8 == 1
+          int part = 0;
+#else
+          unsigned int part = 0;
+#endif
+#pragma unroll ga__rd_unroll
+          for (unsigned int i = ib; i < iend; i += GA_RD_GROUP) {
+            const ga__rd_pack<GA_RD_VEC> t = pv[i];
+            unsigned int w_[GA_RD_VEC / 4];
+            memcpy(w_, &t, sizeof(w_));
+#pragma unroll
+            for (int q = 0; q < GA_RD_VEC / 4; q++)
+#if GA_RD_FAST8 == 1
+              part = __dp4a((int)w_[q], 0x01010101, part);
+#else
+              part = __dp4a(w_[q], 0x01010101u, part);
+#endif
+          }
+          st[0].v = GA_RD_COMBINE(st[0].v, (GA_RD_ACC_T)part);
         }
 #else
 #pragma unroll ga__rd_unroll
@@ -815,7 +908,7 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
       for (; j < jend; j += jstep) {
         const ga__rd_pack<GA_RD_VEC> t = *reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(p);
 #pragma unroll
-        for (int k = 0; k < GA_RD_VEC; k++) ga__take(st[k], GA_RD_LOAD(t.v[k]), (GA_RD_IDX_T)j * rm);
+        for (int k = 0; k < GA_RD_VEC; k++) ga__take_raw(st[k], t.v[k], (GA_RD_IDX_T)j * rm);
         p += step;
       }
     }
@@ -927,7 +1020,7 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
         for (unsigned int n = 0; n < full; n++) {
           const ga__rd_pack<GA_RD_VEC> t = *reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(p);
 #pragma unroll
-          for (int k = 0; k < GA_RD_VEC; k++) ga__take(st[k], GA_RD_LOAD(t.v[k]), f);
+          for (int k = 0; k < GA_RD_VEC; k++) ga__take_raw(st[k], t.v[k], f);
           p += step;
           f += fstep;
         }
@@ -947,7 +1040,7 @@ ga_rd_cols(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
           const ga__rd_pack<GA_RD_VEC> t =
               *reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(base + roff);
 #pragma unroll
-          for (int k = 0; k < GA_RD_VEC; k++) ga__take(st[k], GA_RD_LOAD(t.v[k]), f);
+          for (int k = 0; k < GA_RD_VEC; k++) ga__take_raw(st[k], t.v[k], f);
         }
       }
     }

@@ -37,6 +37,7 @@ static inline ga_half ga_float2half(float f) {
   return h;
 }
 
+static inline float ga__add_f32_f16(float acc, ga_half h) { return acc + ga_half2float(h); }
 static inline void ga__grid_dependency_sync() {}
 static inline void ga__prefetch_l2(const void *, unsigned int) {}
 static inline void ga__cp_async16(void *smem, const void *gmem) { memcpy(smem, gmem, 16); }

@@ -205,6 +205,26 @@ def test_short_run_variants_on_the_emulator(api, oracle, rng):
         assert p["group"] <= 32 and p["mu"] in (2, 4)
         check(api, oracle, "MAXANDARGMAX", x, [1], expect={"onerun": 1})
         check(api, oracle, "ARGMIN", x, [1])
+    # (value, index) over one short run with several vectors per lane: values-only scan, then
+    # the element, its bit pattern and its index from the winning vector; NaN first, NaNs
+    # before the only candidate, signed zeros, ties, rows of the identity
+    z = ties(rng, (40, 512))
+    z[0, :8] = np.nan
+    z[1, 0] = np.nan
+    z[2, :] = -np.inf
+    z[2, 3:40] = np.nan
+    z[3, :] = -1
+    z[3, 130] = -0.0
+    z[3, 131] = 0.0
+    z[4, :] = 3
+    z[4, [127, 128, 400]] = 9
+    z[5, :] = np.nan
+    for op in ("MAXANDARGMAX", "ARGMAX", "MAX"):
+        check(api, oracle, op, z, [1], expect={"onerun": 1, "lazy": 1, "group": 32})
+    check(api, oracle, "MINANDARGMIN", -z, [1], expect={"onerun": 1, "lazy": 1})
+    check(api, oracle, "MAXANDARGMAX", ties(rng, (300, 24)), [1], expect={"onerun": 1, "lazy": 1, "group": 2})
+    check(api, oracle, "MINANDARGMIN", rng.integers(-5, 5, (100, 200)).astype(np.int32), [1],
+          expect={"onerun": 1, "lazy": 1})
     # rows that do not start on a 16-byte boundary (49 floats), fp64, int8 -> int64
     check(api, oracle, "SUM", ties(rng, (77, 49)), [1], expect={"onerun": 1, "vec": 1})
     check(api, oracle, "MAXANDARGMAX", ties(rng, (40, 64), np.float64), [1], expect={"onerun": 1, "vec": 2})

@@ -53,8 +53,9 @@ def check_invariants(p, itemsize, kind_pair):
             assert p["group"] in (32, 256)
         if p["group"] == 256:
             assert p["flat"] == 0 and p["mu"] == 1
-        if p["lazy"]:
-            assert kind_pair and not p["onerun"] and not p["flat"] and p["mu"] == 1
+        if p["lazy"]:                                 # values-only scan: long runs, or one short run
+            assert kind_pair and not p["flat"] and (p["onerun"] or p["mu"] == 1) and p["vec"] > 1 or \
+                (kind_pair and not p["onerun"] and not p["flat"] and p["mu"] == 1)
         if p["fast8"]:
             assert itemsize == 1 and p["vec"] % 4 == 0
     elif p["shape"] == SHAPE_COLS:
@@ -85,6 +86,9 @@ def test_named_configurations_get_the_intended_kernels(api):
     # short runs: part of a warp per output, several outputs at once, 3 CTAs per SM
     err, p = plan(api, "SUM", np.float32, [1 << 21, 32], c_strides([1 << 21, 32], 4), [1])
     assert err == 0 and p["onerun"] == 1 and p["group"] == 2 and p["mu"] == 2 and p["gx"] == 148 * 3
+    # ARGMAX over 512-element rows: one run per output, 32 lanes, values-only scan
+    err, p = plan(api, "ARGMAX", np.float32, [1 << 17, 512], c_strides([1 << 17, 512], 4), [1])
+    assert err == 0 and p["onerun"] == 1 and p["group"] == 32 and p["lazy"] == 1
     # an unaligned base drops to scalar loads
     err, p = plan(api, "SUM", np.float32, [4096, 4096], c_strides([4096, 4096], 4), [1], base=0x7f0000000004)
     assert err == 0 and p["vec"] == 1

@@ -65,3 +65,9 @@ def test_noalloc_sum_rejects_what_it_cannot_do(api, ctx):
     err = L.gpuarray_b200_sum_f32_noalloc(ctypes.c_void_p(g.devptr + 4), 8,
                                           ctypes.c_void_p(out.devptr), ctypes.c_void_p(ctx.stream))
     assert err == api.GA_UNALIGNED_ERROR
+    # a host pointer (or memory of another device) is refused before anything is queued
+    host = np.zeros(72, np.float32)
+    addr = (host.ctypes.data + 15) & ~15
+    err = L.gpuarray_b200_sum_f32_noalloc(ctypes.c_void_p(addr), 8, ctypes.c_void_p(out.devptr),
+                                          ctypes.c_void_p(ctx.stream))
+    assert err == api.GA_VALUE_ERROR and b"device memory" in L.gpucontext_error(None, err)
