@@ -481,7 +481,7 @@ static int all_multiple(const long long *v, unsigned n, long long m) {
  * lean_rows (0/1),cols_early_rows,lazy_min_vectors_per_lane_short_runs". The
  * defaults are the best of sweeps on a B200. */
 static unsigned rd_cols_ctas_per_sm = 0, rd_cols_by = 0;
-static unsigned rd_simple = 1, rd_cols_early = 4, rd_lazy_onerun_min = 3;
+static unsigned rd_simple = 1, rd_cols_early = 4, rd_lazy_onerun_min = 8;
 static unsigned rd_onerun_ctas_per_sm = 3, rd_onerun_lpl = 4, rd_onerun_mu = 0, rd_lazy = 1, rd_lazy_min = 32;
 
 static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_bytes) {
@@ -714,8 +714,10 @@ static int rd_plan(const rd_plan_in *in, rd_layout *L, rd_variant *want, unsigne
   if (in->kind == 1 && want->shape == SHAPE_ROWS && !want->onerun && !want->flat && want->mu <= 1 &&
       rd_lazy && L->seg / (unsigned)want->vec / (unsigned)(want->group ? want->group : RD_THREADS) >= rd_lazy_min)
     want->lazy = 1;
-  /* ... and over one short run per output when a lane still sees several vectors (measured on
-   * B200, ARGMAX of fp32 (2^17, 512): see the profile notes) */
+  /* ... and over one short run per output when a lane sees many vectors. Measured on B200: with
+   * 4 vectors per lane the second look at the winning vector costs more than the scan saves
+   * (ARGMAX of fp32 (2^17, 512): 57.4 -> 59.3 us; MAX of (2^22, 16): 60.0 -> 64.5 us), hence
+   * the threshold of 8. */
   if (in->kind == 1 && want->shape == SHAPE_ROWS && want->onerun && rd_lazy && want->vec > 1 &&
       L->inner / (unsigned)want->vec / (unsigned)want->group >= rd_lazy_onerun_min)
     want->lazy = 1;

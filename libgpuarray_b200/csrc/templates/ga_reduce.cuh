@@ -741,32 +741,6 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
             ga__merge(st[0], loc);
           }
         }
-#elif GA_RD_FAST8 == 1 || GA_RD_FAST8 == 2
-        /* byte sums staged in 32 bits: the dot products of up to 2^15 vectors (at most
-         * 2^15 * 16 * 255 < 2^31) go into one 32-bit partial, which is widened to the
-         * accumulator once - one wide add per block instead of one per vector */
-        for (unsigned int ib = lane; ib < nv; ib += GA_RD_GROUP * 32768u) {
-          const unsigned int iend = (nv - ib > GA_RD_GROUP * 32768u) ? ib + GA_RD_GROUP * 32768u : nv;
-#if GA_RD_FAST8 == 1
-          int part = 0;
-#else
-          unsigned int part = 0;
-#endif
-#pragma unroll ga__rd_unroll
-          for (unsigned int i = ib; i < iend; i += GA_RD_GROUP) {
-            const ga__rd_pack<GA_RD_VEC> t = pv[i];
-            unsigned int w_[GA_RD_VEC / 4];
-            memcpy(w_, &t, sizeof(w_));
-#pragma unroll
-            for (int q = 0; q < GA_RD_VEC / 4; q++)
-#if GA_RD_FAST8 == 1
-              part = __dp4a((int)w_[q], 0x01010101, part);
-#else
-              part = __dp4a(w_[q], 0x01010101u, part);
-#endif
-          }
-          st[0].v = GA_RD_COMBINE(st[0].v, (GA_RD_ACC_T)part);
-        }
 #else
 #pragma unroll ga__rd_unroll
         for (unsigned int i = lane; i < nv; i += GA_RD_GROUP) {

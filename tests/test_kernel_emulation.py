@@ -208,7 +208,7 @@ def test_short_run_variants_on_the_emulator(api, oracle, rng):
     # (value, index) over one short run with several vectors per lane: values-only scan, then
     # the element, its bit pattern and its index from the winning vector; NaN first, NaNs
     # before the only candidate, signed zeros, ties, rows of the identity
-    z = ties(rng, (40, 512))
+    z = ties(rng, (40, 1024))
     z[0, :8] = np.nan
     z[1, 0] = np.nan
     z[2, :] = -np.inf
@@ -222,8 +222,7 @@ def test_short_run_variants_on_the_emulator(api, oracle, rng):
     for op in ("MAXANDARGMAX", "ARGMAX", "MAX"):
         check(api, oracle, op, z, [1], expect={"onerun": 1, "lazy": 1, "group": 32})
     check(api, oracle, "MINANDARGMIN", -z, [1], expect={"onerun": 1, "lazy": 1})
-    check(api, oracle, "MAXANDARGMAX", ties(rng, (300, 24)), [1], expect={"onerun": 1, "lazy": 1, "group": 2})
-    check(api, oracle, "MINANDARGMIN", rng.integers(-5, 5, (100, 200)).astype(np.int32), [1],
+    check(api, oracle, "MINANDARGMIN", rng.integers(-5, 5, (100, 1024)).astype(np.int32), [1],
           expect={"onerun": 1, "lazy": 1})
     # rows that do not start on a 16-byte boundary (49 floats), fp64, int8 -> int64
     check(api, oracle, "SUM", ties(rng, (77, 49)), [1], expect={"onerun": 1, "vec": 1})

@@ -86,9 +86,12 @@ def test_named_configurations_get_the_intended_kernels(api):
     # short runs: part of a warp per output, several outputs at once, 3 CTAs per SM
     err, p = plan(api, "SUM", np.float32, [1 << 21, 32], c_strides([1 << 21, 32], 4), [1])
     assert err == 0 and p["onerun"] == 1 and p["group"] == 2 and p["mu"] == 2 and p["gx"] == 148 * 3
-    # ARGMAX over 512-element rows: one run per output, 32 lanes, values-only scan
-    err, p = plan(api, "ARGMAX", np.float32, [1 << 17, 512], c_strides([1 << 17, 512], 4), [1])
+    # ARGMAX over 1024-element rows: one run per output, 32 lanes x 8 vectors, values-only scan;
+    # 512-element rows (4 vectors per lane) compare pairs element by element
+    err, p = plan(api, "ARGMAX", np.float32, [1 << 16, 1024], c_strides([1 << 16, 1024], 4), [1])
     assert err == 0 and p["onerun"] == 1 and p["group"] == 32 and p["lazy"] == 1
+    err, p = plan(api, "ARGMAX", np.float32, [1 << 17, 512], c_strides([1 << 17, 512], 4), [1])
+    assert err == 0 and p["onerun"] == 1 and p["group"] == 32 and p["lazy"] == 0
     # an unaligned base drops to scalar loads
     err, p = plan(api, "SUM", np.float32, [4096, 4096], c_strides([4096, 4096], 4), [1], base=0x7f0000000004)
     assert err == 0 and p["vec"] == 1
