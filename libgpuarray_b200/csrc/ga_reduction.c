@@ -478,10 +478,12 @@ static int all_multiple(const long long *v, unsigned n, long long m) {
 /* Tuning for experiments: GPUARRAY_B200_RD="ctas_per_sm,seg_vectors,cta_min_vectors,
  * cols_ctas_per_sm (0 = the lanes rule),onerun_ctas_per_sm,onerun_loads_per_lane,
  * onerun_outputs_at_once,lazy_index (0/1),lazy_min_vectors_per_lane,cols_row_lanes (0 = rule),
- * lean_rows (0/1),cols_early_rows,lazy_min_vectors_per_lane_short_runs". The
+ * lean_rows (0/1),cols_early_rows,lazy_min_vectors_per_lane_short_runs,
+ * outputs_per_sm_from_which_a_warp_owns_an_output,
+ * warps_per_sm_wanted_when_2_or_4_warps_share_a_run (0 = a CTA per run)". The
  * defaults are the best of sweeps on a B200. */
 static unsigned rd_cols_ctas_per_sm = 0, rd_cols_by = 0;
-static unsigned rd_simple = 1, rd_cols_early = 4, rd_lazy_onerun_min = 8;
+static unsigned rd_simple = 1, rd_cols_early = 4, rd_lazy_onerun_min = 8, rd_warp_rows_per_sm = 16, rd_subcta = 24;
 static unsigned rd_onerun_ctas_per_sm = 3, rd_onerun_lpl = 4, rd_onerun_mu = 0, rd_lazy = 1, rd_lazy_min = 32;
 
 static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_bytes) {
@@ -491,9 +493,10 @@ static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_
   if (!parsed) {
     const char *env = getenv("GPUARRAY_B200_RD");
     if (env != NULL)
-      sscanf(env, "%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm,
+      sscanf(env, "%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm,
              &rd_onerun_ctas_per_sm, &rd_onerun_lpl, &rd_onerun_mu, &rd_lazy, &rd_lazy_min,
-             &rd_cols_by, &rd_simple, &rd_cols_early, &rd_lazy_onerun_min);
+             &rd_cols_by, &rd_simple, &rd_cols_early, &rd_lazy_onerun_min, &rd_warp_rows_per_sm,
+             &rd_subcta);
     *warp_bytes = t_warp;
     if (t_ctas == 0) t_ctas = 32;
     if (t_seg == 0) t_seg = 8;
@@ -580,9 +583,17 @@ static int rd_plan(const rd_plan_in *in, rd_layout *L, rd_variant *want, unsigne
       want->flat = nvrow < 16;
       want->mu = want->flat ? 1 : nload <= 64 ? 4 : nload <= 256 ? 2 : 1;
       if (nvrow >= cta_min_vecs) want->group = RD_THREADS;
-      else if (L->nf_total >= (unsigned long long)in->num_sms * 16) want->group = 32;
-      else if (L->nf_total >= (unsigned long long)in->num_sms * 4 && nvrow >= 1024)
-        want->group = RD_THREADS;
+      else if (L->nf_total >= (unsigned long long)in->num_sms * rd_warp_rows_per_sm) want->group = 32;
+      else if (L->nf_total >= (unsigned long long)in->num_sms * 4 && nvrow >= 1024) {
+        /* A moderate number of long runs: a warp per run would leave the SMs with too few
+         * warps to cover DRAM latency, a CTA per run makes every CTA short-lived. Two or
+         * four warps share a run when that gives at least 24 warps per SM. Measured on
+         * B200, MAXANDARGMAX of fp32 (2048, 32000) (the 8-GPU shard of the headline):
+         * 54.5 us with a warp or a CTA per row; see the profile notes for the shared form. */
+        unsigned g = 64;
+        while (g < RD_THREADS && L->nf_total * (g / 32) < (unsigned long long)in->num_sms * rd_subcta) g *= 2;
+        want->group = (int)(rd_subcta ? g : RD_THREADS);
+      }
       else {
         /* warps, unless long runs would leave them either too few or with
          * shares too short to be worth a ticket (see the cap below) */
@@ -596,7 +607,7 @@ static int rd_plan(const rd_plan_in *in, rd_layout *L, rd_variant *want, unsigne
                                         L->nf_total * s_w < (unsigned long long)in->num_sms * 16))
                          ? RD_THREADS : 32;
       }
-      if (want->group == RD_THREADS) want->flat = 0, want->mu = 1;
+      if (want->group > 32) want->flat = 0, want->mu = 1;
       gpb = RD_THREADS / (unsigned)want->group;
       /* measured on B200: whole-CTA groups run best as a few long-lived CTAs
        * per SM, warp groups as many (a full complement of resident warps) */

@@ -39,7 +39,7 @@
  *   GA_RD_LOAD(raw) GA_RD_STORE(acc) GA_RD_MAP(x) GA_RD_COMBINE(a,b)
  *   GA_RD_IDENT GA_RD_BETTER(b,a) GA_RD_KIND GA_RD_ISFLOAT
  *   GA_RD_WRITE_VAL GA_RD_WRITE_IDX GA_RD_IDX_T GA_RD_VEC GA_RD_THREADS
- *   GA_RD_TPO GA_RD_BY GA_RD_GROUP (rows: 32 or GA_RD_THREADS) GA_RD_FLAT
+ *   GA_RD_TPO GA_RD_BY GA_RD_GROUP (rows: 32, 64, 128 or GA_RD_THREADS) GA_RD_FLAT
  */
 #include "cluda.h"
 
@@ -210,6 +210,23 @@ static __device__ __forceinline__ ga__state ga__block_reduce(ga__state s, ga__st
   if (tid < 32) {
     s = tid < (nthreads >> 5) ? sm[tid] : ga__init();
     s = ga__warp_reduce(s);
+  }
+  return s;
+}
+
+/* A group of W consecutive warps of the CTA (W a power of two; W = all of them gives the
+ * CTA-wide reduction) combines in a fixed order; the result is valid in the group's first
+ * thread. Every thread of the CTA must call it (one barrier inside; the caller places
+ * another before `sm` is reused). `sm` holds one state per warp of the CTA. */
+template <int W>
+static __device__ __forceinline__ ga__state ga__group_reduce(ga__state s, ga__state *sm,
+                                                             const unsigned tid) {
+  s = ga__warp_reduce(s);
+  if ((tid & 31u) == 0) sm[tid >> 5] = s;
+  __syncthreads();
+  if (tid % (32 * W) == 0) {
+#pragma unroll
+    for (int k = 1; k < W; k++) ga__merge(s, sm[(tid >> 5) + k]);
   }
   return s;
 }
@@ -450,7 +467,7 @@ static __device__ __forceinline__ void ga__row_decode(const ga__rd_layout &L, co
   }
 }
 
-/* GA_RD_GROUP threads (a warp or the whole CTA) share one work item, i.e. one
+/* GA_RD_GROUP threads (a warp, 2 or 4 warps, or the whole CTA) share one work item, i.e. one
  * (output, split) pair, and walk its units (a unit = one contiguous run, or
  * one segment of a long run) one after the other; inside a unit each thread
  * strides 128-bit loads, so the inner loop is a pointer, a counter and the
@@ -480,7 +497,7 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
   ga__grid_dependency_sync();
 #if GA_RD_GROUP > 32
   __shared__ ga__state sm[32];
-  __shared__ int sm_last;
+  __shared__ int sm_last[GA_RD_THREADS / GA_RD_GROUP]; /* one slot per group of the CTA */
 #endif
   const ga__u64 nwork = L.nf_total * L.splits;
   const int nro = (int)L.nr - 1; /* reduced dims outside the contiguous run */
@@ -785,7 +802,7 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
 #pragma unroll
     for (int j = 1; j < GA_RD_VEC; j++) ga__merge(st[0], st[j]);
 #if GA_RD_GROUP > 32
-    const ga__state tot = ga__block_reduce(st[0], sm, threadIdx.x, GA_RD_THREADS);
+    const ga__state tot = ga__group_reduce<GA_RD_GROUP / 32>(st[0], sm, threadIdx.x);
 #else
     const ga__state tot = ga__warp_reduce(st[0]);
 #endif
@@ -802,9 +819,9 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
         last = ga__take_ticket(&tickets[o], (unsigned int)L.splits) ? 1 : 0;
       }
 #if GA_RD_GROUP > 32
-      if (lane == 0) sm_last = last;
+      if (lane == 0) sm_last[threadIdx.x / GA_RD_GROUP] = last;
       __syncthreads();
-      last = sm_last;
+      last = sm_last[threadIdx.x / GA_RD_GROUP];
 #else
       last = __shfl_sync(0xffffffffu, last, 0);
 #endif
@@ -815,7 +832,7 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
           ga__merge(fin, ga__get_partial(L, pval, pidx, sp, o));
       }
 #if GA_RD_GROUP > 32
-      fin = ga__block_reduce(fin, sm, threadIdx.x, GA_RD_THREADS);
+      fin = ga__group_reduce<GA_RD_GROUP / 32>(fin, sm, threadIdx.x);
       __syncthreads();
 #else
       fin = ga__warp_reduce(fin);

@@ -179,6 +179,10 @@ def test_rows_kernel_variants_on_the_emulator(api, oracle, rng):
     p = check(api, oracle, "SUM", w, [0], sms=1)
     assert p["group"] == 256 and p["splits"] > 1
     check(api, oracle, "ARGMIN", w, [0], sms=1)
+    # a moderate number of long rows: two and four warps share a row (one barrier, fixed order)
+    check(api, oracle, "MAXANDARGMAX", ties(rng, (30, 4100)), [1], sms=2, expect={"group": 64, "splits": 1})
+    check(api, oracle, "SUM", ties(rng, (20, 4101)), [1], sms=2, expect={"group": 128})
+    check(api, oracle, "MINANDARGMIN", ties(rng, (20, 16500)), [1], sms=2, expect={"group": 128, "lazy": 1})
     # scalar loads: a base that is not 16-byte aligned
     big = ties(rng, (3, 4100))
     u = big[:, 1:]

@@ -44,14 +44,14 @@ def check_invariants(p, itemsize, kind_pair):
     assert p["splits"] >= 1
     assert p["vec"] in (1, 2, 4, 8, 16) and p["vec"] * itemsize <= 16
     if p["shape"] == SHAPE_ROWS:
-        assert p["group"] in (1, 2, 4, 8, 16, 32, 256)
+        assert p["group"] in (1, 2, 4, 8, 16, 32, 64, 128, 256)
         assert p["seg"] >= 1 and p["nseg"] >= 1 and p["seg"] < 2 ** 31
         assert p["splits"] <= max(p["units"], 1)
         if p["onerun"]:
             assert p["units"] == 1 and p["splits"] == 1 and p["mu"] in (2, 4) and p["group"] <= 32
         else:
-            assert p["group"] in (32, 256)
-        if p["group"] == 256:
+            assert p["group"] in (32, 64, 128, 256)
+        if p["group"] > 32:
             assert p["flat"] == 0 and p["mu"] == 1
         if p["lazy"]:                                 # values-only scan: long runs, or one short run
             assert kind_pair and not p["flat"] and (p["onerun"] or p["mu"] == 1) and p["vec"] > 1 or \
@@ -69,6 +69,11 @@ def test_named_configurations_get_the_intended_kernels(api):
     err, p = plan(api, "MAXANDARGMAX", np.float32, [16384, 32000], c_strides([16384, 32000], 4), [1])
     assert err == 0 and p["shape"] == SHAPE_ROWS and p["group"] == 32 and p["splits"] == 1
     assert p["vec"] == 4 and p["lazy"] == 1 and p["gx"] == 2048
+    # the headline's 8-GPU shard: 2048 rows, two warps per row (27 warps per SM), values-only scan
+    err, p = plan(api, "MAXANDARGMAX", np.float32, [2048, 32000], c_strides([2048, 32000], 4), [1])
+    assert err == 0 and p["group"] == 64 and p["lazy"] == 1 and p["splits"] == 1 and p["gx"] == 512
+    err, p = plan(api, "MAXANDARGMAX", np.float32, [1024, 32000], c_strides([1024, 32000], 4), [1])
+    assert err == 0 and p["group"] == 128 and p["gx"] == 512
     # cfg2: rows and columns
     err, p = plan(api, "SUM", np.float32, [4096, 4096], c_strides([4096, 4096], 4), [1])
     assert err == 0 and p["shape"] == SHAPE_ROWS and p["splits"] == 1 and p["gx"] == 512
