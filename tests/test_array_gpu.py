@@ -153,3 +153,56 @@ def test_arrays_that_reach_outside_their_buffer_are_refused_on_the_host(api, ctx
     assert float(tot.to_numpy()) == float(np.arange(16, dtype=np.float32).sum())
     ge(real, out)
     assert (out.to_numpy() == np.arange(4096, dtype=np.float32) + 1).all()
+
+
+def test_fresh_expression_compiles_into_an_empty_cache(api, tmp_path):
+    """NVRTC JIT on the GPU box itself: a context whose cubin directory is empty builds a new
+    expression (and a reduction variant), runs it, and leaves the cubins behind; a second
+    context on the same directory loads them without compiling."""
+    import os
+    cache = tmp_path / "cubins"
+    cache.mkdir()
+    R, W = api.GE_READ, api.GE_WRITE
+    x = np.arange(1000, dtype=np.float32)
+    for attempt in range(2):
+        c = api.Context(0, kernel_cache=str(cache))
+        ge = api.GpuElemwise(c, "o = a * 3.25f + 41.0f", [("a", np.float32, R), ("o", np.float32, W)], nd=1)
+        ga = api.GpuArray.from_numpy(c, x)
+        go = api.GpuArray.empty(c, x.shape, np.float32)
+        ge(ga, go)
+        assert (go.to_numpy() == x * np.float32(3.25) + np.float32(41.0)).all()
+        d = api.GpuArray.empty(c, (), np.float32)
+        api.GpuReduction(c, api.GA_REDUCE_MAX, np.float32)(d, None, ga, [0])
+        assert float(d.to_numpy()) == 999.0
+        names = sorted(os.listdir(cache))
+        assert len(names) >= 2 and all(n.endswith(".cubin") for n in names)
+        if attempt == 0:
+            first = names
+        else:
+            assert names == first                      # nothing new was compiled
+        ge.free()
+        c.close()
+
+
+def test_operator_construction_on_a_module_cache_hit_is_cheap(api, ctx):
+    """pygpu builds a new GpuElemwise for every Python operator it evaluates
+    (pygpu/elemwise.py:35,76,94); after the first one the kernel is found in the context's
+    module cache. Budget: 50 us per GpuElemwise_new + GpuElemwise_free pair (measured on the
+    B200 box through a C caller: 4.1 us; through ctypes a little more)."""
+    import ctypes
+    import time
+    L = api.lib()
+    args = (api._ElemwiseArg * 3)()
+    for i, (nm, fl) in enumerate(((b"a", api.GE_READ), (b"b", api.GE_READ), (b"o", api.GE_WRITE))):
+        args[i].name, args[i].typecode, args[i].flags = nm, api.GA_FLOAT, fl
+    p = L.GpuElemwise_new(ctx.ptr, b"", b"o = a * b + 7.5f", 3, args, 1, 0)
+    assert p
+    L.GpuElemwise_free(ctypes.c_void_p(p))
+    best = 1e9
+    for _ in range(5):
+        t0 = time.perf_counter()
+        for _ in range(200):
+            q = L.GpuElemwise_new(ctx.ptr, b"", b"o = a * b + 7.5f", 3, args, 1, 0)
+            L.GpuElemwise_free(ctypes.c_void_p(q))
+        best = min(best, (time.perf_counter() - t0) / 200)
+    assert best < 50e-6, best
