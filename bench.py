@@ -461,10 +461,12 @@ def sharded_configs(api, ctx, torch, dist, stream, rank, world, host_slab, t1_cf
     cfg3_strong: the seed-2 (16384, 32000) logits, rank r owning rows
       [r*16384/world, (r+1)*16384/world); no communication.
     cfg5_*_sharded: fp64 (2048, 1024, 1024), rank r owning 2048/world leading
-      planes; per-GPU partial of the final shape, then ONE gpucomm all-reduce
-      (NCCL, same stream). Reported: kernel + all-reduce, the kernel alone, the
-      all-reduce alone, and the same reduction over all 2048 planes on one GPU
-      (x_vs_1gpu = that time / the sharded time).
+      planes, through GpuReduction_call_sharded: per-GPU partial of the final
+      shape, then one exchange kernel over the communicator's peer windows
+      (or one gpucomm all-reduce where those are unavailable). Reported: the
+      whole call, the kernel alone, the same with an NCCL all-reduce instead,
+      that all-reduce alone, and the same reduction over all 2048 planes on one
+      GPU (x_vs_1gpu = that time / the sharded time).
     cfg5_f64_maxandargmax_axes02_sharded: (value, global first index) over the
       sharded extent through GpuReduction_call_sharded."""
     out = {}
@@ -532,19 +534,28 @@ def sharded_configs(api, ctx, torch, dist, stream, rank, world, host_slab, t1_cf
         gr = api.GpuReduction(ctx, rop, np.float64)
 
         def both():
+            api.reduction_call_sharded(gr, comm, res, None, g5, axes, rank * planes, 2048)
+
+        def both_nccl():
             gr(part, None, g5, axes)
             comm.all_reduce(part, res, cop)
         us_both = span(both, 10)
+        us_nccl = span(both_nccl, 10)
         us_kernel = span(lambda: gr(part, None, g5, axes), 10)
         us_comm = span(lambda: comm.all_reduce(part, res, cop), 20)
         us_one = span(lambda: gr(res, None, g_full, axes), 4)
+        state = comm.peer_state()
         out["cfg5_f64_%s_sharded" % name] = {
             "us": round(us_both, 2), "GB/s": round(total_bytes / us_both / 1e3, 1),
             "kernel_only_us": round(us_kernel, 2), "all_reduce_only_us": round(us_comm, 2),
+            "with_nccl_all_reduce_us": round(us_nccl, 2),
             "t_1gpu_us": round(us_one, 2), "x_vs_1gpu": round(us_one / us_both, 3),
             "frac_nominal_8TBs_x_gpus": round(total_bytes / us_both / 1e3 / (NOMINAL_HBM_GBS * world), 3),
-            "planes_per_gpu": planes, "collective": "gpucomm_all_reduce (NCCL), %d B" % res.nbytes,
-            "scaling": "strong"}
+            "planes_per_gpu": planes,
+            "collective": ("GpuReduction_call_sharded: one exchange kernel over peer (NVLink) windows, %d B"
+                           if state[0] == 1 else
+                           "GpuReduction_call_sharded: gpucomm_all_reduce (NCCL), %d B") % res.nbytes,
+            "peer_windows": state[0] == 1, "peer_windows_reason": state[1], "scaling": "strong"}
         gr.free()
 
     # ---- (value, first global index) with the reduced extent sharded
@@ -562,8 +573,10 @@ def sharded_configs(api, ctx, torch, dist, stream, rank, world, host_slab, t1_cf
             "x_vs_1gpu": round(us_one / us_both, 3),
             "frac_nominal_8TBs_x_gpus": round(total_bytes / us_both / 1e3 / (NOMINAL_HBM_GBS * world), 3),
             "planes_per_gpu": planes,
-            "collective": "all-reduce of the value, candidate-index kernel, all-reduce MIN of the index",
-            "scaling": "strong"}
+            "collective": ("one exchange kernel over peer (NVLink) windows: better value, then lower index"
+                           if comm.peer_state()[0] == 1 else
+                           "all-reduce of the value, candidate-index kernel, all-reduce MIN of the index"),
+            "peer_windows": comm.peer_state()[0] == 1, "scaling": "strong"}
         gr.free()
     ctx.sync()
     comm.free()

@@ -143,6 +143,21 @@ GPUARRAY_PUBLIC int gpuarray_b200_mapreduction_plan(int out_tc, unsigned int n,
                                                     unsigned long long *out, void *layout,
                                                     size_t cap, size_t *used);
 
+/* State of a communicator's peer-memory windows, through which
+ * GpuReduction_call_sharded combines the ranks' partial results with one
+ * kernel per GPU (every rank stores its partials into all peers' windows over
+ * NVLink and folds what arrives). Returns 0 before the first sharded
+ * reduction, 1 when the windows are in use, -1 when they could not be set up
+ * on every rank (*reason, if not NULL, then points to a text inside the
+ * communicator) and gpucomm_all_reduce is used instead. *timed_out, if not
+ * NULL, is non-zero once a kernel gave up waiting for a rank
+ * (GPUARRAY_B200_PEER_TIMEOUT_MS, default 10000); sharded calls on that
+ * communicator then return GA_COMM_ERROR. GPUARRAY_B200_NO_PEER_WINDOW=1
+ * keeps the windows off. No counterpart in the reference. */
+struct _gpucomm;
+GPUARRAY_PUBLIC int gpuarray_b200_comm_peer_state(struct _gpucomm *comm, const char **reason,
+                                                  unsigned int *timed_out);
+
 /* Sum of n contiguous float32 values on the current device WITHOUT allocating
  * anything: no cudaMalloc / cudaFree, no library workspace. (No counterpart in
  * the reference, whose reductions allocate per call.) It is for callers that

@@ -79,17 +79,30 @@ GPUARRAY_PUBLIC int GpuReduction_call(const GpuReduction *gr, GpuArray *d0, GpuA
  * [shard_lo, shard_lo + s0->dimensions[shard_axis]) of an axis of extent
  * shard_global, the other ranks of `comm` hold the rest. Every rank calls it
  * with its own shard and receives the result of the WHOLE array in its
- * destinations: per-GPU partial, then gpucomm_all_reduce on the context's
- * stream (the call site of src/gpuarray_collectives_cuda_nccl.c:286-316), no
- * host round trip.
- *  - SUM, PROD, PRODNZ, ALL, ANY: one all-reduce (sum / prod / min / max) of the
- *    partial. AND, OR, XOR: GA_UNSUPPORTED_ERROR (the collectives have no
- *    bitwise operator).
+ * destinations, everything enqueued on the context's stream with no host
+ * round trip: the per-GPU kernel, then ONE exchange kernel per GPU that stores
+ * the partial results into every peer's window of device memory over NVLink
+ * and folds what the peers stored (csrc/templates/ga_exchange.cuh). The
+ * windows are set up by the first such call on a communicator, which is
+ * therefore collective and synchronises once. Where they cannot be set up on
+ * every rank (ranks in one process or on several hosts, more than 16 ranks,
+ * results beyond 1 MiB per rank, GPUARRAY_B200_NO_PEER_WINDOW=1) the partials
+ * are combined with gpucomm_all_reduce instead (the call site of
+ * src/gpuarray_collectives_cuda_nccl.c:286-316).
+ *  - SUM, PROD, PRODNZ, ALL, ANY: the fold runs in rank order, so every rank
+ *    ends with the same bits (one all-reduce sum / prod / min / max on the
+ *    fallback path). AND, OR, XOR: GA_UNSUPPORTED_ERROR (the collectives have
+ *    no bitwise operator).
  *  - MIN, MAX and the ARG variants: the index written is the flat index in the
- *    whole reduced extent (shard offset and global radix included); ranks are
- *    combined with an all-reduce MAX/MIN of the value followed by an all-reduce
- *    MIN of a candidate index, so the lowest global index wins ties exactly as
- *    on one GPU, the NaN-first rule and signed zeros included.
+ *    whole reduced extent (shard offset and global radix included); the better
+ *    value wins, the lower global index among equal values, so ties go exactly
+ *    where they go on one GPU, the NaN-first rule and signed zeros included
+ *    (on the fallback path: an all-reduce MAX/MIN of the value followed by an
+ *    all-reduce MIN of a candidate index, same result).
+ * A rank that does not arrive within GPUARRAY_B200_PEER_TIMEOUT_MS (default
+ * 10000) makes the waiting kernels give up: they return, and later sharded
+ * calls on the communicator fail with GA_COMM_ERROR
+ * (gpuarray_b200_comm_peer_state in b200.h).
  * comm may be NULL (one rank: no collective), which also serves to test the
  * path on one GPU. <gpuarray/collectives.h> declares gpucomm. */
 struct _gpucomm;

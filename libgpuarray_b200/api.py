@@ -685,6 +685,17 @@ class GpuComm:
         _check(self.ctx.ptr, lib().GpuArray_all_gather(ctypes.byref(src.ga), ctypes.byref(dst.ga),
                                                        self.ptr))
 
+    def peer_state(self):
+        """(state, reason, timed_out) of the communicator's peer-memory windows: state 0 before
+        the first sharded reduction, 1 in use, -1 unavailable (reason says why; NCCL all-reduces
+        are used instead); timed_out != 0 once a kernel gave up waiting for a rank."""
+        f = lib().gpuarray_b200_comm_peer_state
+        f.restype = ctypes.c_int
+        f.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(ctypes.c_uint)]
+        reason, timed = ctypes.c_char_p(), ctypes.c_uint()
+        st = f(self.ptr, ctypes.byref(reason), ctypes.byref(timed))
+        return st, (reason.value or b"").decode(errors="replace"), int(timed.value)
+
     def free(self):
         if self.ptr is not None:
             lib().gpucomm_free(self.ptr)

@@ -11,6 +11,7 @@
  * per-GPU partial results when the reduced extent is sharded. */
 #include <dlfcn.h>
 #include <limits.h>
+#include <unistd.h>
 #include "private.h"
 
 /* The few NCCL declarations used, so that no NCCL header is needed to build. */
@@ -68,9 +69,39 @@ static int load_nccl(ga_error_rec *e) {
   return GA_NO_ERROR;
 }
 
+/* Peer window: see the head of templates/ga_exchange.cuh for the layout and
+ * the protocol. The constants mirror the GA_XC_* defines there. */
+#define XC_MAX_RANKS 16
+#define XC_MAX_CTAS 64
+#define XC_DATA_OFF 32768
+#define XC_THREADS 256
+#define XC_SLOT_BYTES ((size_t)1 << 20)
+
+typedef struct xc_kernel {
+  int pair, op, tc;
+  ga_function fn;
+  struct xc_kernel *next;
+} xc_kernel;
+
+typedef struct xc_window { /* a window no communicator uses any more, kept for the next one */
+  CUdeviceptr ptr;
+  size_t bytes;
+  struct xc_window *next;
+} xc_window;
+
 struct _gpucomm {
   gpucontext *ctx; /* MUST stay first (reference src/private.h:86-88) */
   ncclComm_t c;
+  int ndev, rank;
+  int win_state;                 /* 0 not tried yet, 1 in use, -1 unavailable (win_reason) */
+  char win_reason[200];
+  CUdeviceptr win[XC_MAX_RANKS]; /* [rank]: own allocation; others: imported mappings */
+  size_t win_bytes;
+  unsigned long long seq;        /* exchanges enqueued so far */
+  unsigned long long timeout_ns;
+  unsigned int *status_host;     /* pinned, mapped: set by a kernel whose wait ran out */
+  CUdeviceptr status_dev;
+  xc_kernel *kernels;
 };
 
 static int nccl_fail(gpucontext *ctx, const char *call, ncclResult_t r) {
@@ -125,6 +156,8 @@ int gpucomm_new(gpucomm **out, gpucontext *ctx, gpucommCliqueId comm_id, int nde
   comm = calloc(1, sizeof(*comm));
   if (comm == NULL) return ga_err_sys(ctx->err, "calloc");
   comm->ctx = ctx;
+  comm->ndev = ndev;
+  comm->rank = rank;
   memcpy(id.internal, comm_id.internal, GA_COMM_ID_BYTES);
   ga_ctx_enter(ctx);
   r = nccl.CommInitRank(&comm->c, ndev, id, rank);
@@ -138,12 +171,15 @@ int gpucomm_new(gpucomm **out, gpucontext *ctx, gpucommCliqueId comm_id, int nde
   return GA_NO_ERROR;
 }
 
+static void peer_window_release(gpucomm *comm);
+
 void gpucomm_free(gpucomm *comm) {
   gpucontext *ctx;
   if (comm == NULL) return;
   ctx = comm->ctx;
   ga_ctx_enter(ctx);
   ga_cu.p_cuStreamSynchronize(ctx->s);
+  peer_window_release(comm);
   nccl.CommDestroy(comm->c);
   ga_ctx_exit(ctx);
   free(comm);
@@ -269,6 +305,313 @@ int gpucomm_all_gather(gpudata *src, size_t offsrc, gpudata *dest, size_t offdes
   NCCL_ENQUEUE("ncclAllGather",
                nccl.AllGather((const void *)(src->ptr + offsrc), (void *)(dest->ptr + offdest),
                               count, t, comm->c, ctx->s));
+}
+
+/* ------------------------------------------------------------ peer window */
+
+/* What the ranks tell one another while the windows are set up (one
+ * all-gather of 128 bytes per rank over the communicator itself). */
+typedef union xc_hello {
+  struct {
+    CUipcMemHandle handle;
+    int ok;                      /* this rank allocated and exported its window */
+    int pid;
+    unsigned long long host;     /* hash of the host name: IPC handles stay on one node */
+    char pci[16];                /* two ranks on one GPU cannot wait for each other */
+  } f;
+  char bytes[128];
+} xc_hello;
+
+static int env_off(const char *name) {
+  const char *v = getenv(name);
+  return v != NULL && v[0] != '\0' && v[0] != '0';
+}
+
+/* Frees the windows parked on a context (context teardown). */
+void ga_peer_windows_free(gpucontext *ctx) {
+  xc_window *w = (xc_window *)ctx->peer_windows, *n;
+  ctx->peer_windows = NULL;
+  for (; w != NULL; w = n) {
+    n = w->next;
+    ga_cu.p_cuMemFree(w->ptr);
+    free(w);
+  }
+}
+
+/* Un-maps the peers' windows and parks the own one on the context: a peer may
+ * still have it mapped (it closes its mapping in its own gpucomm_free, at a
+ * time of its choosing), and freeing exported memory under a live mapping is
+ * undefined; the next communicator of the context takes it over instead. */
+static void peer_window_release(gpucomm *comm) {
+  gpucontext *ctx = comm->ctx;
+  xc_kernel *k, *kn;
+  int p;
+  if (comm->win_state == 1) {
+    for (p = 0; p < comm->ndev; p++)
+      if (p != comm->rank && comm->win[p] != 0) ga_cu.p_cuIpcCloseMemHandle(comm->win[p]);
+  }
+  if (comm->win[comm->rank] != 0) {
+    xc_window *w = malloc(sizeof(*w));
+    if (w != NULL) {
+      w->ptr = comm->win[comm->rank];
+      w->bytes = comm->win_bytes;
+      w->next = (xc_window *)ctx->peer_windows;
+      ctx->peer_windows = w;
+    } /* else: leaked rather than freed under a peer's mapping */
+  }
+  memset(comm->win, 0, sizeof(comm->win));
+  if (comm->status_host != NULL) ga_cu.p_cuMemFreeHost(comm->status_host);
+  comm->status_host = NULL;
+  for (k = comm->kernels; k != NULL; k = kn) {
+    kn = k->next;
+    free(k);
+  }
+  comm->kernels = NULL;
+  comm->win_state = -1;
+}
+
+static void peer_window_refuse(gpucomm *comm, const char *fmt, const char *a, int b) {
+  snprintf(comm->win_reason, sizeof(comm->win_reason), fmt, a, b);
+}
+
+/* COLLECTIVE over the communicator (every rank reaches it in its first sharded
+ * reduction): allocates this rank's window, exchanges IPC handles through the
+ * communicator, maps the peers' windows, and agrees with all ranks on the
+ * outcome, so that either every rank uses the windows or none does. */
+static int peer_window_setup(gpucomm *comm) {
+  gpucontext *ctx = comm->ctx;
+  const int n = comm->ndev, me = comm->rank;
+  const size_t bytes = XC_DATA_OFF + 2 * (size_t)n * XC_SLOT_BYTES;
+  xc_hello mine, *all = NULL;
+  CUdeviceptr stage = 0;
+  CUresult cr;
+  ncclResult_t nr;
+  char host[256];
+  int p, q, agreed = 1, opened = 1, err = GA_NO_ERROR;
+  const char *t;
+
+  comm->win_state = -1;
+  comm->win_reason[0] = '\0';
+  memset(&mine, 0, sizeof(mine));
+  mine.f.pid = (int)getpid();
+  memset(host, 0, sizeof(host));
+  gethostname(host, sizeof(host) - 1);
+  mine.f.host = ga_hash64(host, strlen(host), 17);
+  memcpy(mine.f.pci, ctx->pci_id, sizeof(mine.f.pci));
+  t = getenv("GPUARRAY_B200_PEER_TIMEOUT_MS");
+  comm->timeout_ns = (t != NULL && atoll(t) > 0 ? (unsigned long long)atoll(t) : 10000ULL) * 1000000ULL;
+
+  ga_ctx_enter(ctx);
+  if (n < 2 || n > XC_MAX_RANKS) {
+    peer_window_refuse(comm, "%s%d ranks", "", n);
+  } else if (env_off("GPUARRAY_B200_NO_PEER_WINDOW")) {
+    peer_window_refuse(comm, "%s (rank %d)", "switched off by GPUARRAY_B200_NO_PEER_WINDOW", me);
+  } else {
+    xc_window **pw = (xc_window **)&ctx->peer_windows, *w;
+    for (; (w = *pw) != NULL; pw = &w->next)
+      if (w->bytes == bytes) break;
+    if (w != NULL) {
+      *pw = w->next;
+      comm->win[me] = w->ptr;
+      free(w);
+      cr = CUDA_SUCCESS;
+    } else {
+      cr = ga_cu.p_cuMemAlloc(&comm->win[me], bytes);
+    }
+    if (cr == CUDA_SUCCESS) {
+      comm->win_bytes = bytes;
+      cr = ga_cu.p_cuMemsetD8Async(comm->win[me], 0, XC_DATA_OFF, ctx->s);
+    }
+    if (cr == CUDA_SUCCESS) cr = ga_cu.p_cuIpcGetMemHandle(&mine.f.handle, comm->win[me]);
+    if (cr == CUDA_SUCCESS)
+      cr = ga_cu.p_cuMemHostAlloc((void **)&comm->status_host, 64, CU_MEMHOSTALLOC_DEVICEMAP);
+    if (cr == CUDA_SUCCESS) {
+      memset(comm->status_host, 0, 64);
+      cr = ga_cu.p_cuMemHostGetDevicePointer(&comm->status_dev, comm->status_host, 0);
+    }
+    if (cr == CUDA_SUCCESS) mine.f.ok = 1;
+    else peer_window_refuse(comm, "%s: CUDA error %d", "window allocation or export", (int)cr);
+  }
+
+  /* round 1: everyone's hello */
+  all = calloc((size_t)n, sizeof(*all));
+  if (all == NULL) { err = ga_err_sys(ctx->err, "calloc"); goto out; }
+  cr = ga_cu.p_cuMemAlloc(&stage, sizeof(xc_hello) * (size_t)(n + 1));
+  if (cr != CUDA_SUCCESS) { err = ga_err_cuda(ctx->err, "cuMemAlloc", cr); goto out; }
+  cr = ga_cu.p_cuMemcpyHtoDAsync(stage, &mine, sizeof(mine), ctx->s);
+  if (cr != CUDA_SUCCESS) { err = ga_err_cuda(ctx->err, "cuMemcpyHtoDAsync", cr); goto out; }
+  nr = nccl.AllGather((const void *)stage, (void *)(stage + sizeof(xc_hello)), sizeof(xc_hello),
+                      ncclUint8, comm->c, ctx->s);
+  if (nr != ncclSuccess) { err = nccl_fail(ctx, "ncclAllGather", nr); goto out; }
+  cr = ga_cu.p_cuMemcpyDtoHAsync(all, stage + sizeof(xc_hello), sizeof(xc_hello) * (size_t)n, ctx->s);
+  if (cr == CUDA_SUCCESS) cr = ga_cu.p_cuStreamSynchronize(ctx->s);
+  if (cr != CUDA_SUCCESS) { err = ga_err_cuda(ctx->err, "peer window hello", cr); goto out; }
+  for (p = 0; p < n; p++) {
+    if (!all[p].f.ok) {
+      agreed = 0;
+      if (comm->win_reason[0] == '\0') peer_window_refuse(comm, "%srank %d has no window", "", p);
+    }
+    if (all[p].f.host != mine.f.host) {
+      agreed = 0;
+      if (comm->win_reason[0] == '\0') peer_window_refuse(comm, "%srank %d is on another host", "", p);
+    }
+    for (q = 0; q < p; q++)
+      if (memcmp(all[p].f.pci, all[q].f.pci, sizeof(mine.f.pci)) == 0 || all[p].f.pid == all[q].f.pid) {
+        agreed = 0;
+        if (comm->win_reason[0] == '\0')
+          peer_window_refuse(comm, "%srank %d shares a GPU or a process with another rank", "", p);
+      }
+  }
+  /* round 2: map the peers; then agree on whether everyone could */
+  if (agreed) {
+    for (p = 0; p < n && opened; p++) {
+      if (p == me) continue;
+      cr = ga_cu.p_cuIpcOpenMemHandle(&comm->win[p], all[p].f.handle, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS);
+      if (cr != CUDA_SUCCESS) {
+        comm->win[p] = 0;
+        opened = 0;
+        peer_window_refuse(comm, "%s of rank %d failed", "cuIpcOpenMemHandle", p);
+      }
+    }
+  } else {
+    opened = 0;
+  }
+  {
+    int flag = opened;
+    cr = ga_cu.p_cuMemcpyHtoDAsync(stage, &flag, sizeof(flag), ctx->s);
+    if (cr != CUDA_SUCCESS) { err = ga_err_cuda(ctx->err, "cuMemcpyHtoDAsync", cr); goto out; }
+    nr = nccl.AllReduce((const void *)stage, (void *)stage, 1, ncclInt32, ncclMin, comm->c, ctx->s);
+    if (nr != ncclSuccess) { err = nccl_fail(ctx, "ncclAllReduce", nr); goto out; }
+    cr = ga_cu.p_cuMemcpyDtoHAsync(&flag, stage, sizeof(flag), ctx->s);
+    if (cr == CUDA_SUCCESS) cr = ga_cu.p_cuStreamSynchronize(ctx->s);
+    if (cr != CUDA_SUCCESS) { err = ga_err_cuda(ctx->err, "peer window agreement", cr); goto out; }
+    if (flag == 1) {
+      comm->win_state = 1;
+    } else {
+      if (comm->win_reason[0] == '\0') peer_window_refuse(comm, "%sanother rank could not map its peers (%d)", "", flag);
+      comm->win_state = 1; /* so that the release below un-maps what was mapped */
+      {
+        char keep[sizeof(comm->win_reason)];
+        memcpy(keep, comm->win_reason, sizeof(keep));
+        peer_window_release(comm);
+        memcpy(comm->win_reason, keep, sizeof(keep));
+      }
+    }
+  }
+out:
+  if (stage != 0) ga_cu.p_cuMemFree(stage);
+  free(all);
+  ga_ctx_exit(ctx);
+  return err;
+}
+
+/* 1 when results of `bytes_per_rank` bytes can be combined through the peer
+ * windows of `comm`; the first call sets them up (collective). */
+int ga_comm_peer_ready(gpucomm *comm, size_t bytes_per_rank) {
+  if (comm == NULL) return 0;
+  if (comm->win_state == 0 && peer_window_setup(comm) != GA_NO_ERROR) return 0;
+  return comm->win_state == 1 && bytes_per_rank <= XC_SLOT_BYTES;
+}
+
+static void xc_type_defines(ga_strb *sb, int tc, int pair) {
+  const char *ct = ga_ctype(tc);
+  ga_strb_printf(sb, "#define GA_XC_T %s\n", ct);
+  if (tc == GA_HALF) {
+    ga_strb_puts(sb, "#define GA_XC_W_T float\n#define GA_XC_LOAD(x) ga_half2float(x)\n"
+                     "#define GA_XC_STORE(w) ga_float2half(w)\n");
+  } else {
+    ga_strb_printf(sb, "#define GA_XC_W_T %s\n#define GA_XC_LOAD(x) (x)\n#define GA_XC_STORE(w) (w)\n", ct);
+  }
+  ga_strb_printf(sb, "#define GA_XC_PAIR %d\n", pair);
+}
+
+/* Enqueues the exchange of `n` partial results held in val (and idx for pair
+ * operators; both dense, written in place) on the context's stream.
+ *  pair  0: accumulating, op one of GA_SUM / GA_PROD / GA_MIN / GA_MAX
+ *        1: (value, index), op GA_MIN or GA_MAX
+ *        2: value only, op GA_MIN or GA_MAX, equal values (+0.0, -0.0) go to the
+ *           rank with the lowest `key`; idx is not used */
+int ga_comm_exchange(gpucomm *comm, int pair, int op, int tc, CUdeviceptr val, CUdeviceptr idx,
+                     size_t n, unsigned long long key) {
+  gpucontext *ctx = comm->ctx;
+  xc_kernel *k;
+  struct {
+    unsigned long long n, seq, slot_bytes, idx_off, timeout_ns, key, win[XC_MAX_RANKS];
+    unsigned int nranks, rank, chunk, phases;
+  } L;
+  const size_t es = gpuarray_get_elsize(tc);
+  unsigned int grid[3] = {1, 1, 1}, block[3] = {XC_THREADS, 1, 1};
+  void *params[4];
+  size_t ctas;
+  int p, err;
+
+  if (comm->win_state != 1) return ga_err_set(ctx->err, GA_COMM_ERROR, "No peer windows");
+  if (*(volatile unsigned int *)comm->status_host != 0)
+    return ga_err_set(ctx->err, GA_COMM_ERROR,
+                      "An earlier exchange over peer memory gave up waiting for a rank; the "
+                      "communicator cannot be used any more");
+  if (n == 0) return GA_NO_ERROR;
+  for (k = comm->kernels; k != NULL; k = k->next)
+    if (k->pair == pair && k->op == op && k->tc == tc) break;
+  if (k == NULL) {
+    ga_strb sb;
+    ga_function fn;
+    ga_strb_init(&sb);
+    xc_type_defines(&sb, tc, pair);
+    if (pair) {
+      ga_strb_printf(&sb, "#define GA_XC_MIN %d\n", op == GA_MIN);
+    } else {
+      ga_strb_printf(&sb, "#define GA_XC_OP(a, b) %s\n",
+                     op == GA_SUM ? "((a) + (b))" : op == GA_PROD ? "((a) * (b))"
+                     : op == GA_MIN ? "((b) < (a) ? (b) : (a))" : "((b) > (a) ? (b) : (a))");
+    }
+    ga_strb_puts(&sb, "#include \"ga_exchange.cuh\"\n");
+    if (sb.failed) {
+      ga_strb_free(&sb);
+      return ga_err_sys(ctx->err, "malloc");
+    }
+    err = ga_compile(ctx, ga_strb_cstr(&sb), "ga_exchange", NULL, &fn, NULL);
+    ga_strb_free(&sb);
+    if (err != GA_NO_ERROR) return err;
+    fn.dependent_ok = 1;
+    k = calloc(1, sizeof(*k));
+    if (k == NULL) return ga_err_sys(ctx->err, "calloc");
+    k->pair = pair; k->op = op; k->tc = tc; k->fn = fn;
+    k->next = comm->kernels;
+    comm->kernels = k;
+  }
+  memset(&L, 0, sizeof(L));
+  L.n = n;
+  L.seq = ++comm->seq;
+  L.slot_bytes = XC_SLOT_BYTES;
+  L.idx_off = (n * es + 15) & ~(size_t)15;
+  L.timeout_ns = comm->timeout_ns;
+  L.key = key;
+  for (p = 0; p < comm->ndev; p++) L.win[p] = (unsigned long long)comm->win[p];
+  L.nranks = (unsigned int)comm->ndev;
+  L.rank = (unsigned int)comm->rank;
+  ctas = (n + XC_THREADS - 1) / XC_THREADS;
+  if (ctas > XC_MAX_CTAS) ctas = XC_MAX_CTAS;
+  L.chunk = (unsigned int)((((n + ctas - 1) / ctas) + 15) & ~(size_t)15);
+  grid[0] = (unsigned int)((n + L.chunk - 1) / L.chunk);
+  L.phases = 3;
+  params[0] = &L;
+  params[1] = &val;
+  params[2] = &idx;
+  params[3] = &comm->status_dev;
+  return ga_launch(ctx, &k->fn, grid, block, 0, params);
+}
+
+/* State of the peer windows of a communicator, for tests and benchmarks:
+ * 0 not set up yet, 1 in use, -1 unavailable (reason, if asked for, is a
+ * pointer into the communicator). *timed_out is non-zero once a kernel gave
+ * up waiting for a peer. */
+GPUARRAY_PUBLIC int gpuarray_b200_comm_peer_state(gpucomm *comm, const char **reason,
+                                                  unsigned int *timed_out) {
+  if (reason != NULL) *reason = comm->win_reason;
+  if (timed_out != NULL)
+    *timed_out = comm->status_host != NULL ? *(volatile unsigned int *)comm->status_host : 0;
+  return comm->win_state;
 }
 
 /* ------------------------------------------------------------ on GpuArrays */

@@ -246,6 +246,7 @@ static void ctx_destroy(gpucontext *ctx) {
     ctx->errbuf = NULL;
   }
   ga_modules_free(ctx);
+  ga_peer_windows_free(ctx);
   for (b = ctx->free_blocks; b != NULL; b = nb) {
     nb = b->next;
     ga_cu.p_cuMemFree(b->ptr);

@@ -1036,6 +1036,55 @@ static int sh_elemwise(gpucontext *ctx, GpuElemwise **slot, const char *expr, un
  *      the winner's sign when best is zero.
  * Bit-exact with the single-GPU kernel on the whole array, ties, NaN-first and
  * signed zeros included (the NaN written is the canonical quiet NaN). */
+static size_t sh_count(const GpuArray *a) {
+  size_t n = 1;
+  unsigned int k;
+  for (k = 0; k < a->nd; k++) n *= a->dimensions[k];
+  return n;
+}
+
+/* The same over the communicator's peer windows (ga_comm.c,
+ * templates/ga_exchange.cuh): the local kernel writes (v, i) with global
+ * indices, ONE more launch pushes them into every peer's window over NVLink
+ * and folds the peers' pairs - better value first, then lower index; a NaN can
+ * only come from the shard that holds element 0 and is then the answer. The
+ * winner's own bits are written, so signed zeros need no side channel. */
+static int sharded_pair_peer(GpuReduction *gr, gpucomm *comm, GpuArray *d0, GpuArray *d1,
+                             const GpuArray *s0, unsigned reduxLen, const int *reduxList,
+                             const rd_shard *sh) {
+  gpucontext *ctx = gr->ctx;
+  const GpuArray *shape_of = d0 != NULL ? d0 : d1;
+  const size_t n = sh_count(shape_of);
+  GpuArray v, i, *pv = d0, *pi = d1;
+  int have_v = 0, have_i = 0, err;
+
+  if (d0 == NULL || !ga_array_is_c_contiguous(d0) || !GpuArray_ISALIGNED(d0) ||
+      d0->typecode != gr->src_tc) {
+    err = GpuArray_empty(&v, ctx, gr->src_tc, shape_of->nd, shape_of->dimensions, GA_C_ORDER);
+    if (err != GA_NO_ERROR) return err;
+    have_v = 1;
+    pv = &v;
+  }
+  if (d1 == NULL || !ga_array_is_c_contiguous(d1) || !GpuArray_ISALIGNED(d1) ||
+      gpuarray_get_elsize(d1->typecode) != 8) {
+    err = GpuArray_empty(&i, ctx, GA_ULONG, shape_of->nd, shape_of->dimensions, GA_C_ORDER);
+    if (err != GA_NO_ERROR) goto done;
+    have_i = 1;
+    pi = &i;
+  }
+  err = rd_call(gr->sh_pair, pv, pi, s0, reduxLen, reduxList, 0, sh);
+  if (err != GA_NO_ERROR) goto done;
+  err = ga_comm_exchange(comm, 1, op_is_min(gr->op) ? GA_MIN : GA_MAX, gr->src_tc,
+                         pv->data->ptr + pv->offset, pi->data->ptr + pi->offset, n, 0);
+  if (err != GA_NO_ERROR) goto done;
+  if (have_v && d0 != NULL) err = GpuArray_move(d0, &v);
+  if (err == GA_NO_ERROR && have_i && d1 != NULL) err = GpuArray_move(d1, &i);
+done:
+  if (have_v) GpuArray_clear(&v);
+  if (have_i) GpuArray_clear(&i);
+  return err;
+}
+
 static int sharded_pair(GpuReduction *gr, gpucomm *comm, GpuArray *d0, GpuArray *d1,
                         const GpuArray *s0, unsigned reduxLen, const int *reduxList,
                         const rd_shard *sh) {
@@ -1051,6 +1100,12 @@ static int sharded_pair(GpuReduction *gr, gpucomm *comm, GpuArray *d0, GpuArray 
     err = GpuReduction_new(&gr->sh_pair, ctx, is_min ? GA_REDUCE_MINANDARGMIN : GA_REDUCE_MAXANDARGMAX,
                            0, 0, tc, 0);
     if (err != GA_NO_ERROR) return err;
+  }
+  if (comm != NULL) {
+    const size_t n = sh_count(shape_of);
+    const size_t need = ((n * gpuarray_get_elsize(tc) + 15) & ~(size_t)15) + n * 8;
+    if (ga_comm_peer_ready(comm, need))
+      return sharded_pair_peer(gr, comm, d0, d1, s0, reduxLen, reduxList, sh);
   }
 #define SH_TMP(arr, slot, typecode)                                                            \
   err = GpuArray_empty(&arr, ctx, typecode, shape_of->nd, shape_of->dimensions, GA_C_ORDER);   \
@@ -1170,6 +1225,31 @@ int GpuReduction_call_sharded(const GpuReduction *cgr, gpucomm *comm, GpuArray *
       return ga_err_set(ctx->err, GA_INVALID_ERROR, "Destination is NULL");
     if ((op_writes_val(gr->op) && d0 == NULL) || (op_writes_idx(gr->op) && d1 == NULL))
       return ga_err_set(ctx->err, GA_INVALID_ERROR, "Destination is NULL");
+    if (comm != NULL && d1 == NULL &&
+        (!tc_is_float(gr->src_tc) || (reduxLen > 0 && reduxList[0] == shard_axis)) &&
+        ga_comm_peer_ready(comm, sh_count(d0) * gpuarray_get_elsize(gr->src_tc))) {
+      /* MIN / MAX without an index: the value-only kernel, then the exchange with the
+       * shard's first coordinate as the tie-break key. When the sharded axis is the
+       * slowest reduced one, every element of a lower shard precedes every element of a
+       * higher one, so "equal values go to the lower shard" is the single-GPU rule (it
+       * only shows between +0.0 and -0.0; integers have no distinguishable ties). */
+      GpuArray tmp, *part = d0;
+      const int use_tmp = !(GpuArray_IS_C_CONTIGUOUS(d0) || GpuArray_IS_F_CONTIGUOUS(d0)) ||
+                          !GpuArray_ISALIGNED(d0) || d0->typecode != gr->src_tc;
+      if (use_tmp) {
+        err = GpuArray_empty(&tmp, ctx, gr->src_tc, d0->nd, d0->dimensions, GA_C_ORDER);
+        if (err != GA_NO_ERROR) return err;
+        part = &tmp;
+      }
+      err = rd_call(gr, part, NULL, s0, reduxLen, reduxList, flags, &sh);
+      if (err == GA_NO_ERROR)
+        err = ga_comm_exchange(comm, 2, op_is_min(gr->op) ? GA_MIN : GA_MAX, gr->src_tc,
+                               part->data->ptr + part->offset, 0, sh_count(part),
+                               (unsigned long long)shard_lo);
+      if (err == GA_NO_ERROR && use_tmp) err = GpuArray_move(d0, &tmp);
+      if (use_tmp) GpuArray_clear(&tmp);
+      return err;
+    }
     return sharded_pair(gr, comm, d0, d1, s0, reduxLen, reduxList, &sh);
   }
   /* accumulating operators: per-GPU partial of the final shape, ONE all-reduce */
@@ -1187,14 +1267,20 @@ int GpuReduction_call_sharded(const GpuReduction *cgr, gpucomm *comm, GpuArray *
   {
     GpuArray tmp, view;
     GpuArray *part = d0;
-    int use_tmp = !(GpuArray_IS_C_CONTIGUOUS(d0) || GpuArray_IS_F_CONTIGUOUS(d0));
+    int use_tmp = !(GpuArray_IS_C_CONTIGUOUS(d0) || GpuArray_IS_F_CONTIGUOUS(d0)) ||
+                  !GpuArray_ISALIGNED(d0);
     if (use_tmp) {
       err = GpuArray_empty(&tmp, ctx, d0->typecode, d0->nd, d0->dimensions, GA_C_ORDER);
       if (err != GA_NO_ERROR) return err;
       part = &tmp;
     }
     err = rd_call(gr, part, NULL, s0, reduxLen, reduxList, flags, &sh);
-    if (err == GA_NO_ERROR && comm != NULL) {
+    if (err == GA_NO_ERROR && comm != NULL &&
+        ga_comm_peer_ready(comm, sh_count(part) * gpuarray_get_elsize(part->typecode))) {
+      /* one launch over the peer windows; every rank folds in rank order */
+      err = ga_comm_exchange(comm, 0, opcode, part->typecode == GA_BOOL ? GA_UBYTE : part->typecode,
+                             part->data->ptr + part->offset, 0, sh_count(part), 0);
+    } else if (err == GA_NO_ERROR && comm != NULL) {
       if (part->typecode == GA_BOOL) { /* the collectives know no bool: same bytes as unsigned */
         err = GpuArray_view(&view, part);
         if (err == GA_NO_ERROR) {

@@ -179,6 +179,7 @@ struct _gpucontext {
   /* lazily created MAXANDARGMAX operators keyed by source type (ga_reduction.c) */
   void *maxandargmax_cache;
   void *take1_cache;        /* compiled gather kernels by (types, rank): ga_array.c */
+  void *peer_windows;       /* exported windows of freed communicators, for reuse: ga_comm.c */
 };
 
 #define GA_BUF_EXTERNAL 0x10000    /* memory not owned (cuda_make_buf) */
@@ -252,6 +253,13 @@ GA_HIDDEN int ga_array_in_bounds(const GpuArray *a);
 GA_HIDDEN void ga_extcopy_cache_free(gpucontext *ctx);
 GA_HIDDEN void ga_maxandargmax_cache_free(gpucontext *ctx);
 GA_HIDDEN void ga_take1_cache_free(gpucontext *ctx);
+GA_HIDDEN void ga_peer_windows_free(gpucontext *ctx);
+
+/* Combination of per-GPU partial results through peer memory (ga_comm.c). */
+struct _gpucomm;
+GA_HIDDEN int ga_comm_peer_ready(struct _gpucomm *comm, size_t bytes_per_rank);
+GA_HIDDEN int ga_comm_exchange(struct _gpucomm *comm, int pair, int op, int tc, CUdeviceptr val,
+                               CUdeviceptr idx, size_t n, unsigned long long key);
 
 /* Name of the C type used in kernel source for a typecode, or NULL. */
 GA_HIDDEN const char *ga_ctype(int typecode);

@@ -39,6 +39,13 @@ static inline ga_half ga_float2half(float f) {
 
 static inline float ga__add_f32_f16(float acc, ga_half h) { return acc + ga_half2float(h); }
 static inline void ga__grid_dependency_sync() {}
+static inline void ga__fence_system() {}
+static inline void ga__st_release_sys(unsigned long long *p, unsigned long long v) { *p = v; }
+static inline unsigned long long ga__ld_acquire_sys(const unsigned long long *p) { return *p; }
+static inline unsigned long long ga__globaltimer_ns() { static unsigned long long t; return t += 1000; }
+static inline void ga__nanosleep(unsigned int) {}
+template <typename T>
+static inline T ga__ld_volatile(const T *p) { return *p; }
 static inline void ga__prefetch_l2(const void *, unsigned int) {}
 static inline void ga__cp_async16(void *smem, const void *gmem) { memcpy(smem, gmem, 16); }
 static inline void ga__cp_async_wait_all() {}

@@ -1,6 +1,9 @@
-"""Two ranks on two GPUs: sharded reductions finished with gpucomm_all_reduce
-(NCCL over NVLink). Skipped when fewer than two GPUs are visible. NVLS is
-switched off for these short-lived child processes."""
+"""Two ranks on two GPUs: reductions whose reduced extent is sharded, combined
+on the device - once through the communicator's peer-memory windows (one
+exchange kernel per GPU over NVLink, templates/ga_exchange.cuh) and once
+through gpucomm_all_reduce (NCCL), the path taken where the windows cannot be
+set up. Skipped when fewer than two GPUs are visible. NVLS is switched off for
+these short-lived child processes."""
 import os
 import sys
 
@@ -22,12 +25,15 @@ def _ngpus():
         return 0
 
 
-def _worker(rank, world, q_id, q_err):
+def _worker(rank, world, q_id, q_err, peer):
     """Every collective is enqueued BEFORE anything is checked: a rank that
-    failed an assertion between two collectives would leave its peer's NCCL
-    kernel waiting on the GPU for a rank that has already left."""
+    failed an assertion between two collectives would leave its peer's kernel
+    waiting on the GPU for a rank that has already left."""
     try:
         os.environ["NCCL_NVLS_ENABLE"] = "0"
+        os.environ["GPUARRAY_B200_PEER_TIMEOUT_MS"] = "4000"
+        if not peer:
+            os.environ["GPUARRAY_B200_NO_PEER_WINDOW"] = "1"
         from libgpuarray_b200 import api, sharding
         from oracle import oracle as O
         ctx = api.Context(rank, kernel_cache=os.path.join(ROOT, ".kernel_cache"))
@@ -73,6 +79,55 @@ def _worker(rank, world, q_id, q_err):
                                        comm, v, i, gt, axes, lo, 64, shard_axis=0)
             got[tag] = (v, i)
 
+        # value-only extremes of the array with signed zeros and NaNs: sharded axis slowest
+        # (the keyed exchange) and fastest (falls back to the pair exchange)
+        for tag, opname, axes in (("max02", "MAX", [0, 2]), ("max20", "MAX", [2, 0]), ("min02", "MIN", [0, 2])):
+            v = api.GpuArray.empty(ctx, (48,), np.float64)
+            api.reduction_call_sharded(api.GpuReduction(ctx, getattr(api, "GA_REDUCE_" + opname), np.float64),
+                                       comm, v, None, gt, axes, lo, 64, shard_axis=0)
+            got[tag] = v
+
+        # destinations that are not dense, an index-only operator, other types, and many
+        # exchanges in a row (the two halves of the windows alternate)
+        wide_v = api.GpuArray.from_numpy(ctx, np.full((48, 2), 7.0))
+        wide_i = api.GpuArray.from_numpy(ctx, np.full((48, 2), -7, np.int64))
+        api.reduction_call_sharded(api.GpuReduction(ctx, api.GA_REDUCE_MAXANDARGMAX, np.float64), comm,
+                                   wide_v[:, 0], wide_i[:, 1], gt, [0, 2], lo, 64, shard_axis=0)
+        only_i = api.GpuArray.empty(ctx, (48,), np.uint64)
+        api.reduction_call_sharded(api.GpuReduction(ctx, api.GA_REDUCE_ARGMIN, np.float64), comm, None,
+                                   only_i, gt, [0, 2], lo, 64, shard_axis=0)
+        xh = (np.round(rng.standard_normal((64, 300)) * 4) / 4).astype(np.float16)
+        gh = api.GpuArray.from_numpy(ctx, xh[lo:hi])
+        sum_h = api.GpuArray.empty(ctx, (300,), np.float16)
+        api.reduction_call_sharded(api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.float16), comm, sum_h, None,
+                                   gh, [0], lo, 64)
+        max_h = (api.GpuArray.empty(ctx, (300,), np.float16), api.GpuArray.empty(ctx, (300,), np.int64))
+        api.reduction_call_sharded(api.GpuReduction(ctx, api.GA_REDUCE_MAXANDARGMAX, np.float16), comm,
+                                   max_h[0], max_h[1], gh, [0], lo, 64)
+        xb = (rng.random((64, 5000)) < 0.01).astype(np.uint8)
+        gb = api.GpuArray.from_numpy(ctx, xb[lo:hi])
+        any_b = api.GpuArray.empty(ctx, (5000,), np.bool_)
+        api.reduction_call_sharded(api.GpuReduction(ctx, api.GA_REDUCE_ANY, np.uint8), comm, any_b, None,
+                                   gb, [0], lo, 64)
+        xi = rng.integers(-1000, 1000, (64, 70000)).astype(np.int32)     # 70000 outputs: 64 CTAs, ragged chunks
+        gi32 = api.GpuArray.from_numpy(ctx, xi[lo:hi])
+        min_i = (api.GpuArray.empty(ctx, (70000,), np.int32), api.GpuArray.empty(ctx, (70000,), np.int64))
+        api.reduction_call_sharded(api.GpuReduction(ctx, api.GA_REDUCE_MINANDARGMIN, np.int32), comm,
+                                   min_i[0], min_i[1], gi32, [0], lo, 64)
+        many = []
+        gr_sum = api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.float64)
+        gr_max = api.GpuReduction(ctx, api.GA_REDUCE_MAXANDARGMAX, np.float64)
+        for rep in range(24):
+            dv = api.GpuArray.empty(ctx, (48,), np.float64)
+            if rep % 2:
+                api.reduction_call_sharded(gr_sum, comm, dv, None, g, [0, 2], lo, 64)
+                many.append((dv, None))
+            else:
+                di = api.GpuArray.empty(ctx, (48,), np.int64)
+                api.reduction_call_sharded(gr_max, comm, dv, di, gt, [0, 2], lo, 64, shard_axis=0)
+                many.append((dv, di))
+        state = comm.peer_state()
+
         # the other collectives of the reference's interface (src/gpuarray/collectives.h):
         # reduce to a root, reduce-scatter, broadcast, all-gather
         a = np.arange(6 * world, dtype=np.float32).reshape(world, 6) + 100 * rank
@@ -100,6 +155,35 @@ def _worker(rank, world, q_id, q_err):
             assert (bi == wi).all(), (tag, bi, wi)
             nan = np.isnan(wv)
             assert (np.isnan(bv) == nan).all() and bv[~nan].tobytes() == wv[~nan].tobytes(), tag
+        assert state[0] == (1 if peer else -1) and state[2] == 0, state
+        assert comm.peer_state()[2] == 0
+        for tag, is_min, axes in (("max02", False, [0, 2]), ("max20", False, [2, 0]), ("min02", True, [0, 2])):
+            bv = got[tag].to_numpy()
+            wv = O.minmaxarg(xt, axes, is_min=is_min)[0]
+            nan = np.isnan(wv)
+            assert (np.isnan(bv) == nan).all() and bv[~nan].tobytes() == wv[~nan].tobytes(), tag
+        assert np.signbit(got["max20"].to_numpy()[6]) and not np.signbit(got["max02"].to_numpy()[6])
+        wv, wi = O.minmaxarg(xt, [0, 2])
+        ok = ~np.isnan(wv)
+        hv, hi_ = wide_v.to_numpy(), wide_i.to_numpy()
+        assert (hi_[:, 1] == wi).all() and (hi_[:, 0] == -7).all() and (hv[:, 1] == 7.0).all()
+        assert (np.isnan(hv[:, 0]) == ~ok).all() and hv[ok, 0].tobytes() == wv[ok].tobytes()
+        assert (only_i.to_numpy().astype(np.int64) == O.minmaxarg(xt, [0, 2], is_min=True)[1]).all()
+        assert (sum_h.to_numpy() == xh.astype(np.float64).sum(0).astype(np.float16)).all()   # quarter steps: exact
+        wv, wi = O.minmaxarg(xh, [0])
+        assert max_h[0].to_numpy().tobytes() == wv.tobytes() and (max_h[1].to_numpy() == wi).all()
+        assert (any_b.to_numpy() == xb.any(0)).all()
+        wv, wi = O.minmaxarg(xi, [0], is_min=True)
+        assert (min_i[0].to_numpy() == wv).all() and (min_i[1].to_numpy() == wi).all()
+        wv, wi = O.minmaxarg(xt, [0, 2])
+        first_sum = None
+        for rep, (dv, di) in enumerate(many):
+            if di is None:
+                first_sum = dv.to_numpy() if first_sum is None else first_sum
+                assert dv.to_numpy().tobytes() == first_sum.tobytes()               # same bits every time
+                assert np.allclose(first_sum, x.sum(axis=(0, 2)), rtol=1e-12, atol=1e-9)
+            else:
+                assert (di.to_numpy() == wi).all() and dv.to_numpy()[ok].tobytes() == wv[ok].tobytes()
         if rank == 1:
             want = sum(np.arange(6 * world, dtype=np.float32).reshape(world, 6) + 100 * r
                        for r in range(world))
@@ -146,12 +230,13 @@ def _transfer_worker(q_err):
 
 
 @pytest.mark.skipif(_ngpus() < 2, reason="needs two GPUs")
-def test_sharded_reduction_with_gpucomm():
+@pytest.mark.parametrize("peer", [True, False], ids=["peer_windows", "nccl_all_reduce"])
+def test_sharded_reduction_with_gpucomm(peer):
     import torch.multiprocessing as mp
     m = mp.get_context("spawn")
     q_id, q_err = m.Queue(), m.Queue()
     world = 2
-    procs = [m.Process(target=_worker, args=(r, world, q_id, q_err)) for r in range(world)]
+    procs = [m.Process(target=_worker, args=(r, world, q_id, q_err, peer)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
