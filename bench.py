@@ -543,7 +543,12 @@ def sharded_configs(api, ctx, torch, dist, stream, rank, world, host_slab, t1_cf
         us_nccl = span(both_nccl, 10)
         us_kernel = span(lambda: gr(part, None, g5, axes), 10)
         us_comm = span(lambda: comm.all_reduce(part, res, cop), 20)
+        both()
+        got = res.to_numpy().copy()
         us_one = span(lambda: gr(res, None, g_full, axes), 4)
+        want = res.to_numpy()
+        check = bool(np.allclose(got, want, rtol=1e-12, atol=0) if name == "sum_all" else
+                     got.tobytes() == want.tobytes())
         state = comm.peer_state()
         out["cfg5_f64_%s_sharded" % name] = {
             "us": round(us_both, 2), "GB/s": round(total_bytes / us_both / 1e3, 1),
@@ -555,7 +560,8 @@ def sharded_configs(api, ctx, torch, dist, stream, rank, world, host_slab, t1_cf
             "collective": ("GpuReduction_call_sharded: one exchange kernel over peer (NVLink) windows, %d B"
                            if state[0] == 1 else
                            "GpuReduction_call_sharded: gpucomm_all_reduce (NCCL), %d B") % res.nbytes,
-            "peer_windows": state[0] == 1, "peer_windows_reason": state[1], "scaling": "strong"}
+            "peer_windows": state[0] == 1, "peer_windows_reason": state[1], "scaling": "strong",
+            "matches_1gpu_result": check}
         gr.free()
 
     # ---- (value, first global index) with the reduced extent sharded
@@ -565,8 +571,10 @@ def sharded_configs(api, ctx, torch, dist, stream, rank, world, host_slab, t1_cf
         gi = api.GpuArray.empty(ctx, (1024,), np.uint64)
         us_both = span(lambda: api.reduction_call_sharded(gr, comm, gv, gi, g5, [0, 2],
                                                           rank * planes, 2048), 10)
+        got = (gv.to_numpy().copy(), gi.to_numpy().copy())
         us_kernel = span(lambda: gr(gv, gi, g5, [0, 2]), 10)
         us_one = span(lambda: gr(gv, gi, g_full, [0, 2]), 4)
+        check = bool(got[0].tobytes() == gv.to_numpy().tobytes() and (got[1] == gi.to_numpy()).all())
         out["cfg5_f64_maxandargmax_axes02_sharded"] = {
             "us": round(us_both, 2), "GB/s": round(total_bytes / us_both / 1e3, 1),
             "kernel_only_us": round(us_kernel, 2), "t_1gpu_us": round(us_one, 2),
@@ -576,7 +584,7 @@ def sharded_configs(api, ctx, torch, dist, stream, rank, world, host_slab, t1_cf
             "collective": ("one exchange kernel over peer (NVLink) windows: better value, then lower index"
                            if comm.peer_state()[0] == 1 else
                            "all-reduce of the value, candidate-index kernel, all-reduce MIN of the index"),
-            "peer_windows": comm.peer_state()[0] == 1, "scaling": "strong"}
+            "peer_windows": comm.peer_state()[0] == 1, "scaling": "strong", "matches_1gpu_result": check}
         gr.free()
     ctx.sync()
     comm.free()

@@ -162,18 +162,36 @@ static char *gen_source(const GpuReduction *gr, const rd_variant *v) {
     else
       ga_strb_printf(&sb, "#define GA_RD_PICK(a, b) ((a) %s (b) ? (a) : (b))\n", mn ? "<" : ">");
   }
+  {
+    /* experiments: GPUARRAY_B200_RD_DEFINES="NAME=VALUE;NAME=VALUE" puts #define lines in
+     * front of the template (its #ifndef defaults then stand back) */
+    const char *extra = getenv("GPUARRAY_B200_RD_DEFINES");
+    while (extra != NULL && *extra != '\0') {
+      const char *end = strchr(extra, ';'), *eq;
+      size_t len = end != NULL ? (size_t)(end - extra) : strlen(extra);
+      eq = memchr(extra, '=', len);
+      if (eq != NULL) {
+        ga_strb_puts(&sb, "#define ");
+        ga_strb_putn(&sb, extra, (size_t)(eq - extra));
+        ga_strb_puts(&sb, " ");
+        ga_strb_putn(&sb, eq + 1, len - (size_t)(eq - extra) - 1);
+        ga_strb_puts(&sb, "\n");
+      }
+      extra = end != NULL ? end + 1 : NULL;
+    }
+  }
   ga_strb_printf(&sb, "#define GA_RD_KIND %d\n#define GA_RD_ISFLOAT %d\n#define GA_RD_WRITE_VAL %d\n"
                       "#define GA_RD_WRITE_IDX %d\n#define GA_RD_IDX_T %s\n#define GA_RD_VEC %d\n"
                       "#define GA_RD_THREADS %d\n#define GA_RD_TPO %d\n"
                       "#define GA_RD_BY %d\n#define GA_RD_GROUP %d\n#define GA_RD_FLAT %d\n"
                       "#define GA_RD_MU %d\n#define GA_RD_ONERUN %d\n#define GA_RD_FAST8 %d\n#define GA_RD_LAZY %d\n"
-                      "#define GA_RD_SIMPLE %d\n"
+                      "#define GA_RD_SIMPLE %d\n#define GA_RD_UNROLL %d\n"
                       "#define %s\n"
                       "#include \"ga_reduce.cuh\"\n",
                  gr->kind, tc_is_float(gr->src_tc), v->write_val, v->write_idx,
                  v->idx64 ? "unsigned long long" : "unsigned int", v->vec, RD_THREADS, v->tpo,
                  v->by ? v->by : RD_BY, v->group ? v->group : RD_THREADS, v->flat, v->mu ? v->mu : 1,
-                 v->onerun, v->fast8, v->lazy, v->simple,
+                 v->onerun, v->fast8, v->lazy, v->simple, gr->kind == 1 ? 8 : 4,
                  v->shape == SHAPE_ROWS   ? "GA_RD_BUILD_ROWS"
                  : v->shape == SHAPE_COLS ? "GA_RD_BUILD_COLS"
                                           : "GA_RD_BUILD_GENERAL");
@@ -568,7 +586,17 @@ static int rd_plan(const rd_plan_in *in, rd_layout *L, rd_variant *want, unsigne
         lpl = (unsigned)((nload + g - 1) / g);
         want->onerun = 1;
         want->group = (int)g;
-        want->mu = rd_onerun_mu ? (int)rd_onerun_mu : lpl <= 2 ? 4 : 2;
+        /* outputs a group works on at once. Measured on B200 (fp32, 256 MiB, rows of 16 ..
+         * 1024): MIN / MAX / ARGMIN / ARGMAX - one destination, a light state - gain from 4
+         * (rows of 16: 60.4 -> 54.8 us, of 512: 56.6 -> 55.0 us) except with two lanes per
+         * row (32 columns: 55.5 -> 57.0 us) and with the values-only scan of longer rows
+         * (1024 columns: 51.5 -> 54.7 us); value AND index (67 - 74 us against 60) and sums
+         * (rows of 16: 44.9 -> 50.2 us) lose: their four states no longer fit the registers
+         * three CTAs per SM leave. */
+        want->mu = rd_onerun_mu                                                        ? (int)rd_onerun_mu
+                   : lpl <= 2                                                          ? 4
+                   : (in->kind == 1 && !(in->need_val && in->need_idx) && lpl <= 4 && g != 2) ? 4
+                                                                                       : 2;
         L->seg = L->inner;
         L->nseg = 1;
         L->units = 1;
