@@ -344,7 +344,7 @@ def side_configs(api, ctx, torch, stream, once=False):
     return out
 
 
-def other_shapes(api, ctx, torch, stream, once=False):
+def other_shapes(api, ctx, torch, stream, once=False, only=None):
     """`--other-shapes`: shapes outside the five named configurations that the
     same kernels meet in practice (short runs, kept axis in the middle,
     broadcasts, narrow element types), each 130-270 MB so that one launch
@@ -361,6 +361,8 @@ def other_shapes(api, ctx, torch, stream, once=False):
         return api.GpuArray.from_pointer(ctx, t.data_ptr(), tuple(t.shape), npdt[t.dtype])
 
     def timed(name, fn, nbytes, reps=10):
+        if only and only not in name:
+            return
         if once:                      # profiler captures: one launch per case
             reps = 1
         for _ in range(0 if once else 3):
@@ -398,6 +400,8 @@ def other_shapes(api, ctx, torch, stream, once=False):
         ("any i8 (2^28) all", (1 << 28,), [0], torch.int8, ANY),
     ]
     for name, shape, axes, tdt, op in reductions:
+        if only and only not in name:
+            continue
         if tdt == torch.int8:
             t = torch.randint(-3, 4, shape, device="cuda", dtype=torch.int8, generator=g)
         else:
@@ -756,7 +760,7 @@ def run_ours(args, rank, world, local_rank):
         except Exception as e:
             line["configs"] = {"error": str(e)[:300]}
     if world == 1 and args.other_shapes:
-        line["other_shapes"] = other_shapes(api, ctx, torch, stream, once=args.side_once)
+        line["other_shapes"] = other_shapes(api, ctx, torch, stream, once=args.side_once, only=args.only)
     emit(line)
     if world > 1:
         dist.destroy_process_group()
@@ -806,6 +810,9 @@ def main():
     ap.add_argument("--other-shapes", action="store_true",
                     help="also time reductions and elementwise calls on shapes outside the five "
                          "named configurations (adds an `other_shapes` object to the line)")
+    ap.add_argument("--only", default=None,
+                    help="with --other-shapes: run only the cases whose name contains this text "
+                         "(profiler captures of one kernel)")
     ap.add_argument("--cfg5-sharded", action="store_true",
                     help="accepted for compatibility: with N > 1 the sharded configurations "
                          "(cfg3 rows split, cfg5 planes split + all-reduce) always run unless "
