@@ -91,8 +91,9 @@ GPUARRAY_PUBLIC int GpuReduction_call(const GpuReduction *gr, GpuArray *d0, GpuA
  * src/gpuarray_collectives_cuda_nccl.c:286-316).
  *  - SUM, PROD, PRODNZ, ALL, ANY: the fold runs in rank order, so every rank
  *    ends with the same bits (one all-reduce sum / prod / min / max on the
- *    fallback path). AND, OR, XOR: GA_UNSUPPORTED_ERROR (the collectives have
- *    no bitwise operator).
+ *    fallback path). AND, OR, XOR are folded by the exchange kernel as well;
+ *    on the fallback path they return GA_UNSUPPORTED_ERROR (the collectives
+ *    have no bitwise operator).
  *  - MIN, MAX and the ARG variants: the index written is the flat index in the
  *    whole reduced extent (shard offset and global radix included); the better
  *    value wins, the lower global index among equal values, so ties go exactly

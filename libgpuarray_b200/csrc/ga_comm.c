@@ -527,7 +527,8 @@ static void xc_type_defines(ga_strb *sb, int tc, int pair) {
 
 /* Enqueues the exchange of `n` partial results held in val (and idx for pair
  * operators; both dense, written in place) on the context's stream.
- *  pair  0: accumulating, op one of GA_SUM / GA_PROD / GA_MIN / GA_MAX
+ *  pair  0: accumulating, op one of GA_SUM / GA_PROD / GA_MIN / GA_MAX or, for integer
+ *           types, GA_XC_AND / GA_XC_OR / GA_XC_XOR (folds the collectives do not offer)
  *        1: (value, index), op GA_MIN or GA_MAX
  *        2: value only, op GA_MIN or GA_MAX, equal values (+0.0, -0.0) go to the
  *           rank with the lowest `key`; idx is not used */
@@ -551,6 +552,18 @@ int ga_comm_exchange(gpucomm *comm, int pair, int op, int tc, CUdeviceptr val, C
                       "An earlier exchange over peer memory gave up waiting for a rank; the "
                       "communicator cannot be used any more");
   if (n == 0) return GA_NO_ERROR;
+  {
+    /* every exchange carries its own sequence number: a captured launch replayed from a
+     * CUDA graph would present an old one, find its flags already set and read stale slots */
+    CUstreamCaptureStatus cap = CU_STREAM_CAPTURE_STATUS_NONE;
+    ga_ctx_enter(ctx);
+    ga_cu.p_cuStreamIsCapturing(ctx->s, &cap);
+    ga_ctx_exit(ctx);
+    if (cap != CU_STREAM_CAPTURE_STATUS_NONE)
+      return ga_err_set(ctx->err, GA_UNSUPPORTED_ERROR,
+                        "Sharded reductions cannot be captured into a CUDA graph: each exchange over "
+                        "peer memory is numbered");
+  }
   for (k = comm->kernels; k != NULL; k = k->next)
     if (k->pair == pair && k->op == op && k->tc == tc) break;
   if (k == NULL) {
@@ -562,8 +575,13 @@ int ga_comm_exchange(gpucomm *comm, int pair, int op, int tc, CUdeviceptr val, C
       ga_strb_printf(&sb, "#define GA_XC_MIN %d\n", op == GA_MIN);
     } else {
       ga_strb_printf(&sb, "#define GA_XC_OP(a, b) %s\n",
-                     op == GA_SUM ? "((a) + (b))" : op == GA_PROD ? "((a) * (b))"
-                     : op == GA_MIN ? "((b) < (a) ? (b) : (a))" : "((b) > (a) ? (b) : (a))");
+                     op == GA_SUM    ? "((a) + (b))"
+                     : op == GA_PROD ? "((a) * (b))"
+                     : op == GA_MIN  ? "((b) < (a) ? (b) : (a))"
+                     : op == GA_MAX  ? "((b) > (a) ? (b) : (a))"
+                     : op == GA_XC_AND ? "((a) & (b))"
+                     : op == GA_XC_OR  ? "((a) | (b))"
+                                       : "((a) ^ (b))");
     }
     ga_strb_puts(&sb, "#include \"ga_exchange.cuh\"\n");
     if (sb.failed) {

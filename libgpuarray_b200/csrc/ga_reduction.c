@@ -1286,12 +1286,18 @@ int GpuReduction_call_sharded(const GpuReduction *cgr, gpucomm *comm, GpuArray *
   case GA_REDUCE_PROD: case GA_REDUCE_PRODNZ: opcode = GA_PROD; break;
   case GA_REDUCE_ALL: opcode = GA_MIN; break; /* destinations hold 0 / 1 */
   case GA_REDUCE_ANY: opcode = GA_MAX; break;
+  case GA_REDUCE_AND: opcode = GA_XC_AND; break; /* peer windows only, checked below */
+  case GA_REDUCE_OR: opcode = GA_XC_OR; break;
+  case GA_REDUCE_XOR: opcode = GA_XC_XOR; break;
   default:
-    return ga_err_set(ctx->err, GA_UNSUPPORTED_ERROR,
-                      "Bitwise reductions cannot be combined across GPUs: the collectives offer "
-                      "sum, prod, min and max only");
+    return ga_err_set(ctx->err, GA_UNSUPPORTED_ERROR, "Operator cannot be combined across GPUs");
   }
   if (d0 == NULL) return ga_err_set(ctx->err, GA_INVALID_ERROR, "Value destination is NULL");
+  if (opcode >= GA_XC_AND &&
+      (comm == NULL || !ga_comm_peer_ready(comm, sh_count(d0) * gpuarray_get_elsize(d0->typecode))))
+    return ga_err_set(ctx->err, GA_UNSUPPORTED_ERROR,
+                      "Bitwise reductions are combined across GPUs through the communicator's peer "
+                      "windows only: the collectives offer sum, prod, min and max");
   {
     GpuArray tmp, view;
     GpuArray *part = d0;

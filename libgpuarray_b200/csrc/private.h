@@ -93,6 +93,7 @@ GA_HIDDEN uint64_t ga_hash64(const void *data, size_t len, uint64_t seed);
   X(cuCtxPushCurrent) X(cuCtxPopCurrent) X(cuCtxGetCurrent) X(cuCtxSynchronize)    \
   X(cuCtxGetDevice)                                                                \
   X(cuStreamCreate) X(cuStreamDestroy) X(cuStreamSynchronize) X(cuStreamWaitEvent) \
+  X(cuStreamIsCapturing)                                                           \
   X(cuMemAlloc) X(cuMemFree) X(cuMemHostAlloc) X(cuMemFreeHost)                    \
   X(cuMemHostGetDevicePointer) X(cuMemGetInfo) X(cuMemGetAddressRange)             \
   X(cuMemcpyHtoDAsync) X(cuMemcpyDtoHAsync) X(cuMemcpyDtoDAsync) X(cuMemcpyPeerAsync) \
@@ -257,6 +258,7 @@ GA_HIDDEN void ga_peer_windows_free(gpucontext *ctx);
 
 /* Combination of per-GPU partial results through peer memory (ga_comm.c). */
 struct _gpucomm;
+enum { GA_XC_AND = 100, GA_XC_OR = 101, GA_XC_XOR = 102 }; /* beside GA_SUM .. GA_MIN */
 GA_HIDDEN int ga_comm_peer_ready(struct _gpucomm *comm, size_t bytes_per_rank);
 GA_HIDDEN int ga_comm_exchange(struct _gpucomm *comm, int pair, int op, int tc, CUdeviceptr val,
                                CUdeviceptr idx, size_t n, unsigned long long key);

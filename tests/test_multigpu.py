@@ -109,6 +109,15 @@ def _worker(rank, world, q_id, q_err, peer):
         any_b = api.GpuArray.empty(ctx, (5000,), np.bool_)
         api.reduction_call_sharded(api.GpuReduction(ctx, api.GA_REDUCE_ANY, np.uint8), comm, any_b, None,
                                    gb, [0], lo, 64)
+        x8 = rng.integers(0, 256, (64, 5000)).astype(np.uint8)
+        g8 = api.GpuArray.from_numpy(ctx, x8[lo:hi])
+        xor_d = api.GpuArray.empty(ctx, (5000,), np.uint8)
+        try:            # bitwise folds exist in the exchange kernel only; both ranks agree on which path runs
+            api.reduction_call_sharded(api.GpuReduction(ctx, api.GA_REDUCE_XOR, np.uint8), comm, xor_d, None,
+                                       g8, [0], lo, 64)
+            xor_code = 0
+        except api.GpuArrayException as e:
+            xor_code = e.code
         xi = rng.integers(-1000, 1000, (64, 70000)).astype(np.int32)     # 70000 outputs: 64 CTAs, ragged chunks
         gi32 = api.GpuArray.from_numpy(ctx, xi[lo:hi])
         min_i = (api.GpuArray.empty(ctx, (70000,), np.int32), api.GpuArray.empty(ctx, (70000,), np.int64))
@@ -173,6 +182,10 @@ def _worker(rank, world, q_id, q_err, peer):
         wv, wi = O.minmaxarg(xh, [0])
         assert max_h[0].to_numpy().tobytes() == wv.tobytes() and (max_h[1].to_numpy() == wi).all()
         assert (any_b.to_numpy() == xb.any(0)).all()
+        if peer:
+            assert xor_code == 0 and (xor_d.to_numpy() == np.bitwise_xor.reduce(x8, axis=0)).all()
+        else:
+            assert xor_code == api.GA_UNSUPPORTED_ERROR
         wv, wi = O.minmaxarg(xi, [0], is_min=True)
         assert (min_i[0].to_numpy() == wv).all() and (min_i[1].to_numpy() == wi).all()
         wv, wi = O.minmaxarg(xt, [0, 2])
