@@ -27,6 +27,7 @@ enum { SHAPE_ROWS = 0, SHAPE_COLS = 1, SHAPE_GENERAL = 2 };
 typedef struct rd_variant {
   int shape, vec, idx64, tpo, dst_tc, write_val, write_idx, group, flat, mu, onerun, fast8, lazy;
   int simple; /* rows: lean one-run-per-warp loop */
+  int tiny;   /* rows: runs of 1-8 vectors back to back, walked as one flat array of vectors */
   int by;     /* cols: row lanes per CTA (0 = RD_BY) */
   int ctas_per_sm; /* CTAs of RD_THREADS threads the compiled kernel fits on an SM */
   ga_function fn;
@@ -186,13 +187,13 @@ static char *gen_source(const GpuReduction *gr, const rd_variant *v) {
                       "#define GA_RD_THREADS %d\n#define GA_RD_TPO %d\n"
                       "#define GA_RD_BY %d\n#define GA_RD_GROUP %d\n#define GA_RD_FLAT %d\n"
                       "#define GA_RD_MU %d\n#define GA_RD_ONERUN %d\n#define GA_RD_FAST8 %d\n#define GA_RD_LAZY %d\n"
-                      "#define GA_RD_SIMPLE %d\n#define GA_RD_UNROLL %d\n"
+                      "#define GA_RD_SIMPLE %d\n#define GA_RD_UNROLL %d\n#define GA_RD_TINY %d\n"
                       "#define %s\n"
                       "#include \"ga_reduce.cuh\"\n",
                  gr->kind, tc_is_float(gr->src_tc), v->write_val, v->write_idx,
                  v->idx64 ? "unsigned long long" : "unsigned int", v->vec, RD_THREADS, v->tpo,
                  v->by ? v->by : RD_BY, v->group ? v->group : RD_THREADS, v->flat, v->mu ? v->mu : 1,
-                 v->onerun, v->fast8, v->lazy, v->simple, gr->kind == 1 ? 8 : 4,
+                 v->onerun, v->fast8, v->lazy, v->simple, gr->kind == 1 ? 8 : 4, v->tiny,
                  v->shape == SHAPE_ROWS   ? "GA_RD_BUILD_ROWS"
                  : v->shape == SHAPE_COLS ? "GA_RD_BUILD_COLS"
                                           : "GA_RD_BUILD_GENERAL");
@@ -214,7 +215,7 @@ static rd_variant *get_variant(GpuReduction *gr, const rd_variant *want, int *er
         v->write_val == want->write_val && v->write_idx == want->write_idx &&
         v->group == want->group && v->flat == want->flat && v->mu == want->mu &&
         v->onerun == want->onerun && v->fast8 == want->fast8 && v->lazy == want->lazy &&
-        v->simple == want->simple && v->by == want->by)
+        v->simple == want->simple && v->by == want->by && v->tiny == want->tiny)
       return v;
   v = malloc(sizeof(*v));
   if (v == NULL) {
@@ -293,11 +294,13 @@ GPUARRAY_PUBLIC char *gpuarray_b200_reduction_source(int op, int src_tc, int dst
   v.idx64 = idx64;
   v.tpo = tpo;
   v.group = group & 0xffff; /* bits 16-19: runs at once, bit 20: one-run mode, bit 21: flattened,
-                               bit 22: lean one-run-per-warp loop, bits 24-29: row lanes (cols) */
+                               bit 22: lean one-run-per-warp loop, bit 23: flat walk of tiny runs,
+                               bits 24-29: row lanes (cols) */
   v.mu = (group >> 16) & 0xf;
   v.onerun = (group >> 20) & 1;
   v.flat = (group >> 21) & 1;
   v.simple = (group >> 22) & 1;
+  v.tiny = (group >> 23) & 1;
   v.by = (group >> 24) & 0x3f;
   v.dst_tc = dst_tc;
   v.write_val = op_writes_val(gr.op);
@@ -533,11 +536,11 @@ static int all_multiple(const long long *v, unsigned n, long long m) {
  * lean_rows (0/1),cols_early_rows,lazy_min_vectors_per_lane_short_runs,
  * outputs_per_sm_from_which_a_warp_owns_an_output,
  * warps_per_sm_wanted_when_2_or_4_warps_share_a_run (0 = a CTA per run),
- * trim_splits_to_whole_waves (0/1)". The
+ * trim_splits_to_whole_waves (0/1),flat_walk_of_tiny_runs (0/1)". The
  * defaults are the best of sweeps on a B200. */
 static unsigned rd_cols_ctas_per_sm = 0, rd_cols_by = 0;
 static unsigned rd_simple = 1, rd_cols_early = 4, rd_lazy_onerun_min = 8, rd_warp_rows_per_sm = 16, rd_subcta = 24;
-static unsigned rd_wave_fit = 1;
+static unsigned rd_wave_fit = 1, rd_tiny = 1;
 static unsigned rd_onerun_ctas_per_sm = 3, rd_onerun_lpl = 4, rd_onerun_mu = 0, rd_lazy = 1, rd_lazy_min = 32;
 
 static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_bytes) {
@@ -547,10 +550,10 @@ static void rd_tuning(unsigned *ctas_per_sm, unsigned *seg_vecs, unsigned *warp_
   if (!parsed) {
     const char *env = getenv("GPUARRAY_B200_RD");
     if (env != NULL)
-      sscanf(env, "%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm,
+      sscanf(env, "%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u,%u", &t_ctas, &t_seg, &t_warp, &rd_cols_ctas_per_sm,
              &rd_onerun_ctas_per_sm, &rd_onerun_lpl, &rd_onerun_mu, &rd_lazy, &rd_lazy_min,
              &rd_cols_by, &rd_simple, &rd_cols_early, &rd_lazy_onerun_min, &rd_warp_rows_per_sm,
-             &rd_subcta, &rd_wave_fit);
+             &rd_subcta, &rd_wave_fit, &rd_tiny);
     *warp_bytes = t_warp;
     if (t_ctas == 0) t_ctas = 32;
     if (t_seg == 0) t_seg = 8;
@@ -616,6 +619,29 @@ static int rd_plan(const rd_plan_in *in, rd_layout *L, rd_variant *want, unsigne
       /* loads one lane of a warp issues per run: short runs need help to keep
        * enough bytes in flight (see the kernel's comment) */
       unsigned long long nload = nvrow + (L->inner % (unsigned)want->vec != 0);
+      if (rd_tiny && rows_outer == 1 && nload <= 8 && (nload & (nload - 1)) == 0 && elsize > 1 &&
+          (unsigned long long)want->vec * elsize == 16 && L->inner % (unsigned)want->vec == 0 &&
+          L->nf == 1 && L->fsrc[0] == (long long)(L->inner * elsize) &&
+          L->nf_total * nload < 0x7fffffffULL && !(in->kind == 0 && elsize == 8)) {
+        /* runs of 16-128 bytes, back to back: the flat walk (GA_RD_TINY in the template).
+         * Measured on B200, 256 MiB, against the short-run path below: fp32 rows of 4: MAX
+         * 98.6 -> 54.0 us, SUM 59.8 -> 51.1 us; rows of 16: ARGMAX 58.8 -> 49.7 us, MAX AND
+         * ARGMAX 65.4 -> 57.2 us, SUM 45.2 -> 44.6 us; rows of 32: 55.4 / 57.6 / 60.7 / 47.2 ->
+         * 52.2 / 51.6 / 56.7 / 44.1 us; fp16 rows of 32: MAX AND ARGMAX 86.7 -> 64.0 us; fp64
+         * rows of 8: MAX 63.4 -> 53.4 us but SUM 47.6 -> 51.8 us (two 64-bit shuffle steps for
+         * two adds), hence the exception. */
+        unsigned long long vectors = L->nf_total * nload;
+        want->tiny = 1;
+        want->group = (int)nload;
+        want->mu = 1;
+        L->seg = L->inner;
+        L->nseg = 1;
+        L->units = 1;
+        blocks = (vectors + 4ULL * RD_THREADS - 1) / (4ULL * RD_THREADS);
+        if (blocks > (unsigned long long)in->num_sms * 8) blocks = (unsigned long long)in->num_sms * 8;
+        grid[0] = (unsigned)blocks;
+        goto rows_done;
+      }
       if (rows_outer == 1 && nload <= 256) {
         unsigned g = 1, lpl;
         while (g < 32 && g * rd_onerun_lpl < nload) g *= 2;
@@ -907,6 +933,7 @@ static int plan_worker(int op, int src_tc, int dst_tc, unsigned int nd, const si
   out[16] = block[0];
   out[17] = block[1];
   out[20] = (unsigned long long)want.simple;
+  out[21] = (unsigned long long)want.tiny;
   if (layout_out != NULL) *layout_out = L;
   return GA_NO_ERROR;
 }

@@ -57,6 +57,11 @@
 #ifndef GA_RD_ONERUN
 #define GA_RD_ONERUN 0 /* rows: every output is one short contiguous run and nothing is split */
 #endif
+#ifndef GA_RD_TINY
+#define GA_RD_TINY 0 /* rows: every output is one run of 1, 2, 4 or 8 full vectors and the runs lie
+                        back to back: the source is walked as ONE flat array of vectors,
+                        GA_RD_GROUP (= vectors per run) adjacent lanes share an output */
+#endif
 #ifndef GA_RD_SIMPLE
 #define GA_RD_SIMPLE 0 /* rows: every output is ONE contiguous run owned by one warp, nothing is
                           split, fewer than 2^32 outputs: a lean loop with 32-bit indices */
@@ -523,7 +528,56 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
   const ga__u64 ngroups = (ga__u64)gridDim.x * (GA_RD_THREADS / GA_RD_GROUP);
   const ga__u64 rounds = (nwork + ngroups - 1) / ngroups;
 
-#if GA_RD_SIMPLE
+#if GA_RD_TINY
+  /* Runs of at most 128 bytes, back to back in memory. A thread per run (the mapping the
+   * short-run path below would choose) makes every load instruction of a warp touch 32
+   * runs a fragment each - the L1 becomes the limiter (64-73 % of its throughput for rows of
+   * 16 floats) - and lanes sharing a run there repeat the per-run work (output offset
+   * decoding, first-element check, emit) in every lane. Here consecutive threads take
+   * consecutive VECTORS of the whole source, four in flight per thread, so every load
+   * instruction is one contiguous 512 bytes; the GA_RD_GROUP lanes holding a run combine
+   * with shuffles and the first of them, which holds the run's first element, writes. */
+  {
+    const unsigned int nvec = (unsigned int)L.nf_total * GA_RD_GROUP; /* host: below 2^31 */
+    const unsigned int step = gridDim.x * GA_RD_THREADS;
+    const unsigned int sub = threadIdx.x % GA_RD_GROUP;
+    const ga__rd_pack<GA_RD_VEC> *pv = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(src);
+    const GA_RD_IDX_T f0 = (GA_RD_IDX_T)(sub * GA_RD_VEC) * imul;
+    for (unsigned int q0 = blockIdx.x * GA_RD_THREADS + threadIdx.x; q0 < nvec; q0 += 4u * step) {
+      ga__rd_pack<GA_RD_VEC> t[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const unsigned int q = q0 + (unsigned int)u * step;
+        t[u] = pv[q < nvec ? q : q0]; /* past the end: a reload that is dropped below */
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const unsigned int q = q0 + (unsigned int)u * step;
+        ga__state st = ga__init();
+        ga__fold_one(st, t[u], f0, imul);
+        st = ga__lanes_reduce<GA_RD_GROUP>(st); /* whole warps get here: q0 < nvec holds for
+                                                   all lanes of a group or for none */
+        if (sub == 0 && q < nvec) {
+          const unsigned int o = q / GA_RD_GROUP;
+#if GA_RD_KIND == 1 && GA_RD_ISFLOAT
+          const GA_RD_X_T first = GA_RD_LOAD(t[u].v[0]);
+          if (L.nan_first != 0 && first != first) {
+            st.v = first;
+            st.i = 0;
+          }
+#endif
+#if GA_RD_WRITE_VAL
+          *reinterpret_cast<GA_RD_DST_T *>(d0 + (ga__i64)o * L.fdst0[0]) = GA_RD_STORE(st.v);
+#endif
+#if GA_RD_KIND == 1 && GA_RD_WRITE_IDX
+          *reinterpret_cast<ga__u64 *>(d1 + (ga__i64)o * L.fdst1[0]) =
+              (st.i == GA__IDX_NONE) ? ~(ga__u64)0 : (ga__u64)st.i + L.ioff;
+#endif
+        }
+      }
+    }
+  }
+#elif GA_RD_SIMPLE
   /* A warp per output, one contiguous run each, nothing split. Few live values besides
    * the vectors in flight: the kernel needs about half the registers of the general
    * loop below, so the CTAs of the NEXT launch of the stream find room to become

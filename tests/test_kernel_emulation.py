@@ -22,7 +22,7 @@ SIMT = os.path.join(ROOT, "tests", "simt")
 TEMPLATES = os.path.join(ROOT, "libgpuarray_b200", "csrc", "templates")
 BUILD = os.path.join(ROOT, "libgpuarray_b200", "build", "simt")
 KEYS = ["shape", "vec", "group", "flat", "mu", "onerun", "lazy", "fast8", "tpo", "idx64", "splits",
-        "seg", "nseg", "units", "gx", "gy", "bx", "by", "nf", "nr", "simple"]
+        "seg", "nseg", "units", "gx", "gy", "bx", "by", "nf", "nr", "simple", "tiny"]
 ENTRY = ["ga_rd_rows", "ga_rd_cols", "ga_rd_general"]
 
 LAUNCHER = r'''
@@ -62,7 +62,7 @@ def build_variant(api, op, x, dst_dtype, p):
     L = api.lib()
     L.gpuarray_b200_reduction_source.restype = ctypes.c_void_p
     group = p["group"] | (p["mu"] << 16) | (p["onerun"] << 20) | (p["flat"] << 21) | \
-        (p.get("simple", 0) << 22) | ((p["by"] if p["shape"] == 1 else 0) << 24)
+        (p.get("simple", 0) << 22) | (p.get("tiny", 0) << 23) | ((p["by"] if p["shape"] == 1 else 0) << 24)
     ptr = L.gpuarray_b200_reduction_source(getattr(api, "GA_REDUCE_" + op), api.typecode(x.dtype),
                                            api.typecode(np.dtype(dst_dtype)), p["shape"], p["vec"],
                                            p["idx64"], p["tpo"], group)
@@ -204,11 +204,36 @@ def test_64_bit_index_builds_on_the_emulator(api, oracle, rng):
 def test_short_run_variants_on_the_emulator(api, oracle, rng):
     # one short run per output: 1, 2, 8 and 32 lanes per output, several outputs at once
     for cols, group in ((4, 1), (8, 2), (32, 2), (100, 8), (512, 32)):
-        x = ties(rng, (301, cols))
-        p = check(api, oracle, "SUM", x, [1], expect={"onerun": 1})
+        x = ties(rng, (301, cols + 4))[:, :cols]     # a pitch wider than the run: not the flat walk
+        p = check(api, oracle, "SUM", x, [1], expect={"onerun": 1, "tiny": 0})
         assert p["group"] <= 32 and p["mu"] in (2, 4)
         check(api, oracle, "MAXANDARGMAX", x, [1], expect={"onerun": 1})
         check(api, oracle, "ARGMIN", x, [1])
+    # runs of 1, 2, 4, 8 full vectors lying back to back: the source walked as one flat array
+    # of vectors, lanes-per-run = vectors per run; NaN first, NaNs later, signed zeros, ties,
+    # a row of the identity; a count of vectors that leaves the last batch ragged
+    for dtype, cols in ((np.float32, 4), (np.float32, 8), (np.float32, 16), (np.float32, 32),
+                        (np.float64, 2), (np.float64, 16), (np.float16, 8), (np.float16, 64), (np.int32, 16)):
+        x = ties(rng, (301, cols), dtype)
+        if np.dtype(dtype).kind == "f":
+            x[0, 0] = np.nan
+            x[1, cols - 1] = np.nan
+            x[2, :] = -np.inf
+            x[3, :] = -1
+            x[3, cols // 2] = -0.0
+            x[3, cols - 1] = 0.0
+            x[4, :] = np.nan
+        want = {"tiny": 1, "onerun": 0, "group": cols * np.dtype(dtype).itemsize // 16}
+        check(api, oracle, "MAXANDARGMAX", x, [1], expect=want)
+        check(api, oracle, "MIN", x, [1], expect=want)
+        check(api, oracle, "ARGMAX", x, [1], expect=want)
+        if dtype == np.float64:                      # 8-byte sums stay on the short-run path (measured)
+            check(api, oracle, "SUM", ties(rng, (301, cols), dtype), [1], expect={"tiny": 0, "onerun": 1})
+        elif dtype != np.float16:
+            check(api, oracle, "SUM", ties(rng, (301, cols), dtype), [1], expect=want)
+    check(api, oracle, "SUM", ties(rng, (5000, 16)), [1], expect={"tiny": 1, "group": 4}, sms=1)
+    check(api, oracle, "SUM", ties(rng, (301, 12)), [1], expect={"tiny": 0})       # 3 vectors per run
+    check(api, oracle, "SUM", ties(rng, (301, 64)), [1], expect={"tiny": 0, "onerun": 1})
     # (value, index) over one short run with several vectors per lane: values-only scan, then
     # the element, its bit pattern and its index from the winning vector; NaN first, NaNs
     # before the only candidate, signed zeros, ties, rows of the identity

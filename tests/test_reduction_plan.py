@@ -9,7 +9,7 @@ import pytest
 
 SHAPE_ROWS, SHAPE_COLS, SHAPE_GENERAL = 0, 1, 2
 KEYS = ["shape", "vec", "group", "flat", "mu", "onerun", "lazy", "fast8", "tpo", "idx64", "splits",
-        "seg", "nseg", "units", "gx", "gy", "bx", "by", "nf", "nr", "simple"]
+        "seg", "nseg", "units", "gx", "gy", "bx", "by", "nf", "nr", "simple", "tiny"]
 
 
 def plan(api, op, dt, dims, strides, axes, base=0x7f0000000000, sms=148, dst=None):
@@ -49,6 +49,10 @@ def check_invariants(p, itemsize, kind_pair):
         assert p["splits"] <= max(p["units"], 1)
         if p["onerun"]:
             assert p["units"] == 1 and p["splits"] == 1 and p["mu"] in (2, 4) and p["group"] <= 32
+        elif p["tiny"]:
+            assert p["units"] == 1 and p["splits"] == 1 and p["group"] in (1, 2, 4, 8) and p["mu"] == 1
+            assert p["vec"] * itemsize == 16 and p["nf"] * p["group"] < 2 ** 31
+            assert p["nr"] == p["group"] * p["vec"] and p["gx"] <= 148 * 8
         else:
             assert p["group"] in (32, 64, 128, 256)
         if p["group"] > 32:
@@ -89,8 +93,20 @@ def test_named_configurations_get_the_intended_kernels(api):
     assert err == 0 and p["group"] == 32 and p["nf"] == 1024 and p["splits"] == 37
     assert p["nr"] * 8 // p["splits"] >= 24 * 1024
     # short runs: part of a warp per output, several outputs at once, 3 CTAs per SM
+    err, p = plan(api, "SUM", np.float32, [1 << 21, 40], [160, 4], [1])
+    assert err == 0 and p["onerun"] == 1 and p["group"] == 4 and p["mu"] == 2 and p["gx"] == 148 * 3
+    err, p = plan(api, "SUM", np.float32, [1 << 21, 32], [160, 4], [1])          # a pitch wider than the run
+    assert err == 0 and p["onerun"] == 1 and p["group"] == 2 and p["tiny"] == 0
+    # runs of 1, 2, 4, 8 vectors back to back: one flat walk over the vectors, lanes per run =
+    # vectors per run, 8 CTAs per SM at most; MIN / MAX / ARG* of rows of 16: the same
     err, p = plan(api, "SUM", np.float32, [1 << 21, 32], c_strides([1 << 21, 32], 4), [1])
-    assert err == 0 and p["onerun"] == 1 and p["group"] == 2 and p["mu"] == 2 and p["gx"] == 148 * 3
+    assert err == 0 and p["tiny"] == 1 and p["onerun"] == 0 and p["group"] == 8 and p["gx"] == 148 * 8
+    err, p = plan(api, "MAX", np.float32, [1 << 22, 16], c_strides([1 << 22, 16], 4), [1])
+    assert err == 0 and p["tiny"] == 1 and p["group"] == 4 and p["vec"] == 4
+    err, p = plan(api, "MAX", np.float32, [100, 16], c_strides([100, 16], 4), [1])
+    assert err == 0 and p["tiny"] == 1 and p["gx"] == 1
+    err, p = plan(api, "MAX", np.float32, [1 << 22, 12], c_strides([1 << 22, 12], 4), [1])   # 3 vectors
+    assert err == 0 and p["tiny"] == 0 and p["onerun"] == 1
     # ARGMAX over 1024-element rows: one run per output, 32 lanes x 8 vectors, values-only scan;
     # 512-element rows (4 vectors per lane) compare pairs element by element
     err, p = plan(api, "ARGMAX", np.float32, [1 << 16, 1024], c_strides([1 << 16, 1024], 4), [1])
