@@ -543,20 +543,72 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
     const unsigned int sub = threadIdx.x % GA_RD_GROUP;
     const ga__rd_pack<GA_RD_VEC> *pv = reinterpret_cast<const ga__rd_pack<GA_RD_VEC> *>(src);
     const GA_RD_IDX_T f0 = (GA_RD_IDX_T)(sub * GA_RD_VEC) * imul;
-    for (unsigned int q0 = blockIdx.x * GA_RD_THREADS + threadIdx.x; q0 < nvec; q0 += 4u * step) {
+    /* the loop bound is the WARP's first vector, so that whole warps iterate (the shuffles
+     * below name all 32 lanes); lanes past the end load vector 0 and drop the result */
+    const unsigned int lane32 = threadIdx.x & 31u;
+    for (unsigned int q0 = blockIdx.x * GA_RD_THREADS + threadIdx.x; q0 - lane32 < nvec;
+         q0 += 4u * step) {
       ga__rd_pack<GA_RD_VEC> t[4];
 #pragma unroll
       for (int u = 0; u < 4; u++) {
         const unsigned int q = q0 + (unsigned int)u * step;
-        t[u] = pv[q < nvec ? q : q0]; /* past the end: a reload that is dropped below */
+        t[u] = pv[q < nvec ? q : 0u];
       }
+#if GA_RD_KIND == 1 && GA_RD_WRITE_VAL && !GA_RD_WRITE_IDX && defined(GA_RD_PICK)
+      /* MIN / MAX without an index: values only - one instruction per element and per
+       * shuffle step instead of compare-and-select on (value, index) pairs. fmax / fmin skip
+       * NaNs as the pair rule does. The one thing the pair rule decides that values cannot
+       * is the sign of a zero result (the FIRST zero of the run wins): when any lane of the
+       * warp sees a zero result, the lanes find the position and sign of their first zero
+       * and the lowest position of the group supplies the sign. */
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const unsigned int q = q0 + (unsigned int)u * step;
+        GA_RD_X_T m = (GA_RD_X_T)(GA_RD_IDENT);
+#pragma unroll
+        for (int j = 0; j < GA_RD_VEC; j++) {
+          const GA_RD_X_T x = GA_RD_LOAD(t[u].v[j]);
+          m = GA_RD_PICK(m, x);
+        }
+#pragma unroll
+        for (int d = GA_RD_GROUP / 2; d > 0; d >>= 1) {
+          const GA_RD_X_T other = ga__shfl_down(m, d); /* once: the macro may name it twice */
+          m = GA_RD_PICK(m, other);
+        }
+#if GA_RD_ISFLOAT
+        if (__any_sync(0xffffffffu, m == (GA_RD_X_T)0)) {
+          unsigned int key = 0xffffffffu;
+#pragma unroll
+          for (int j = GA_RD_VEC - 1; j >= 0; j--) {
+            unsigned char raw[sizeof(GA_RD_SRC_T)];
+            memcpy(raw, &t[u].v[j], sizeof(raw));
+            if (GA_RD_LOAD(t[u].v[j]) == (GA_RD_X_T)0)
+              key = ((sub * GA_RD_VEC + (unsigned int)j) << 1) | (unsigned int)(raw[sizeof(raw) - 1] >> 7);
+          }
+#pragma unroll
+          for (int d = GA_RD_GROUP / 2; d > 0; d >>= 1) {
+            const unsigned int other = ga__shfl_down(key, d);
+            key = other < key ? other : key;
+          }
+          if (m == (GA_RD_X_T)0 && key != 0xffffffffu) m = (key & 1u) ? -(GA_RD_X_T)0 : (GA_RD_X_T)0;
+        }
+#endif
+        if (sub == 0 && q < nvec) {
+#if GA_RD_ISFLOAT
+          const GA_RD_X_T first = GA_RD_LOAD(t[u].v[0]);
+          if (L.nan_first != 0 && first != first) m = first;
+#endif
+          *reinterpret_cast<GA_RD_DST_T *>(d0 + (ga__i64)(q / GA_RD_GROUP) * L.fdst0[0]) = GA_RD_STORE(m);
+        }
+      }
+#else
 #pragma unroll
       for (int u = 0; u < 4; u++) {
         const unsigned int q = q0 + (unsigned int)u * step;
         ga__state st = ga__init();
         ga__fold_one(st, t[u], f0, imul);
-        st = ga__lanes_reduce<GA_RD_GROUP>(st); /* whole warps get here: q0 < nvec holds for
-                                                   all lanes of a group or for none */
+        st = ga__lanes_reduce<GA_RD_GROUP>(st); /* q < nvec holds for all lanes of a group or
+                                                   for none: nvec is a multiple of the group */
         if (sub == 0 && q < nvec) {
           const unsigned int o = q / GA_RD_GROUP;
 #if GA_RD_KIND == 1 && GA_RD_ISFLOAT
@@ -575,6 +627,7 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
 #endif
         }
       }
+#endif
     }
   }
 #elif GA_RD_SIMPLE

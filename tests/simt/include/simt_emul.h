@@ -116,6 +116,15 @@ static inline T __shfl_sync(unsigned, T v, int src, int width = 32) {
   return simt__shfl(v, (unsigned)src % (unsigned)width, width);
 }
 
+static inline int __any_sync(unsigned, int pred) {
+  const unsigned w = simt::cur->linear / 32, lane = simt::cur->linear % 32, n = simt::warp_lanes(w);
+  simt::warp_slot[w][lane] = pred != 0;
+  simt::warp_barrier(w, n);
+  int r = 0;
+  for (unsigned l = 0; l < n; l++) r |= (int)simt::warp_slot[w][l];
+  simt::warp_barrier(w, n);
+  return r;
+}
 static inline unsigned int atomicAdd(unsigned int *p, unsigned int v) {
   const unsigned int old = *p;
   *p = old + v;

@@ -232,6 +232,10 @@ def test_short_run_variants_on_the_emulator(api, oracle, rng):
         elif dtype != np.float16:
             check(api, oracle, "SUM", ties(rng, (301, cols), dtype), [1], expect=want)
     check(api, oracle, "SUM", ties(rng, (5000, 16)), [1], expect={"tiny": 1, "group": 4}, sms=1)
+    # the vectors end inside a warp (100 and 400 of 256 threads' worth): whole warps keep iterating
+    check(api, oracle, "MAXANDARGMAX", ties(rng, (100, 4)), [1], expect={"tiny": 1, "gx": 1})
+    check(api, oracle, "MINANDARGMIN", ties(rng, (100, 16)), [1], expect={"tiny": 1, "gx": 1})
+    check(api, oracle, "SUM", ties(rng, (1030, 4)), [1], expect={"tiny": 1})
     check(api, oracle, "SUM", ties(rng, (301, 12)), [1], expect={"tiny": 0})       # 3 vectors per run
     check(api, oracle, "SUM", ties(rng, (301, 64)), [1], expect={"tiny": 0, "onerun": 1})
     # (value, index) over one short run with several vectors per lane: values-only scan, then
