@@ -595,6 +595,35 @@ def sharded_configs(api, ctx, torch, dist, stream, rank, world, host_slab, t1_cf
     return out
 
 
+def prefer_host_memory_near(ctx_ptr, api):
+    """Host-side placement of the pinned input slab: asks the kernel to take this
+    process's next pages from the NUMA node the GPU's PCIe root hangs off
+    (set_mempolicy MPOL_PREFERRED), so that with several ranks per host each
+    GPU's DMA reads cross no socket link. Returns (node, restore) - restore()
+    puts the default policy back; node is None when the platform does not say
+    (no sysfs entry, one node, not x86-64) and nothing was changed. Touches no
+    GPU setting."""
+    import ctypes
+    import platform
+    none = (None, lambda: None)
+    try:
+        buf = ctypes.create_string_buffer(16)
+        if api.lib().gpucontext_property(ctx_ptr, 19, buf) != 0:      # GA_CTX_PROP_UNIQUE_ID: PCI bus id
+            return none
+        pci = buf.value.decode().strip().lower()
+        with open("/sys/bus/pci/devices/%s/numa_node" % pci) as f:
+            node = int(f.read().strip())
+        if node < 0 or node > 62 or platform.machine() != "x86_64":
+            return none
+        libc = ctypes.CDLL(None, use_errno=True)
+        mask = ctypes.c_ulong(1 << node)
+        if libc.syscall(238, 1, ctypes.byref(mask), 65) != 0:          # set_mempolicy(MPOL_PREFERRED, ...)
+            return none
+        return node, lambda: libc.syscall(238, 0, None, 0)             # MPOL_DEFAULT
+    except Exception:
+        return none
+
+
 def run_ours(args, rank, world, local_rank):
     global ROWS
     ROWS = args.rows
@@ -612,8 +641,14 @@ def run_ours(args, rank, world, local_rank):
     peak, peak_kind = measured_peak()
 
     # ---- data: host slab in pinned memory, device copy for the resident run
+    numa_node, restore_policy = prefer_host_memory_near(ctx.ptr, api) if not args.no_numa else (None, lambda: None)
     host = torch.empty((ROWS, COLS), dtype=torch.float32, pin_memory=True)
     host.numpy()[...] = make_logits(rank, ROWS)
+    restore_policy()
+    numa_nodes = [numa_node]
+    if world > 1:
+        numa_nodes = [None] * world
+        dist.all_gather_object(numa_nodes, numa_node)
     gx = api.GpuArray.empty(ctx, (ROWS, COLS), np.float32)
     gx.write_raw(host.data_ptr(), host.numel() * 4)
     gmax = api.GpuArray.empty(ctx, (ROWS,), np.float32)
@@ -741,7 +776,8 @@ def run_ours(args, rank, world, local_rank):
         "config": bench_config(ROWS),
         "frac_of_nominal_8TBs_per_gpu": per_gpu / NOMINAL_HBM_GBS,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": ROWS * COLS * 4,
-                "d2h_bytes_per_step": ROWS * 12, "steps": e2e_steps},
+                "d2h_bytes_per_step": ROWS * 12, "steps": e2e_steps,
+                "host_slab_numa_node_per_rank": numa_nodes},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
                      "frac": per_gpu / peak, "peak_kind": peak_kind, "kernel": "ga_rd_rows",
@@ -810,6 +846,8 @@ def main():
     ap.add_argument("--other-shapes", action="store_true",
                     help="also time reductions and elementwise calls on shapes outside the five "
                          "named configurations (adds an `other_shapes` object to the line)")
+    ap.add_argument("--no-numa", action="store_true",
+                    help="leave the placement of the pinned host slab to the default policy")
     ap.add_argument("--only", default=None,
                     help="with --other-shapes: run only the cases whose name contains this text "
                          "(profiler captures of one kernel)")
