@@ -334,6 +334,71 @@ def test_short_runs_nan_first_and_ties(api, ctx, oracle):
         check_reduce(api, ctx, oracle, name, x, [1])
 
 
+@pytest.mark.parametrize("dt,cols", [(np.float32, 4), (np.float32, 8), (np.float32, 16), (np.float32, 32),
+                                     (np.float64, 2), (np.float64, 8), (np.float16, 8), (np.float16, 64),
+                                     (np.int32, 16), (np.int16, 32)])
+def test_tiny_runs_walked_as_one_array_of_vectors(api, ctx, oracle, rng, dt, cols):
+    """Rows of 1, 2, 4 or 8 full vectors lying back to back (GA_RD_TINY): every operator kind,
+    row counts whose vectors end inside a warp, the NaN-first rule from the writing lane's own
+    vector, the first zero's sign in the values-only MIN / MAX, strided destinations, and a
+    shard (global indices, no NaN-first rule)."""
+    for rows in (100, 1030, 7, 4097):
+        x = (np.round(rng.standard_normal((rows, cols)) * 2) / 2).astype(dt)
+        if np.dtype(dt).kind == "f":
+            x[0, 0] = np.nan
+            x[1, cols - 1] = np.nan
+            x[2, :] = -np.inf
+            x[3, :] = -1
+            x[3, cols // 2] = -0.0
+            x[3, cols - 1] = 0.0
+            x[4, :] = 1
+            x[4, 0] = 0.0
+            x[4, cols - 1] = -0.0
+            x[5, :] = np.nan
+        g = api.GpuArray.from_numpy(ctx, x)
+        for name in ("max", "min", "argmax", "argmin", "maxandargmax", "minandargmin"):
+            want_v, want_i = oracle.minmaxarg(x, [1], is_min="min" in name)
+            d0 = api.GpuArray.empty(ctx, (rows,), x.dtype) if name not in ("argmin", "argmax") else None
+            d1 = api.GpuArray.empty(ctx, (rows,), np.int64) if name not in ("min", "max") else None
+            api.GpuReduction(ctx, opcode(api, name), x.dtype)(d0, d1, g, [1])
+            if d0 is not None:
+                got = d0.to_numpy()
+                nan = np.isnan(want_v) if x.dtype.kind == "f" else np.zeros(rows, bool)
+                # a float16 NaN comes back as a NaN, not necessarily with the same payload
+                assert (np.isnan(got) == nan).all() if x.dtype.kind == "f" else True
+                assert got[~nan].tobytes() == want_v[~nan].tobytes(), (name, rows)
+                if x.dtype != np.float16:
+                    assert got.tobytes() == want_v.tobytes(), (name, rows)
+            if d1 is not None:
+                assert (d1.to_numpy() == want_i).all(), (name, rows)
+        clean = (np.round(rng.standard_normal((rows, cols)) * 2) / 2).astype(dt)
+        check_reduce(api, ctx, oracle, "sum", clean, [1])
+    # destinations with strides, and the same rows as the second shard of a longer axis
+    rows = 333
+    x = (np.round(rng.standard_normal((rows, cols)) * 2) / 2).astype(dt)
+    if np.dtype(dt).kind == "f":
+        x[0, 0] = np.nan                                   # not the first element of the WHOLE extent
+    g = api.GpuArray.from_numpy(ctx, x)
+    wide_v = api.GpuArray.from_numpy(ctx, np.full((rows, 3), 9, np.dtype(dt)))
+    wide_i = api.GpuArray.from_numpy(ctx, np.full((rows, 2), -9, np.int64))
+    gr = api.GpuReduction(ctx, api.GA_REDUCE_MAXANDARGMAX, np.dtype(dt))
+    gr(wide_v[:, 1], wide_i[:, 0], g, [1])
+    wv, wi = oracle.minmaxarg(x, [1])
+    got_v, got_i = wide_v.to_numpy(), wide_i.to_numpy()
+    keep = ~np.isnan(wv) if np.dtype(dt).kind == "f" else np.ones(rows, bool)
+    assert got_v[keep, 1].tobytes() == wv[keep].tobytes() and (got_i[:, 0] == wi).all()
+    assert np.dtype(dt).kind != "f" or np.isnan(got_v[~keep, 1]).all()
+    assert (got_v[:, 0] == 9).all() and (got_v[:, 2] == 9).all() and (got_i[:, 1] == -9).all()
+    full = np.concatenate([np.ones((rows, cols), np.dtype(dt)) * 0 - 5, x], axis=1)      # the shard is the tail
+    dv = api.GpuArray.empty(ctx, (rows,), np.dtype(dt))
+    di = api.GpuArray.empty(ctx, (rows,), np.int64)
+    api.reduction_call_sharded(gr, None, dv, di, g, [1], cols, 2 * cols)
+    sv, si = oracle.minmaxarg(full[:, cols:], [1])
+    nan_rows = np.isnan(x[:, 0]) if np.dtype(dt).kind == "f" else np.zeros(rows, bool)
+    ok = ~nan_rows                                         # a leading NaN of a later shard never wins
+    assert (di.to_numpy()[ok] == si[ok] + cols).all() and dv.to_numpy()[ok].tobytes() == sv[ok].tobytes()
+
+
 @pytest.mark.parametrize("shape,axes", [((5, 4100), [1]), ((2100, 36), [0]), ((30, 7, 600), [0, 2])])
 def test_kernel_paths_fp64_and_fp16(api, ctx, oracle, rng, shape, axes):
     for dt in (np.float64, np.float16):
