@@ -433,7 +433,7 @@ static int peer_window_setup(gpucomm *comm) {
     else peer_window_refuse(comm, "%s: CUDA error %d", "window allocation or export", (int)cr);
   }
 
-  /* round 1: everyone's hello */
+  /* first exchange: everyone's hello */
   all = calloc((size_t)n, sizeof(*all));
   if (all == NULL) { err = ga_err_sys(ctx->err, "calloc"); goto out; }
   cr = ga_cu.p_cuMemAlloc(&stage, sizeof(xc_hello) * (size_t)(n + 1));
@@ -462,7 +462,7 @@ static int peer_window_setup(gpucomm *comm) {
           peer_window_refuse(comm, "%srank %d shares a GPU or a process with another rank", "", p);
       }
   }
-  /* round 2: map the peers; then agree on whether everyone could */
+  /* second exchange: map the peers; then agree on whether everyone could */
   if (agreed) {
     for (p = 0; p < n && opened; p++) {
       if (p == me) continue;

@@ -242,6 +242,80 @@ def _transfer_worker(q_err):
         q_err.put("transfer: %s\n%s" % (e, traceback.format_exc()))
 
 
+def _absent_rank_worker(rank, world, q_id, q_err, ready, done):
+    """Failure detection without a fault: after one complete exchange, rank 1 simply makes no
+    further call (it sits idle on the host, nothing of it in flight) while rank 0 makes one
+    more. Rank 0's exchange kernel waits for a flag that nothing sets, gives up after the
+    300 ms limit and returns; the host then finds the status word set and refuses further
+    sharded calls on that communicator."""
+    try:
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
+        os.environ["GPUARRAY_B200_PEER_TIMEOUT_MS"] = "300"
+        from libgpuarray_b200 import api
+        ctx = api.Context(rank, kernel_cache=os.path.join(ROOT, ".kernel_cache"))
+        if rank == 0:
+            cid = api.GpuComm.gen_clique_id(ctx)
+            q_id.put(cid)
+        else:
+            cid = q_id.get(timeout=120)
+        comm = api.GpuComm(ctx, cid, world, rank)
+        x = np.arange(64 * 100, dtype=np.float64).reshape(64, 100)
+        g = api.GpuArray.from_numpy(ctx, x[rank * 32:(rank + 1) * 32])
+        gr = api.GpuReduction(ctx, api.GA_REDUCE_SUM, np.float64)
+        d = api.GpuArray.empty(ctx, (100,), np.float64)
+        api.reduction_call_sharded(gr, comm, d, None, g, [0], rank * 32, 64)        # both ranks: complete
+        ctx.sync()
+        first = d.to_numpy()
+        state = comm.peer_state()
+        ready.wait(timeout=60) if rank == 0 else ready.set()                        # rank 1 is idle from here on
+        if rank == 0:
+            import time
+            t0 = time.perf_counter()
+            api.reduction_call_sharded(gr, comm, d, None, g, [0], 0, 64)            # nobody answers
+            ctx.sync()
+            waited = time.perf_counter() - t0
+            after = comm.peer_state()
+            code = 0
+            try:
+                api.reduction_call_sharded(gr, comm, d, None, g, [0], 0, 64)
+            except api.GpuArrayException as e:
+                code = e.code
+            done.set()
+            assert state[0] == 1 and state[2] == 0 and (first == x.sum(0)).all()
+            assert after[2] != 0, after
+            assert 0.25 <= waited < 5.0, waited
+            assert code == api.GA_COMM_ERROR, code
+        else:
+            done.wait(timeout=60)
+            assert state[0] == 1 and (first == x.sum(0)).all()
+        comm.free()
+        ctx.close()
+    except Exception as e:
+        import traceback
+        q_err.put("rank %d: %s\n%s" % (rank, e, traceback.format_exc()))
+
+
+@pytest.mark.skipif(_ngpus() < 2, reason="needs two GPUs")
+def test_a_rank_that_stays_away_is_reported_after_a_bounded_wait():
+    import torch.multiprocessing as mp
+    m = mp.get_context("spawn")
+    q_id, q_err, ready, done = m.Queue(), m.Queue(), m.Event(), m.Event()
+    procs = [m.Process(target=_absent_rank_worker, args=(r, 2, q_id, q_err, ready, done)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:
+        p.kill()
+    msgs = []
+    while not q_err.empty():
+        msgs.append(q_err.get())
+    assert not hung, "rank hung"
+    assert not msgs, "\n".join(msgs)
+    assert all(p.exitcode == 0 for p in procs)
+
+
 @pytest.mark.skipif(_ngpus() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("peer", [True, False], ids=["peer_windows", "nccl_all_reduce"])
 def test_sharded_reduction_with_gpucomm(peer):

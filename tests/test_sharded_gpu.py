@@ -3,8 +3,8 @@ the two all-reduces): a source that is a slab of a larger array along a
 reduced axis. Checked against the CPU oracle on the whole array: the indices
 written are flat indices of the WHOLE reduced extent, ties go to the lowest
 global index, the NaN-first rule applies only to the slab holding element 0
-(src/gpuarray_reduction.c:557-606 for the rule, SURVEY of the reference's
-collectives src/gpuarray_collectives_cuda_nccl.c:158-185 for why the
+(src/gpuarray_reduction.c:557-606 for the rule; the reference's collectives,
+src/gpuarray_collectives_cuda_nccl.c:158-185, have no pair operator, which is why the
 combination is built from max/min all-reduces). The two-rank run of the same
 entry point over NCCL is in test_multigpu.py; the protocol itself also runs
 over gloo on CPU (test_sharding_cpu.py)."""
