@@ -287,6 +287,30 @@ static __device__ __forceinline__ void ga__emit(const ga__rd_layout &L, const ch
 #endif
 }
 
+/* ga__emit for callers that still hold the first reduced element of the output in a
+ * register (its raw form): spares the load - and the wait for it at the end of every
+ * output - that ga__emit spends on the NaN-first rule */
+static __device__ __forceinline__ void ga__emit_with_first(const ga__rd_layout &L, char *d0, char *d1,
+                                                           const ga__u64 o, ga__state s,
+                                                           const GA_RD_SRC_T first_raw) {
+#if GA_RD_KIND == 1 && GA_RD_ISFLOAT
+  {
+    const GA_RD_X_T first = GA_RD_LOAD(first_raw);
+    if (L.nan_first != 0 && first != first) {
+      s.v = first;
+      s.i = 0;
+    }
+  }
+#endif
+#if GA_RD_WRITE_VAL
+  *reinterpret_cast<GA_RD_DST_T *>(d0 + ga__foff(L, L.fdst0, o)) = GA_RD_STORE(s.v);
+#endif
+#if GA_RD_KIND == 1 && GA_RD_WRITE_IDX
+  *reinterpret_cast<ga__u64 *>(d1 + ga__foff(L, L.fdst1, o)) =
+      (s.i == GA__IDX_NONE) ? ~(ga__u64)0 : (ga__u64)s.i + L.ioff;
+#endif
+}
+
 /* ga__emit when there is ONE kept dimension (the lean column walk): for accumulating
  * operators the offset is a single multiply - no coordinate decoding, no first-element
  * check - which also spares the kernel a spill */
@@ -685,6 +709,13 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
         st[k] = ga__init();
         base[k] = src + ga__foff(L, L.fsrc, w[k]);
       }
+      /* the run's first element, for the NaN-first rule when the output is written: asked for
+       * now, together with the run's vectors, instead of at the end of every output where the
+       * wait for it would be exposed (rows of 64 floats: MAX 53.3 -> 48.5 us, ARGMAX 55.0 -> 49.2 us,
+       * MAX AND ARGMAX 60.7 -> 55.1 us; rows of 1024: 51.5 / 51.7 / 53.4 -> 49.0 / 50.0 / 51.5 us) */
+      GA_RD_SRC_T first_raw[GA_RD_MU];
+#pragma unroll
+      for (int k = 0; k < GA_RD_MU; k++) first_raw[k] = *reinterpret_cast<const GA_RD_SRC_T *>(base[k]);
 #if GA_RD_LAZY
       /* (value, index) operators: scan values only, keeping per output the best value and
        * the first vector that reached it; the element, its bit pattern and its index are
@@ -762,8 +793,9 @@ ga_rd_rows(const __grid_constant__ ga__rd_layout L, const char *src, char *d0, c
       for (int k = 0; k < GA_RD_MU; k++) st[k] = ga__lanes_reduce<GA_RD_GROUP>(st[k]);
       if (lane == 0) {
 #pragma unroll
-        for (int k = 0; k < GA_RD_MU; k++)
-          if (live[k]) ga__emit(L, src, d0, d1, w[k], st[k]);
+        for (int k = 0; k < GA_RD_MU; k++) {
+          if (live[k]) ga__emit_with_first(L, d0, d1, w[k], st[k], first_raw[k]);
+        }
       }
     }
   }

@@ -209,6 +209,27 @@ def test_short_run_variants_on_the_emulator(api, oracle, rng):
         assert p["group"] <= 32 and p["mu"] in (2, 4)
         check(api, oracle, "MAXANDARGMAX", x, [1], expect={"onerun": 1})
         check(api, oracle, "ARGMIN", x, [1])
+    # one short run per output with the first element asked for up front: NaN first, NaNs later,
+    # NaNs only, a run of the identity, signed zeros in both orders, ties; ragged groups
+    for dtype, cols in ((np.float32, 100), (np.float32, 512), (np.float64, 200), (np.float16, 264), (np.int32, 60)):
+        x = ties(rng, (57, cols + 8), dtype)[:, :cols]
+        if np.dtype(dtype).kind == "f":
+            x[0, 0] = np.nan
+            x[1, cols - 1] = np.nan
+            x[2, :] = -np.inf
+            x[3, :] = -1
+            x[3, cols // 2] = -0.0
+            x[3, cols - 1] = 0.0
+            x[4, :] = np.nan
+            x[5, :] = 1
+            x[5, 1] = 0.0
+            x[5, cols - 2] = -0.0
+            x[6, :] = np.inf
+        for op in ("MAXANDARGMAX", "MINANDARGMIN", "ARGMAX", "MIN", "MAX"):
+            check(api, oracle, op, x, [1], expect={"onerun": 1})
+    check(api, oracle, "MAXANDARGMAX", ties(rng, (57, 104))[:, :101], [1], expect={"onerun": 1, "vec": 4})   # ragged end
+    check(api, oracle, "MAXANDARGMAX", ties(rng, (57, 110))[:, :101], [1], expect={"onerun": 1, "vec": 1})   # scalar loads
+    check(api, oracle, "SUM", ties(rng, (57, 108))[:, :100], [1], expect={"onerun": 1})
     # runs of 1, 2, 4, 8 full vectors lying back to back: the source walked as one flat array
     # of vectors, lanes-per-run = vectors per run; NaN first, NaNs later, signed zeros, ties,
     # a row of the identity; a count of vectors that leaves the last batch ragged
