@@ -143,6 +143,15 @@ GPUARRAY_PUBLIC int gpuarray_b200_mapreduction_plan(int out_tc, unsigned int n,
                                                     unsigned long long *out, void *layout,
                                                     size_t cap, size_t *used);
 
+/* Tooling hook: the split count a split row reduction is trimmed to so that its grid ends on
+ * a full or nearly full wave of resident CTAs (outputs x splits work items of `group` threads,
+ * 256 threads per CTA, `slots` CTAs resident at once); *ctas receives the grid size. */
+GPUARRAY_PUBLIC unsigned long long gpuarray_b200_reduction_fit_waves(unsigned long long outputs,
+                                                                     unsigned long long splits,
+                                                                     int group,
+                                                                     unsigned long long slots,
+                                                                     unsigned int *ctas);
+
 /* State of a communicator's peer-memory windows, through which
  * GpuReduction_call_sharded combines the ranks' partial results with one
  * kernel per GPU (every rank stores its partials into all peers' windows over

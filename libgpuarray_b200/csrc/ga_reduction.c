@@ -279,6 +279,30 @@ static void rd_fit_waves(rd_layout *L, const rd_variant *v, unsigned grid[3], un
   grid[0] = (unsigned)((L->nf_total * best + gpb - 1) / gpb);
 }
 
+/* Test hook: what rd_fit_waves makes of a split row reduction of `outputs` outputs planned
+ * with `splits` splits and `group` threads per work item on a device that holds `slots` CTAs
+ * at once. Returns the trimmed split count; *ctas receives the grid size. */
+GPUARRAY_PUBLIC unsigned long long gpuarray_b200_reduction_fit_waves(unsigned long long outputs,
+                                                                     unsigned long long splits,
+                                                                     int group,
+                                                                     unsigned long long slots,
+                                                                     unsigned int *ctas) {
+  rd_layout L;
+  rd_variant v;
+  unsigned grid[3] = {0, 1, 1};
+  memset(&L, 0, sizeof(L));
+  memset(&v, 0, sizeof(v));
+  L.nf_total = outputs;
+  L.splits = splits;
+  v.shape = SHAPE_ROWS;
+  v.group = group;
+  grid[0] = (unsigned)((outputs * splits + (unsigned long long)(RD_THREADS / group) - 1) /
+                       (unsigned long long)(RD_THREADS / group));
+  rd_fit_waves(&L, &v, grid, slots);
+  if (ctas != NULL) *ctas = grid[0];
+  return L.splits;
+}
+
 /* Test hook: source of one reduction kernel variant; caller frees. */
 GPUARRAY_PUBLIC char *gpuarray_b200_reduction_source(int op, int src_tc, int dst_tc, int shape,
                                                      int vec, int idx64, int tpo, int group) {

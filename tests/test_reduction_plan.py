@@ -168,3 +168,33 @@ def test_plan_invariants_over_random_and_extreme_shapes(api, rng):
 def test_plan_rejects_bad_axes(api, bad):
     err, _ = plan(api, "SUM", np.float32, [4, 5], [20, 4], bad["axes"])
     assert err == api.GA_INVALID_ERROR
+
+
+def test_split_counts_are_trimmed_to_whole_waves(api):
+    """rd_fit_waves (ga_reduction.c): grids a little over a whole number of waves of resident
+    CTAs lose their last, mostly idle, wave; grids within one wave and grids already ending on
+    a full or >= 70 % full wave stay; the count only ever goes down, by a third at most."""
+    f = api.lib().gpuarray_b200_reduction_fit_waves
+    f.restype = ctypes.c_ulonglong
+    f.argtypes = [ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_int, ctypes.c_ulonglong,
+                  ctypes.POINTER(ctypes.c_uint)]
+
+    def fit(outputs, splits, group=32, slots=592):
+        ctas = ctypes.c_uint()
+        s = int(f(outputs, splits, group, slots, ctypes.byref(ctas)))
+        return s, int(ctas.value)
+
+    assert fit(64, 170) == (148, 1184)          # (256, 64, 4096) over (0, 2): 2.3 waves -> 2.0
+    assert fit(512, 21) == (18, 1152)           # (512, 512, 256) over (1, 2): 2.27 -> 1.95 waves
+    assert fit(512, 21, slots=444) == (20, 1280)  # three CTAs per SM: 3.03 -> 2.88 waves
+    assert fit(256, 32) == (32, 1024)           # 1.73 waves: the last one is 73 % full, stays
+    assert fit(256, 16) == (16, 512)            # within one wave: untouched
+    assert fit(1024, 37) == (37, 4736)          # exactly 8 waves
+    assert fit(100, 3) == (3, 38)
+    s, c = fit(7, 1000)
+    assert 667 <= s <= 1000 and (c % 592 == 0 or c % 592 >= 415)
+    assert fit(64, 170, slots=0) == (170, 1360)  # occupancy unknown: nothing changes
+    # two warps per work item
+    assert fit(2048, 3, group=64) == (2, 1024)  # 2.59 waves -> 1.73
+    assert fit(2048, 7, group=64) == (7, 3584)  # 6.05 waves; 6 and 5 splits end on 19 % / 32 % full waves: left alone
+
