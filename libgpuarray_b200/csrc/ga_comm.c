@@ -553,6 +553,13 @@ int ga_comm_exchange(gpucomm *comm, int pair, int op, int tc, CUdeviceptr val, C
                       "communicator cannot be used any more");
   if (n == 0) return GA_NO_ERROR;
   {
+    /* what one rank puts into a slot: the values, then (16-byte aligned) the indices or the key */
+    const size_t idx_off = (n * es + 15) & ~(size_t)15;
+    const size_t need = pair == 1 ? idx_off + n * 8 : pair == 2 ? idx_off + 8 : n * es;
+    if (need > XC_SLOT_BYTES)
+      return ga_err_set(ctx->err, GA_VALUE_ERROR, "Result too large for the peer windows");
+  }
+  {
     /* every exchange carries its own sequence number: a captured launch replayed from a
      * CUDA graph would present an old one, find its flags already set and read stale slots */
     CUstreamCaptureStatus cap = CU_STREAM_CAPTURE_STATUS_NONE;

@@ -1343,8 +1343,9 @@ int GpuReduction_call_sharded(const GpuReduction *cgr, gpucomm *comm, GpuArray *
       return ga_err_set(ctx->err, GA_INVALID_ERROR, "Destination is NULL");
     if (comm != NULL && d1 == NULL &&
         (!tc_is_float(gr->src_tc) || (reduxLen > 0 && reduxList[0] == shard_axis)) &&
-        ga_comm_peer_ready(comm, sh_count(d0) * gpuarray_get_elsize(gr->src_tc))) {
-      /* MIN / MAX without an index: the value-only kernel, then the exchange with the
+        ga_comm_peer_ready(comm, sh_count(d0) * gpuarray_get_elsize(gr->src_tc) + 32)) {
+      /* (+ 32: the rank's key follows the values in its slot, 16-byte aligned)
+       * MIN / MAX without an index: the value-only kernel, then the exchange with the
        * shard's first coordinate as the tie-break key. When the sharded axis is the
        * slowest reduced one, every element of a lower shard precedes every element of a
        * higher one, so "equal values go to the lower shard" is the single-GPU rule (it
