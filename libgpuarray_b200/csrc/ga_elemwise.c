@@ -97,6 +97,24 @@ static const char *compute_type(const GpuElemwise *ge, const gpuelemwise_arg *a)
 static void gen_prologue(const GpuElemwise *ge, ga_strb *sb, const ew_variant *v) {
   unsigned int j, k;
   ga_strb_puts(sb, "#include \"cluda.h\"\n");
+  {
+    /* experiments: GPUARRAY_B200_EW_DEFINES="NAME=VALUE;NAME=VALUE" puts #define lines in
+     * front of the template (its #ifndef defaults then stand back) */
+    const char *extra = getenv("GPUARRAY_B200_EW_DEFINES");
+    while (extra != NULL && *extra != '\0') {
+      const char *end = strchr(extra, ';'), *eq;
+      size_t len = end != NULL ? (size_t)(end - extra) : strlen(extra);
+      eq = memchr(extra, '=', len);
+      if (eq != NULL) {
+        ga_strb_puts(sb, "#define ");
+        ga_strb_putn(sb, extra, (size_t)(eq - extra));
+        ga_strb_puts(sb, " ");
+        ga_strb_putn(sb, eq + 1, len - (size_t)(eq - extra) - 1);
+        ga_strb_puts(sb, "\n");
+      }
+      extra = end != NULL ? end + 1 : NULL;
+    }
+  }
   if (ge->preamble != NULL) ga_strb_puts(sb, ge->preamble);
   ga_strb_puts(sb, "\n#define GA_EW_ARRAYS(X)");
   for (j = 0, k = 0; j < ge->n; j++) {
